@@ -1,0 +1,847 @@
+// Host runtime behind the C ABI (include/oeq_b200.h).
+//
+// Replaces the reference's native layer (openequivariance/extension/:
+// JITTPImpl / JITConvImpl in tensorproducts.hpp:50-98 and convolution.hpp:94-176,
+// the NVRTC + driver wrapper CUJITKernel in util/backend_cuda.hpp:139-300) and the
+// launch-shape half of its scheduler (implementations/ComputationSchedule.py:232-425).
+//
+// For a problem it (1) picks the thread mapping (channels per group, path
+// partitions, groups per CTA), (2) emits a small header of constexpr tables that
+// describes the problem -- irreps, instructions, Clebsch-Gordan nonzeros scaled by
+// the path weights, the mapping -- (3) compiles the hand-written kernel templates
+// in csrc/*.cuh against it with NVRTC for sm_100a, caching the CUBIN on disk, and
+// (4) launches through the CUDA runtime's library API on the caller's stream.
+// No kernel body is generated; no CPU fallback exists.
+
+#include <cuda_runtime.h>
+#include <dlfcn.h>
+#include <nvrtc.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <fstream>
+#include <mutex>
+#include <sstream>
+#include <string>
+#include <vector>
+
+#include "../../include/oeq_b200.h"
+
+namespace {
+
+thread_local std::string g_error;
+int fail(int code, const std::string& msg) {
+    g_error = msg;
+    return code;
+}
+#define OEQ_CUDA(expr)                                                                          \
+    do {                                                                                        \
+        cudaError_t e_ = (expr);                                                                \
+        if (e_ != cudaSuccess)                                                                  \
+            return fail(OEQ_ERR_CUDA, std::string(#expr) + ": " + cudaGetErrorString(e_));      \
+    } while (0)
+
+std::mutex g_mutex;
+std::string g_kernel_dir, g_cache_dir;
+
+std::string library_dir() {
+    Dl_info info;
+    if (dladdr(reinterpret_cast<void*>(&library_dir), &info) && info.dli_fname) {
+        std::string p(info.dli_fname);
+        size_t slash = p.find_last_of('/');
+        return slash == std::string::npos ? std::string(".") : p.substr(0, slash);
+    }
+    return ".";
+}
+std::string kernel_dir() {
+    if (!g_kernel_dir.empty()) return g_kernel_dir;
+    if (const char* e = getenv("OEQ_B200_KERNEL_DIR")) return e;
+    return library_dir() + "/csrc";
+}
+std::string cache_dir() {
+    if (!g_cache_dir.empty()) return g_cache_dir;
+    if (const char* e = getenv("OEQ_B200_CACHE_DIR")) return e;
+    return library_dir() + "/_kcache";
+}
+int env_int(const char* name, int fallback) {
+    const char* e = getenv(name);
+    return e && *e ? atoi(e) : fallback;
+}
+
+// ------------------------------------------------------------------ NVRTC, loaded on first use
+
+struct Nvrtc {
+    void* lib = nullptr;
+    decltype(&nvrtcCreateProgram) create = nullptr;
+    decltype(&nvrtcCompileProgram) compile = nullptr;
+    decltype(&nvrtcGetCUBINSize) cubin_size = nullptr;
+    decltype(&nvrtcGetCUBIN) cubin = nullptr;
+    decltype(&nvrtcGetProgramLogSize) log_size = nullptr;
+    decltype(&nvrtcGetProgramLog) log = nullptr;
+    decltype(&nvrtcDestroyProgram) destroy = nullptr;
+    decltype(&nvrtcGetErrorString) error_string = nullptr;
+};
+Nvrtc g_nvrtc;
+
+int load_nvrtc() {
+    if (g_nvrtc.lib) return OEQ_OK;
+    const char* names[] = {"libnvrtc.so.12", "/usr/local/cuda/lib64/libnvrtc.so.12", "libnvrtc.so",
+                           "/usr/local/cuda/lib64/libnvrtc.so"};
+    void* lib = nullptr;
+    for (const char* n : names) {
+        lib = dlopen(n, RTLD_NOW | RTLD_LOCAL);
+        if (lib) break;
+    }
+    if (!lib) return fail(OEQ_ERR_COMPILE, "cannot load libnvrtc (needed to specialise kernels)");
+#define OEQ_SYM(field, name)                                                      \
+    g_nvrtc.field = reinterpret_cast<decltype(g_nvrtc.field)>(dlsym(lib, name));  \
+    if (!g_nvrtc.field) return fail(OEQ_ERR_COMPILE, std::string("libnvrtc lacks ") + name);
+    OEQ_SYM(create, "nvrtcCreateProgram")
+    OEQ_SYM(compile, "nvrtcCompileProgram")
+    OEQ_SYM(cubin_size, "nvrtcGetCUBINSize")
+    OEQ_SYM(cubin, "nvrtcGetCUBIN")
+    OEQ_SYM(log_size, "nvrtcGetProgramLogSize")
+    OEQ_SYM(log, "nvrtcGetProgramLog")
+    OEQ_SYM(destroy, "nvrtcDestroyProgram")
+    OEQ_SYM(error_string, "nvrtcGetErrorString")
+#undef OEQ_SYM
+    g_nvrtc.lib = lib;
+    return OEQ_OK;
+}
+
+// ------------------------------------------------------------------ problem model
+
+struct Irrep {
+    int mul, l, parity, dim, off;
+};
+struct Instr {
+    int i1, i2, io, mode;
+    double pw;
+    std::vector<int> ci, cj, ck;
+    std::vector<double> cv;
+    int w_off;  // first weight of the instruction (same in e3nn and kernel order)
+    long long cost() const { return (long long)cv.size(); }
+};
+struct Problem {
+    std::vector<Irrep> in1, in2, out;
+    std::vector<Instr> instr;
+    int dtype = 0, shared = 0, mode = 0;
+    int x_dim = 0, y_dim = 0, z_dim = 0, w_numel = 0;
+    int elem() const { return dtype == OEQ_F64 ? 8 : 4; }
+};
+
+int ingest_irreps(const oeq_irrep* src, int n, std::vector<Irrep>& dst, int& dim, const char* what) {
+    if (n < 0 || (n > 0 && !src)) return fail(OEQ_ERR_INVALID, std::string(what) + ": null irreps");
+    int off = 0;
+    for (int i = 0; i < n; ++i) {
+        if (src[i].mul < 0 || src[i].l < 0 || (src[i].parity != 1 && src[i].parity != -1))
+            return fail(OEQ_ERR_INVALID, std::string(what) + ": bad irrep entry");
+        Irrep r{src[i].mul, src[i].l, src[i].parity, 2 * src[i].l + 1, off};
+        off += r.mul * r.dim;
+        dst.push_back(r);
+    }
+    dim = off;
+    return OEQ_OK;
+}
+
+int ingest(const oeq_problem_desc* d, Problem& p) {
+    if (!d) return fail(OEQ_ERR_INVALID, "null problem descriptor");
+    if (d->dtype != OEQ_F32 && d->dtype != OEQ_F64) return fail(OEQ_ERR_INVALID, "dtype must be OEQ_F32 or OEQ_F64");
+    p.dtype = d->dtype;
+    p.shared = d->shared_weights ? 1 : 0;
+    int rc;
+    if ((rc = ingest_irreps(d->in1, d->n_in1, p.in1, p.x_dim, "irreps_in1"))) return rc;
+    if ((rc = ingest_irreps(d->in2, d->n_in2, p.in2, p.y_dim, "irreps_in2"))) return rc;
+    if ((rc = ingest_irreps(d->out, d->n_out, p.out, p.z_dim, "irreps_out"))) return rc;
+    if (d->n_instr <= 0 || !d->instr)
+        return fail(OEQ_ERR_INVALID, "Tensor product problem has no valid intructions!");
+    p.mode = d->instr[0].mode;
+    if (p.mode != OEQ_MODE_UVU && p.mode != OEQ_MODE_UVW)
+        return fail(OEQ_ERR_UNSUPPORTED, "connection mode must be 'uvu' or 'uvw'");
+    int w = 0;
+    for (int n = 0; n < d->n_instr; ++n) {
+        const oeq_instruction& s = d->instr[n];
+        if (s.mode != p.mode) return fail(OEQ_ERR_UNSUPPORTED, "all instructions must share one connection mode");
+        if (s.i_in1 < 0 || s.i_in1 >= d->n_in1 || s.i_in2 < 0 || s.i_in2 >= d->n_in2 || s.i_out < 0 ||
+            s.i_out >= d->n_out)
+            return fail(OEQ_ERR_INVALID, "instruction index out of range");
+        const Irrep &a = p.in1[s.i_in1], &b = p.in2[s.i_in2], &c = p.out[s.i_out];
+        if (a.parity * b.parity != c.parity || c.l < std::abs(a.l - b.l) || c.l > a.l + b.l)
+            return fail(OEQ_ERR_INVALID, "instruction violates the selection rules");
+        if (p.mode == OEQ_MODE_UVU && a.mul != c.mul)
+            return fail(OEQ_ERR_INVALID, "'uvu' needs equal multiplicities of the first input and the output");
+        Instr t;
+        t.i1 = s.i_in1; t.i2 = s.i_in2; t.io = s.i_out; t.mode = s.mode; t.pw = s.path_weight;
+        if (s.cg_nnz < 0 || (s.cg_nnz > 0 && (!s.cg_i || !s.cg_j || !s.cg_k || !s.cg_value)))
+            return fail(OEQ_ERR_INVALID, "instruction has a malformed Clebsch-Gordan list");
+        for (int z = 0; z < s.cg_nnz; ++z) {
+            if (s.cg_i[z] < 0 || s.cg_i[z] >= a.dim || s.cg_j[z] < 0 || s.cg_j[z] >= b.dim || s.cg_k[z] < 0 ||
+                s.cg_k[z] >= c.dim)
+                return fail(OEQ_ERR_INVALID, "Clebsch-Gordan index out of range");
+            t.ci.push_back(s.cg_i[z]); t.cj.push_back(s.cg_j[z]); t.ck.push_back(s.cg_k[z]);
+            t.cv.push_back(s.cg_value[z] * s.path_weight);
+        }
+        t.w_off = w;
+        w += a.mul * b.mul * (p.mode == OEQ_MODE_UVW ? c.mul : 1);
+        p.instr.push_back(std::move(t));
+    }
+    p.w_numel = w;
+    return OEQ_OK;
+}
+
+// ------------------------------------------------------------------ thread mapping for the "uvu" kernels
+
+enum Kind { K_FWD_BATCH = 0, K_BWD_BATCH, K_FWD_DET, K_BWD_DET, K_FWD_ATOMIC, K_BWD_ATOMIC, K_COUNT };
+bool kind_is_bwd(int k) { return k & 1; }
+bool kind_is_batch(int k) { return k < 2; }
+
+constexpr int SMEM_LIMIT = 232448;  // opt-in dynamic shared memory per CTA on sm_100
+int pad16(int b) { return (b + 15) / 16 * 16; }
+
+struct Mapping {
+    int mulg = 32, nch = 1, ps = 1, ng = 1;
+    std::vector<int> part_of_out, part_of_instr, zr_off, xr_off;
+    int zpc_max = 1, xpc = 1;
+    int stage_bytes = 0, extra_bytes = 0, sw_bytes = 0;
+    int threads() const { return ng * mulg * ps + 32; }
+    int fixed_bytes(int stages) const { return ng * stages * 48 + pad16((2 * ng + 2) * 8) + sw_bytes; }
+    int smem(int stages) const { return fixed_bytes(stages) + ng * (stages * stage_bytes + extra_bytes); }
+    int max_stages() const {
+        int s = 0;
+        while (s < 8 && smem(s + 1) <= SMEM_LIMIT) ++s;
+        return s;
+    }
+};
+
+void assign_partitions(const Problem& p, bool bwd, Mapping& m) {
+    // longest-processing-time first; forward units are output irreps, backward units instructions
+    const int n_units = bwd ? (int)p.instr.size() : (int)p.out.size();
+    std::vector<long long> cost(n_units, 0);
+    for (size_t i = 0; i < p.instr.size(); ++i) {
+        long long c = p.instr[i].cost() * p.in2[p.instr[i].i2].mul + 2;
+        cost[bwd ? (int)i : p.instr[i].io] += c;
+    }
+    std::vector<int> order(n_units);
+    for (int i = 0; i < n_units; ++i) order[i] = i;
+    std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return cost[a] > cost[b]; });
+    std::vector<long long> load(m.ps, 0);
+    std::vector<int> part(n_units, 0);
+    for (int unit : order) {
+        int best = 0;
+        for (int q = 1; q < m.ps; ++q)
+            if (load[q] < load[best]) best = q;
+        part[unit] = best;
+        load[best] += cost[unit];
+    }
+    m.part_of_out.assign(p.out.size(), 0);
+    m.part_of_instr.assign(p.instr.size(), 0);
+    if (bwd) {
+        m.part_of_instr = part;
+    } else {
+        m.part_of_out = part;
+        for (size_t i = 0; i < p.instr.size(); ++i) m.part_of_instr[i] = part[p.instr[i].io];
+    }
+    // register offsets of the per-channel accumulators
+    m.zr_off.assign(p.out.size(), 0);
+    std::vector<int> fill(m.ps, 0);
+    for (size_t o = 0; o < p.out.size(); ++o) {
+        int q = bwd ? 0 : m.part_of_out[o];
+        m.zr_off[o] = fill[q];
+        fill[q] += p.out[o].dim;
+    }
+    m.zpc_max = std::max(1, *std::max_element(fill.begin(), fill.end()));
+    m.xr_off.assign(p.in1.size(), 0);
+    int x = 0;
+    for (size_t a = 0; a < p.in1.size(); ++a) {
+        m.xr_off[a] = x;
+        x += p.in1[a].dim;
+    }
+    m.xpc = std::max(1, x);
+}
+
+int choose_mapping(const Problem& p, int kind, Mapping& m) {
+    const bool bwd = kind_is_bwd(kind), batch = kind_is_batch(kind);
+    int maxmul = 1;
+    for (const Instr& t : p.instr) maxmul = std::max(maxmul, p.in1[t.i1].mul);
+    for (const Irrep& r : p.out) maxmul = std::max(maxmul, r.mul);
+    m.mulg = std::min((maxmul + 31) / 32 * 32, 256);
+    m.nch = (maxmul + m.mulg - 1) / m.mulg;
+    const int e = p.elem();
+    const int xb = pad16(p.x_dim * e), yb = pad16(p.y_dim * e), zb = pad16(p.z_dim * e);
+    const int wb = p.shared ? 0 : pad16(p.w_numel * e);
+    m.sw_bytes = p.shared ? pad16(p.w_numel * e) : 0;
+    m.stage_bytes = xb + yb + wb + (bwd ? zb : 0);
+    int zpc = 0;
+    for (const Irrep& r : p.out) zpc += r.dim;
+    const int units = bwd ? (int)p.instr.size() : (int)p.out.size();
+
+    auto extra = [&](int ps) {
+        const int warps = m.mulg * ps / 32;
+        if (!bwd) return batch ? 2 * zb : 0;
+        return ps * xb + 2 * warps * yb + (p.shared ? pad16(p.w_numel * e) : 0);
+    };
+    int best_ps = 0, best_ng = 0;
+    long long best_score = -1;
+    for (int ps : {1, 2, 4}) {
+        if (ps > 1 && ps > units) break;
+        const int g = m.mulg * ps;
+        if (g > 512) break;
+        if (!bwd && !batch && zpc * m.nch / ps > 64 && ps < 4 && ps * 2 <= units) continue;  // register pressure
+        Mapping t = m;
+        t.ps = ps;
+        t.extra_bytes = extra(ps);
+        int ng = 0;
+        for (int cand = 1; cand <= 8; ++cand) {
+            t.ng = cand;
+            if (cand * g > 512) break;
+            if (t.smem(2) > SMEM_LIMIT) break;
+            ng = cand;
+        }
+        if (ng == 0) continue;
+        const long long threads = (long long)ng * g;
+        // enough threads to hide latency first, then as few partitions as possible
+        const long long score = std::min<long long>(threads, 512) * 8 - ps;
+        if (score > best_score) {
+            best_score = score;
+            best_ps = ps;
+            best_ng = ng;
+        }
+    }
+    if (best_ps == 0)
+        return fail(OEQ_ERR_UNSUPPORTED, "problem rows do not fit in shared memory (two stages of one item exceed 227 KB)");
+    m.ps = env_int("OEQ_B200_PS", best_ps);
+    m.ng = env_int("OEQ_B200_NG", best_ng);
+    m.extra_bytes = extra(m.ps);
+    if (m.smem(2) > SMEM_LIMIT || m.ng * m.mulg * m.ps > 992 || m.ng < 1 || m.ng > 8)
+        return fail(OEQ_ERR_INVALID, "OEQ_B200_PS / OEQ_B200_NG override does not fit");
+    assign_partitions(p, bwd, m);
+    if (env_int("OEQ_B200_VERBOSE", 0))
+        fprintf(stderr, "[oeq_b200] kind %d: mulg %d nch %d ps %d ng %d threads %d stage %d B extra %d B max stages %d\n",
+                kind, m.mulg, m.nch, m.ps, m.ng, m.threads(), m.stage_bytes, m.extra_bytes, m.max_stages());
+    return OEQ_OK;
+}
+
+// ------------------------------------------------------------------ descriptor text
+
+template <class V, class F>
+void emit_array(std::ostringstream& s, const char* type, const char* name, const V& v, F&& fmt) {
+    s << "constexpr " << type << " " << name << "[] = {";
+    if (v.empty()) s << "0";
+    for (size_t i = 0; i < v.size(); ++i) {
+        if (i) s << ", ";
+        fmt(s, v[i]);
+    }
+    s << "};\n";
+}
+
+std::string descriptor_text(const Problem& p, const Mapping& m) {
+    std::ostringstream s;
+    s.precision(17);
+    s << "// problem descriptor (tables only; kernel bodies are in the included headers)\n";
+    s << "namespace oeqd {\n";
+    s << "typedef " << (p.dtype == OEQ_F64 ? "double" : "float") << " T;\n";
+    s << "constexpr int X_DIM = " << p.x_dim << ", Y_DIM = " << p.y_dim << ", Z_DIM = " << p.z_dim
+      << ", W_NUMEL = " << p.w_numel << ";\n";
+    s << "constexpr bool SHARED_W = " << (p.shared ? "true" : "false") << ";\n";
+    s << "constexpr int N_IN1 = " << p.in1.size() << ", N_IN2 = " << p.in2.size() << ", N_OUT = " << p.out.size()
+      << ", N_INSTR = " << p.instr.size() << ";\n";
+    auto put_int = [](std::ostringstream& o, int v) { o << v; };
+    auto irreps = [&](const char* prefix, const std::vector<Irrep>& v) {
+        std::vector<int> mul, dim, off;
+        for (const Irrep& r : v) {
+            mul.push_back(r.mul); dim.push_back(r.dim); off.push_back(r.off);
+        }
+        emit_array(s, "int", (std::string(prefix) + "_MUL").c_str(), mul, put_int);
+        emit_array(s, "int", (std::string(prefix) + "_D").c_str(), dim, put_int);
+        emit_array(s, "int", (std::string(prefix) + "_OFF").c_str(), off, put_int);
+    };
+    irreps("IN1", p.in1);
+    irreps("IN2", p.in2);
+    irreps("OUT", p.out);
+    std::vector<int> i1, i2, io, woff, begin, ci, cj, ck;
+    std::vector<double> cv;
+    for (const Instr& t : p.instr) {
+        i1.push_back(t.i1); i2.push_back(t.i2); io.push_back(t.io); woff.push_back(t.w_off);
+        begin.push_back((int)ci.size());
+        ci.insert(ci.end(), t.ci.begin(), t.ci.end());
+        cj.insert(cj.end(), t.cj.begin(), t.cj.end());
+        ck.insert(ck.end(), t.ck.begin(), t.ck.end());
+        cv.insert(cv.end(), t.cv.begin(), t.cv.end());
+    }
+    begin.push_back((int)ci.size());
+    emit_array(s, "int", "I_IN1", i1, put_int);
+    emit_array(s, "int", "I_IN2", i2, put_int);
+    emit_array(s, "int", "I_OUT", io, put_int);
+    emit_array(s, "int", "W_OFF", woff, put_int);
+    emit_array(s, "int", "CG_BEGIN", begin, put_int);
+    emit_array(s, "int", "CG_I", ci, put_int);
+    emit_array(s, "int", "CG_J", cj, put_int);
+    emit_array(s, "int", "CG_K", ck, put_int);
+    const bool f64 = p.dtype == OEQ_F64;
+    emit_array(s, "T", "CG_V", cv, [f64](std::ostringstream& o, double v) {
+        char buf[64];
+        if (f64) snprintf(buf, sizeof buf, "%a", v);
+        else snprintf(buf, sizeof buf, "%af", (double)(float)v);
+        o << buf;
+    });
+    s << "constexpr int MULG = " << m.mulg << ", NCH = " << m.nch << ", PS = " << m.ps << ", NG = " << m.ng << ";\n";
+    emit_array(s, "int", "FWD_PART_OF_OUT", m.part_of_out, put_int);
+    emit_array(s, "int", "BWD_PART_OF_INSTR", m.part_of_instr, put_int);
+    emit_array(s, "int", "ZR_OFF", m.zr_off, put_int);
+    emit_array(s, "int", "XR_OFF", m.xr_off, put_int);
+    s << "constexpr int ZPC_MAX = " << m.zpc_max << ", XPC = " << m.xpc << ";\n";
+    s << "}  // namespace oeqd\n";
+    return s.str();
+}
+
+// ------------------------------------------------------------------ compile + cache
+
+unsigned long long fnv1a(const std::string& s, unsigned long long h = 1469598103934665603ull) {
+    for (unsigned char c : s) {
+        h ^= c;
+        h *= 1099511628211ull;
+    }
+    return h;
+}
+
+bool read_file(const std::string& path, std::string& out) {
+    std::ifstream f(path, std::ios::binary);
+    if (!f) return false;
+    std::ostringstream ss;
+    ss << f.rdbuf();
+    out = ss.str();
+    return true;
+}
+
+struct Compiled {
+    std::string cubin;
+    std::string log;
+};
+
+int compile_kernel(const std::string& descriptor, const std::string& main_header, int kernel_id, Compiled& out) {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    const std::string dir = kernel_dir();
+    std::string common, body;
+    if (!read_file(dir + "/oeq_common.cuh", common) || !read_file(dir + "/" + main_header, body))
+        return fail(OEQ_ERR_COMPILE, "kernel headers not found in " + dir);
+    const std::string source = descriptor + "#define OEQ_KERNEL " + std::to_string(kernel_id) + "\n#include \"" +
+                               main_header + "\"\n";
+    const std::string options = "-arch=sm_100a -std=c++17 -lineinfo -default-device -diag-suppress 177";
+    unsigned long long h = fnv1a(source);
+    h = fnv1a(common, h);
+    h = fnv1a(body, h);
+    h = fnv1a(options, h);
+    char name[64];
+    snprintf(name, sizeof name, "/k_%016llx.cubin", h);
+    const std::string cdir = cache_dir();
+    const std::string path = cdir + name;
+    if (!env_int("OEQ_B200_NO_CACHE", 0) && read_file(path, out.cubin) && !out.cubin.empty()) return OEQ_OK;
+
+    int rc = load_nvrtc();
+    if (rc) return rc;
+    nvrtcProgram prog;
+    if (g_nvrtc.create(&prog, source.c_str(), "oeq_specialisation.cu", 0, nullptr, nullptr) != NVRTC_SUCCESS)
+        return fail(OEQ_ERR_COMPILE, "nvrtcCreateProgram failed");
+    const std::string inc = "-I" + dir;
+    std::vector<const char*> opts = {"-arch=sm_100a", "-std=c++17", "-lineinfo", "-default-device", "-diag-suppress=177", inc.c_str()};
+    std::string ptxas_v = "--ptxas-options=-v";
+    if (env_int("OEQ_B200_VERBOSE", 0)) opts.push_back(ptxas_v.c_str());
+    nvrtcResult res = g_nvrtc.compile(prog, (int)opts.size(), opts.data());
+    size_t log_size = 0;
+    g_nvrtc.log_size(prog, &log_size);
+    out.log.assign(log_size, '\0');
+    if (log_size > 1) g_nvrtc.log(prog, &out.log[0]);
+    if (env_int("OEQ_B200_VERBOSE", 0) && log_size > 1) fprintf(stderr, "[oeq_b200] %s\n", out.log.c_str());
+    if (res != NVRTC_SUCCESS) {
+        g_nvrtc.destroy(&prog);
+        if (env_int("OEQ_B200_KEEP_SOURCE", 0)) {
+            std::ofstream f("/tmp/oeq_failed_specialisation.cu");
+            f << source;
+        }
+        return fail(OEQ_ERR_COMPILE, std::string("kernel specialisation failed: ") + g_nvrtc.error_string(res) + "\n" +
+                                         out.log.substr(0, 4000));
+    }
+    size_t size = 0;
+    g_nvrtc.cubin_size(prog, &size);
+    out.cubin.assign(size, '\0');
+    g_nvrtc.cubin(prog, &out.cubin[0]);
+    g_nvrtc.destroy(&prog);
+    mkdir(cdir.c_str(), 0755);
+    const std::string tmp = path + ".tmp" + std::to_string((long long)getpid());
+    {
+        std::ofstream f(tmp, std::ios::binary);
+        f.write(out.cubin.data(), (std::streamsize)out.cubin.size());
+    }
+    rename(tmp.c_str(), path.c_str());
+    return OEQ_OK;
+}
+
+// ------------------------------------------------------------------ a specialised kernel
+
+struct Kernel {
+    Mapping map;
+    Compiled code;
+    bool compiled = false, loaded = false;
+    cudaLibrary_t lib = nullptr;
+    cudaKernel_t fn = nullptr, reduce_fn = nullptr;
+    int stages = 0, smem = 0, regs = 0, ctas_per_sm = 1, sm_count = 0;
+};
+
+int build_uvu(const Problem& p, int kind, Kernel& k) {
+    int rc = choose_mapping(p, kind, k.map);
+    if (rc) return rc;
+    rc = compile_kernel(descriptor_text(p, k.map), "uvu_kernels.cuh", kind, k.code);
+    if (rc) return rc;
+    k.compiled = true;
+    return OEQ_OK;
+}
+
+int load_kernel(Kernel& k, const char* entry, bool want_reduce) {
+    if (k.loaded) return OEQ_OK;
+    OEQ_CUDA(cudaLibraryLoadData(&k.lib, k.code.cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0));
+    OEQ_CUDA(cudaLibraryGetKernel(&k.fn, k.lib, entry));
+    if (want_reduce) OEQ_CUDA(cudaLibraryGetKernel(&k.reduce_fn, k.lib, "oeq_reduce_partials"));
+    int dev = 0;
+    OEQ_CUDA(cudaGetDevice(&dev));
+    OEQ_CUDA(cudaDeviceGetAttribute(&k.sm_count, cudaDevAttrMultiProcessorCount, dev));
+    int stages = std::min(k.map.max_stages(), env_int("OEQ_B200_STAGES", 4));
+    if (stages < 2) return fail(OEQ_ERR_UNSUPPORTED, "not enough shared memory for two stages");
+    k.stages = stages;
+    k.smem = k.map.smem(stages);
+    OEQ_CUDA(cudaFuncSetAttribute((const void*)k.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, k.smem));
+    cudaFuncAttributes attr;
+    if (cudaFuncGetAttributes(&attr, (const void*)k.fn) == cudaSuccess) k.regs = attr.numRegs;
+    else (void)cudaGetLastError();
+    int occ = 1;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, (const void*)k.fn, k.map.threads(), k.smem) != cudaSuccess) {
+        (void)cudaGetLastError();
+        occ = 1;
+    }
+    k.ctas_per_sm = std::max(1, std::min(occ, env_int("OEQ_B200_CTAS_PER_SM", 4)));
+    k.loaded = true;
+    return OEQ_OK;
+}
+
+// Mirror of oeq::UvuParams (uvu_kernels.cuh).
+struct UvuParams {
+    const void* X; const void* Y; const void* W; void* Z;
+    const void* dZ; void* dX; void* dY; void* dW;
+    const long long* rows; const long long* cols; const long long* perm;
+    long long n_items, n_nodes;
+    void* ws;
+    int* status;
+    int stages, flags;
+};
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+int launch_uvu(Kernel& k, const Problem& p, UvuParams& prm, cudaStream_t stream) {
+    const int e = p.elem();
+    int flags = 0;
+    if ((p.x_dim * e) % 16 == 0 && aligned16(prm.X)) flags |= 1;
+    if ((p.y_dim * e) % 16 == 0 && aligned16(prm.Y)) flags |= 2;
+    if (!p.shared && (p.w_numel * e) % 16 == 0 && aligned16(prm.W)) flags |= 4;
+    const void* zlike = prm.dZ ? prm.dZ : prm.Z;
+    if ((p.z_dim * e) % 16 == 0 && aligned16(zlike)) flags |= 8;
+    if (env_int("OEQ_B200_NO_BULK", 0)) flags = 0;
+    prm.flags = flags;
+    prm.stages = k.stages;
+    long long want = (prm.n_items + k.map.ng - 1) / k.map.ng;
+    long long grid = std::max<long long>(1, std::min<long long>((long long)k.sm_count * k.ctas_per_sm, want));
+    void* args[] = {&prm};
+    OEQ_CUDA(cudaLaunchKernel((const void*)k.fn, dim3((unsigned)grid), dim3((unsigned)k.map.threads()), args,
+                              (size_t)k.smem, stream));
+    return OEQ_OK;
+}
+
+long long uvu_grid(const Kernel& k, long long n_items) {
+    long long want = (n_items + k.map.ng - 1) / k.map.ng;
+    return std::max<long long>(1, std::min<long long>((long long)k.sm_count * k.ctas_per_sm, want));
+}
+
+}  // namespace
+
+// ====================================================================== C ABI
+
+struct oeq_tp {
+    Problem prob;
+    Kernel fwd, bwd;
+    int* d_status = nullptr;
+    cudaStream_t last_stream = nullptr;
+};
+struct oeq_conv {
+    Problem prob;
+    bool deterministic = false;
+    Kernel fwd, bwd;
+    int* d_status = nullptr;
+    cudaStream_t last_stream = nullptr;
+};
+
+extern "C" {
+
+const char* oeq_version(void) { return "oeq_b200 0.1 (sm_100a)"; }
+const char* oeq_last_error(void) { return g_error.c_str(); }
+
+int oeq_set_kernel_dir(const char* path) {
+    if (!path) return fail(OEQ_ERR_INVALID, "null path");
+    g_kernel_dir = path;
+    return OEQ_OK;
+}
+int oeq_set_cache_dir(const char* path) {
+    if (!path) return fail(OEQ_ERR_INVALID, "null path");
+    g_cache_dir = path;
+    return OEQ_OK;
+}
+
+static int check_conv_problem(const Problem& p) {
+    if (p.mode != OEQ_MODE_UVU) return fail(OEQ_ERR_UNSUPPORTED, "fused convolution supports 'uvu' problems only");
+    if (p.shared) return fail(OEQ_ERR_UNSUPPORTED, "fused convolution needs per-edge weights (shared_weights=False)");
+    for (const Irrep& r : p.in2)
+        if (r.mul != 1) return fail(OEQ_ERR_UNSUPPORTED, "fused convolution needs multiplicity 1 for every irrep of the second input");
+    return OEQ_OK;
+}
+
+int oeq_precompile(const oeq_problem_desc* desc, int kinds) {
+    Problem p;
+    int rc = ingest(desc, p);
+    if (rc) return rc;
+    if (p.mode != OEQ_MODE_UVU) return fail(OEQ_ERR_UNSUPPORTED, "'uvw' kernels are not available in this build");
+    auto one = [&](int kind) {
+        Kernel k;
+        return build_uvu(p, kind, k);
+    };
+    if (kinds & 1) {
+        if ((rc = one(K_FWD_BATCH)) || (rc = one(K_BWD_BATCH))) return rc;
+    }
+    if (kinds & 6) {
+        if ((rc = check_conv_problem(p))) return rc;
+    }
+    if (kinds & 2) {
+        if ((rc = one(K_FWD_DET)) || (rc = one(K_BWD_DET))) return rc;
+    }
+    if (kinds & 4) {
+        if ((rc = one(K_FWD_ATOMIC)) || (rc = one(K_BWD_ATOMIC))) return rc;
+    }
+    return OEQ_OK;
+}
+
+// ---------------------------------------------------------------- batch TP
+
+int oeq_tp_create(const oeq_problem_desc* desc, oeq_tp** out) {
+    if (!out) return fail(OEQ_ERR_INVALID, "null output handle");
+    *out = nullptr;
+    oeq_tp* h = new oeq_tp();
+    int rc = ingest(desc, h->prob);
+    if (!rc && h->prob.mode != OEQ_MODE_UVU) rc = fail(OEQ_ERR_UNSUPPORTED, "'uvw' kernels are not available in this build");
+    if (!rc) rc = build_uvu(h->prob, K_FWD_BATCH, h->fwd);
+    if (!rc) rc = build_uvu(h->prob, K_BWD_BATCH, h->bwd);
+    if (rc) {
+        delete h;
+        return rc;
+    }
+    *out = h;
+    return OEQ_OK;
+}
+
+int oeq_tp_destroy(oeq_tp* h) {
+    if (!h) return OEQ_OK;
+    if (h->d_status) cudaFree(h->d_status);
+    if (h->fwd.lib) cudaLibraryUnload(h->fwd.lib);
+    if (h->bwd.lib) cudaLibraryUnload(h->bwd.lib);
+    delete h;
+    return OEQ_OK;
+}
+
+int64_t oeq_tp_weight_numel(const oeq_tp* h) { return h ? h->prob.w_numel : -1; }
+
+static int ensure_status(int** d_status) {
+    if (*d_status) return OEQ_OK;
+    OEQ_CUDA(cudaMalloc(d_status, sizeof(int)));
+    OEQ_CUDA(cudaMemset(*d_status, 0, sizeof(int)));
+    return OEQ_OK;
+}
+
+int oeq_tp_forward(oeq_tp* h, int64_t batch, const void* X, const void* Y, const void* W, void* Z, void* stream) {
+    if (!h) return fail(OEQ_ERR_INVALID, "null handle");
+    if (batch < 0) return fail(OEQ_ERR_INVALID, "negative batch");
+    if (batch == 0) return OEQ_OK;
+    if (!X || !Y || !W || !Z) return fail(OEQ_ERR_INVALID, "null buffer");
+    int rc = ensure_status(&h->d_status);
+    if (!rc) rc = load_kernel(h->fwd, "oeq_uvu_kernel", false);
+    if (rc) return rc;
+    UvuParams prm{};
+    prm.X = X; prm.Y = Y; prm.W = W; prm.Z = Z;
+    prm.n_items = batch; prm.n_nodes = batch; prm.status = h->d_status;
+    h->last_stream = (cudaStream_t)stream;
+    return launch_uvu(h->fwd, h->prob, prm, (cudaStream_t)stream);
+}
+
+size_t oeq_tp_workspace_bytes(const oeq_tp* h, int64_t batch) {
+    if (!h || !h->prob.shared || batch <= 0) return 0;
+    // one partial weight gradient per group of the backward launch (upper bound over devices: 256 SMs)
+    const long long groups = 256ll * 4 * h->bwd.map.ng;
+    return (size_t)groups * h->prob.w_numel * h->prob.elem();
+}
+
+int oeq_tp_backward(oeq_tp* h, int64_t batch, const void* X, const void* Y, const void* W, const void* dZ, void* dX,
+                    void* dY, void* dW, void* workspace, size_t workspace_bytes, void* stream) {
+    if (!h) return fail(OEQ_ERR_INVALID, "null handle");
+    if (batch < 0) return fail(OEQ_ERR_INVALID, "negative batch");
+    cudaStream_t st = (cudaStream_t)stream;
+    const Problem& p = h->prob;
+    if (batch == 0) {
+        if (p.shared && dW) OEQ_CUDA(cudaMemsetAsync(dW, 0, (size_t)p.w_numel * p.elem(), st));
+        return OEQ_OK;
+    }
+    if (!X || !Y || !W || !dZ || !dX || !dY || !dW) return fail(OEQ_ERR_INVALID, "null buffer");
+    int rc = ensure_status(&h->d_status);
+    if (!rc) rc = load_kernel(h->bwd, "oeq_uvu_kernel", true);
+    if (rc) return rc;
+    UvuParams prm{};
+    prm.X = X; prm.Y = Y; prm.W = W; prm.dZ = dZ; prm.dX = dX; prm.dY = dY; prm.dW = dW;
+    prm.n_items = batch; prm.n_nodes = batch; prm.status = h->d_status;
+    long long groups = 0;
+    if (p.shared) {
+        groups = uvu_grid(h->bwd, batch) * h->bwd.map.ng;
+        const size_t need = (size_t)groups * p.w_numel * p.elem();
+        if (!workspace || workspace_bytes < need)
+            return fail(OEQ_ERR_INVALID, "workspace too small for the shared-weight gradient (see oeq_tp_workspace_bytes)");
+        prm.ws = workspace;
+    }
+    h->last_stream = st;
+    rc = launch_uvu(h->bwd, p, prm, st);
+    if (rc) return rc;
+    if (p.shared) {
+        int n = p.w_numel;
+        const void* ws = workspace;
+        void* args[] = {&ws, &dW, &n, &groups};
+        OEQ_CUDA(cudaLaunchKernel((const void*)h->bwd.reduce_fn, dim3((n + 127) / 128), dim3(128), args, 0, st));
+    }
+    return OEQ_OK;
+}
+
+static int check_status(int* d_status, cudaStream_t st) {
+    if (!d_status) return OEQ_OK;
+    int v = 0;
+    OEQ_CUDA(cudaStreamSynchronize(st));
+    OEQ_CUDA(cudaMemcpy(&v, d_status, sizeof v, cudaMemcpyDeviceToHost));
+    if (v != 0) {
+        cudaMemset(d_status, 0, sizeof v);
+        return fail(OEQ_ERR_DEVICE_WAIT, "a kernel abandoned a bounded wait (code " + std::to_string(v) + ")");
+    }
+    return OEQ_OK;
+}
+int oeq_tp_check(oeq_tp* h) { return h ? check_status(h->d_status, h->last_stream) : fail(OEQ_ERR_INVALID, "null handle"); }
+
+static int launch_info(const Kernel& k, int* threads, int* ng, int* ps, int* stages, int* smem, int* regs) {
+    if (threads) *threads = k.map.threads();
+    if (ng) *ng = k.map.ng;
+    if (ps) *ps = k.map.ps;
+    if (stages) *stages = k.stages;
+    if (smem) *smem = k.smem;
+    if (regs) *regs = k.regs;
+    return OEQ_OK;
+}
+int oeq_tp_launch_info(const oeq_tp* h, int which, int* threads, int* ng, int* ps, int* stages, int* smem, int* regs) {
+    if (!h) return fail(OEQ_ERR_INVALID, "null handle");
+    return launch_info(which ? h->bwd : h->fwd, threads, ng, ps, stages, smem, regs);
+}
+
+// ---------------------------------------------------------------- fused convolution
+
+int oeq_conv_create(const oeq_problem_desc* desc, int deterministic, oeq_conv** out) {
+    if (!out) return fail(OEQ_ERR_INVALID, "null output handle");
+    *out = nullptr;
+    oeq_conv* h = new oeq_conv();
+    h->deterministic = deterministic != 0;
+    int rc = ingest(desc, h->prob);
+    if (!rc) rc = check_conv_problem(h->prob);
+    if (!rc) rc = build_uvu(h->prob, deterministic ? K_FWD_DET : K_FWD_ATOMIC, h->fwd);
+    if (!rc) rc = build_uvu(h->prob, deterministic ? K_BWD_DET : K_BWD_ATOMIC, h->bwd);
+    if (rc) {
+        delete h;
+        return rc;
+    }
+    *out = h;
+    return OEQ_OK;
+}
+
+int oeq_conv_destroy(oeq_conv* h) {
+    if (!h) return OEQ_OK;
+    if (h->d_status) cudaFree(h->d_status);
+    if (h->fwd.lib) cudaLibraryUnload(h->fwd.lib);
+    if (h->bwd.lib) cudaLibraryUnload(h->bwd.lib);
+    delete h;
+    return OEQ_OK;
+}
+
+size_t oeq_conv_workspace_bytes(const oeq_conv* h, int64_t nodes, int64_t edges) {
+    (void)h; (void)nodes; (void)edges;
+    return 0;  // the segmented reduction is node-aligned: no scratch, no fix-up pass
+}
+
+int oeq_conv_forward(oeq_conv* h, int64_t nodes, int64_t edges, const void* X, const void* Y, const void* W,
+                     const int64_t* rows, const int64_t* cols, void* Z, void* workspace, size_t workspace_bytes,
+                     void* stream) {
+    (void)workspace; (void)workspace_bytes;
+    if (!h) return fail(OEQ_ERR_INVALID, "null handle");
+    if (nodes < 0 || edges < 0) return fail(OEQ_ERR_INVALID, "negative size");
+    cudaStream_t st = (cudaStream_t)stream;
+    const Problem& p = h->prob;
+    if (nodes == 0) return OEQ_OK;
+    if (!Z) return fail(OEQ_ERR_INVALID, "null buffer");
+    if (edges == 0 || !h->deterministic)
+        OEQ_CUDA(cudaMemsetAsync(Z, 0, (size_t)nodes * p.z_dim * p.elem(), st));
+    if (edges == 0) return OEQ_OK;
+    if (!X || !Y || !W || !rows || !cols) return fail(OEQ_ERR_INVALID, "null buffer");
+    int rc = ensure_status(&h->d_status);
+    if (!rc) rc = load_kernel(h->fwd, "oeq_uvu_kernel", false);
+    if (rc) return rc;
+    UvuParams prm{};
+    prm.X = X; prm.Y = Y; prm.W = W; prm.Z = Z;
+    prm.rows = (const long long*)rows; prm.cols = (const long long*)cols;
+    prm.n_items = edges; prm.n_nodes = nodes; prm.status = h->d_status;
+    h->last_stream = st;
+    return launch_uvu(h->fwd, p, prm, st);
+}
+
+int oeq_conv_backward(oeq_conv* h, int64_t nodes, int64_t edges, const void* X, const void* Y, const void* W,
+                      const void* dZ, const int64_t* rows, const int64_t* cols, const int64_t* perm, void* dX,
+                      void* dY, void* dW, void* workspace, size_t workspace_bytes, void* stream) {
+    (void)workspace; (void)workspace_bytes;
+    if (!h) return fail(OEQ_ERR_INVALID, "null handle");
+    if (nodes < 0 || edges < 0) return fail(OEQ_ERR_INVALID, "negative size");
+    cudaStream_t st = (cudaStream_t)stream;
+    const Problem& p = h->prob;
+    if (nodes == 0) return OEQ_OK;
+    if (!dX) return fail(OEQ_ERR_INVALID, "null buffer");
+    if (edges == 0 || !h->deterministic)
+        OEQ_CUDA(cudaMemsetAsync(dX, 0, (size_t)nodes * p.x_dim * p.elem(), st));
+    if (edges == 0) return OEQ_OK;
+    if (!X || !Y || !W || !dZ || !rows || !cols || !dY || !dW) return fail(OEQ_ERR_INVALID, "null buffer");
+    if (h->deterministic && !perm)
+        return fail(OEQ_ERR_INVALID, "deterministic backward needs the sender-order permutation");
+    int rc = ensure_status(&h->d_status);
+    if (!rc) rc = load_kernel(h->bwd, "oeq_uvu_kernel", false);
+    if (rc) return rc;
+    UvuParams prm{};
+    prm.X = X; prm.Y = Y; prm.W = W; prm.dZ = dZ; prm.dX = dX; prm.dY = dY; prm.dW = dW;
+    prm.rows = (const long long*)rows; prm.cols = (const long long*)cols; prm.perm = (const long long*)perm;
+    prm.n_items = edges; prm.n_nodes = nodes; prm.status = h->d_status;
+    h->last_stream = st;
+    return launch_uvu(h->bwd, p, prm, st);
+}
+
+int oeq_conv_check(oeq_conv* h) { return h ? check_status(h->d_status, h->last_stream) : fail(OEQ_ERR_INVALID, "null handle"); }
+
+int oeq_conv_launch_info(const oeq_conv* h, int which, int* threads, int* ng, int* ps, int* stages, int* smem, int* regs) {
+    if (!h) return fail(OEQ_ERR_INVALID, "null handle");
+    return launch_info(which ? h->bwd : h->fwd, threads, ng, ps, stages, smem, regs);
+}
+
+}  // extern "C"

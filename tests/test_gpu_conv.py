@@ -1,0 +1,152 @@
+"""Fused graph convolution on the GPU (through the C ABI) vs the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+import openequivariance_b200 as oeq
+from oracle import tp_oracle as orc
+from conftest import problem_by_name
+from helpers import REL_TOL, rel_err, conv_inputs, random_graph
+
+pytestmark = pytest.mark.gpu
+
+
+def cuda(*arrays):
+    return [torch.from_numpy(np.ascontiguousarray(a)).cuda() for a in arrays]
+
+
+def check_conv(problem, nodes, rows, cols, seed, deterministic, dtype=np.float32):
+    edges = len(rows)
+    x, y, w, dz = conv_inputs(problem, nodes, edges, seed)
+    conv = oeq.TensorProductConv(problem, torch_op=True, deterministic=deterministic)
+    if deterministic:
+        rows, cols, order, perm = orc.coord_graph(rows, cols)
+        y, w = y[order], w[order]
+        index = cuda(rows, cols, perm)
+    else:
+        index = cuda(rows, cols)
+    xt, yt, wt, dzt = cuda(x, y, w, dz)
+    z = conv.forward(xt, yt, wt, *index)
+    dx, dy, dw = conv.backward_helper(xt, yt, wt, dzt, *index)
+    torch.cuda.synchronize()
+    conv.check_device_status()
+    tol = REL_TOL[dtype]
+    z_ref = orc.conv_forward(problem, x, y, w, rows, cols)
+    rx, ry, rw = orc.conv_backward(problem, x, y, w, dz, rows, cols)
+    assert rel_err(z.cpu().numpy(), z_ref) < tol
+    assert rel_err(dx.cpu().numpy(), rx) < tol
+    assert rel_err(dy.cpu().numpy(), ry) < tol
+    assert rel_err(dw.cpu().numpy(), rw) < tol
+    return conv, (xt, yt, wt, dzt, index), (z, dx, dy, dw)
+
+
+@pytest.mark.parametrize("deterministic", [False, True], ids=["atomic", "deterministic"])
+@pytest.mark.parametrize("name", ["readme", "nequip_32", "cw_mixed", "mace_128", "mace_large_128"])
+def test_small_random_graph(name, deterministic):
+    p = problem_by_name(name)
+    nodes = 23
+    rows, cols = random_graph(nodes, 150, seed=2)           # duplicates, self loops, asymmetric
+    check_conv(p, nodes, rows, cols, 9, deterministic)
+
+
+@pytest.mark.parametrize("deterministic", [False, True], ids=["atomic", "deterministic"])
+def test_fp64(deterministic):
+    p = problem_by_name("nequip_32", irrep_dtype=np.float64, weight_dtype=np.float64)
+    rows, cols = random_graph(40, 300, seed=3, symmetric=True)
+    check_conv(p, 40, rows, cols, 10, deterministic, dtype=np.float64)
+
+
+@pytest.mark.parametrize("deterministic", [False, True], ids=["atomic", "deterministic"])
+def test_isolated_nodes_and_hubs(deterministic):
+    """Receivers without edges must come out as zero rows; one node receives most edges."""
+    p = problem_by_name("nequip_32")
+    nodes = 300
+    rng = np.random.default_rng(4)
+    rows = np.concatenate([np.full(2000, 17), rng.integers(100, 200, 500)]).astype(np.int64)
+    cols = np.concatenate([rng.integers(0, nodes, 2000), rng.integers(250, 300, 500)]).astype(np.int64)
+    conv, _, (z, dx, _, _) = check_conv(p, nodes, rows, cols, 11, deterministic)
+    untouched = np.setdiff1d(np.arange(nodes), rows)
+    assert torch.count_nonzero(z[torch.from_numpy(untouched).cuda()]) == 0
+    silent = np.setdiff1d(np.arange(nodes), cols)
+    assert torch.count_nonzero(dx[torch.from_numpy(silent).cuda()]) == 0
+
+
+@pytest.mark.parametrize("deterministic", [False, True], ids=["atomic", "deterministic"])
+@pytest.mark.parametrize("edges", [0, 1, 5])
+def test_tiny_edge_counts(edges, deterministic):
+    p = problem_by_name("nequip_32")
+    nodes = 6
+    rows, cols = random_graph(nodes, edges, seed=5)
+    if edges == 0:
+        conv = oeq.TensorProductConv(p, torch_op=True, deterministic=deterministic)
+        x, y, w, dz = conv_inputs(p, nodes, 0, 1)
+        idx = cuda(rows, cols) + (cuda(rows) if deterministic else [])
+        xt, yt, wt, dzt = cuda(x, y, w, dz)
+        z = conv.forward(xt, yt, wt, *idx)
+        dx, dy, dw = conv.backward_helper(xt, yt, wt, dzt, *idx)
+        assert z.shape == (nodes, p.irreps_out.dim) and torch.count_nonzero(z) == 0
+        assert torch.count_nonzero(dx) == 0 and dy.shape[0] == 0 and dw.shape[0] == 0
+    else:
+        check_conv(p, nodes, rows, cols, 12, deterministic)
+
+
+def test_deterministic_is_bit_reproducible_and_matches_atomic():
+    p = problem_by_name("nequip_32")
+    nodes = 2000
+    rows, cols = random_graph(nodes, 30000, seed=6, symmetric=True)
+    conv, (xt, yt, wt, dzt, index), (z, dx, dy, dw) = check_conv(p, nodes, rows, cols, 13, True)
+    for _ in range(4):
+        z2 = conv.forward(xt, yt, wt, *index)
+        dx2, dy2, dw2 = conv.backward_helper(xt, yt, wt, dzt, *index)
+        assert torch.equal(z, z2) and torch.equal(dx, dx2) and torch.equal(dy, dy2) and torch.equal(dw, dw2)
+    atomic = oeq.TensorProductConv(p, torch_op=True, deterministic=False)
+    za = atomic.forward(xt, yt, wt, index[0], index[1])
+    dxa, dya, dwa = atomic.backward_helper(xt, yt, wt, dzt, index[0], index[1])
+    assert rel_err(za.cpu().numpy(), z.cpu().numpy()) < 1e-5
+    assert rel_err(dxa.cpu().numpy(), dx.cpu().numpy()) < 1e-5
+    assert rel_err(dya.cpu().numpy(), dy.cpu().numpy()) < 1e-5
+    assert rel_err(dwa.cpu().numpy(), dw.cpu().numpy()) < 1e-5
+
+
+def test_autograd_and_double_backward():
+    p = problem_by_name("cw_mixed", irrep_dtype=np.float64, weight_dtype=np.float64)
+    nodes = 12
+    rows, cols = random_graph(nodes, 60, seed=7)
+    rows, cols, order, perm = orc.coord_graph(rows, cols)
+    x, y, w, dz = conv_inputs(p, nodes, len(rows), 14)
+    conv = oeq.TensorProductConv(p, torch_op=True, deterministic=True)
+    r, c, pm = cuda(rows, cols, perm)
+    xt, yt, wt, dzt = (t.requires_grad_(True) for t in cuda(x, y, w, dz))
+    z = conv.forward(xt, yt, wt, r, c, pm)
+    dx, dy, dw = torch.autograd.grad(z, (xt, yt, wt), dzt, create_graph=True)
+    rng = np.random.default_rng(15)
+    gx, gy, gw = (torch.from_numpy(rng.normal(size=a.shape)).cuda() for a in (x, y, w))
+    scalar = (dx * gx).sum() + (dy * gy).sum() + (dw * gw).sum()
+    got = torch.autograd.grad(scalar, (xt, yt, wt, dzt))
+    # oracle: same scalar through autograd on the CPU
+    cx, cy, cw, cdz = (torch.from_numpy(a).requires_grad_(True) for a in (x, y, w, dz))
+    zz = orc.conv_torch(p, cx, cy, cw, torch.from_numpy(rows), torch.from_numpy(cols))
+    ex, ey, ew = torch.autograd.grad(zz, (cx, cy, cw), cdz, create_graph=True)
+    s = (ex * gx.cpu()).sum() + (ey * gy.cpu()).sum() + (ew * gw.cpu()).sum()
+    want = torch.autograd.grad(s, (cx, cy, cw, cdz))
+    for a, b in zip(got, want):
+        assert rel_err(a.cpu().numpy(), b.numpy()) < 1e-11
+
+
+def test_readme_call_sequence():
+    """The reference README's convolution example (3 nodes, 4 edges), atomic then deterministic."""
+    p = problem_by_name("readme")
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    rows = torch.tensor([0, 1, 1, 2], device="cuda")
+    cols = torch.tensor([1, 0, 2, 1], device="cuda")
+    X = torch.rand(3, 5, device="cuda", generator=gen)
+    Y = torch.rand(4, 7, device="cuda", generator=gen)
+    W = torch.rand(4, p.weight_numel, device="cuda", generator=gen)
+    tp_conv = oeq.TensorProductConv(p, torch_op=True, deterministic=False)
+    Z = tp_conv.forward(X, Y, W, rows, cols)
+    sender_perm = torch.argsort(cols, stable=True)
+    det = oeq.TensorProductConv(p, torch_op=True, deterministic=True)
+    Z2 = det.forward(X, Y, W, rows, cols, sender_perm)
+    ref = orc.conv_forward(p, X.cpu().numpy(), Y.cpu().numpy(), W.cpu().numpy(), rows.cpu().numpy(),
+                           cols.cpu().numpy())
+    assert rel_err(Z.cpu().numpy(), ref) < 1e-5 and rel_err(Z2.cpu().numpy(), ref) < 1e-5
