@@ -101,13 +101,16 @@ class TensorProductConv(TensorProductBase):
             if perm.shape != rows.shape or perm.dtype != torch.int64:
                 raise ValueError("sender_perm must be int64 and as long as rows")
 
-    def _forward_impl(self, x, y, w, rows, cols, perm=None):
+    def _forward_impl(self, x, y, w, rows, cols, perm=None, n_out=None):
+        """``n_out``: number of output rows when receivers index a different node set than
+        senders (a receiver shard of a partitioned graph); defaults to ``x.shape[0]``."""
         self._check(x, y, w, rows, cols, perm)
         x, y, w = x.contiguous(), y.contiguous(), w.contiguous()
         rows, cols = rows.contiguous(), cols.contiguous()
-        z = torch.empty((x.shape[0], self.L3.dim), dtype=x.dtype, device=x.device)
+        n_out = x.shape[0] if n_out is None else int(n_out)
+        z = torch.empty((n_out, self.L3.dim), dtype=x.dtype, device=x.device)
         with torch.cuda.device(x.device):
-            self.internal.forward(x.shape[0], rows.shape[0], x.data_ptr(), y.data_ptr(), w.data_ptr(),
+            self.internal.forward(n_out, rows.shape[0], x.data_ptr(), y.data_ptr(), w.data_ptr(),
                                   rows.data_ptr(), cols.data_ptr(), z.data_ptr(), 0, 0,
                                   torch.cuda.current_stream().cuda_stream)
         return z

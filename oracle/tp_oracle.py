@@ -71,16 +71,22 @@ def _layout(irreps):
     return out, off
 
 
-def tp_torch(problem, x, y, w, e3nn_style_pairs: bool = False):
+def tp_torch(problem, x, y, w, e3nn_style_pairs: bool = False, fold_second_input: bool = False):
     """Differentiable tensor product on torch tensors; ``w`` in e3nn order.
 
     ``w`` is ``[numel]`` when ``problem.shared_weights`` else ``[B, numel]``.
+    The two flags select other, algebraically identical contraction orders:
+    ``e3nn_style_pairs`` forms the outer product of the inputs first (the order in which
+    e3nn's generated code is written); ``fold_second_input`` contracts the second input
+    with the Clebsch-Gordan tensor first and then does one batched matmul per instruction
+    (the cheapest order on a CPU when the second input has multiplicity 1, which is what
+    an einsum path optimiser picks; used for the timed CPU baseline).
     """
     in1, _ = _layout(problem.irreps_in1)
     in2, _ = _layout(problem.irreps_in2)
     out, zdim = _layout(problem.irreps_out)
     batch = x.shape[0]
-    z = x.new_zeros(batch, zdim)
+    blocks = [None] * len(out)          # per output irrep: sum of its instructions' results
     shared = w.dim() == 1
     woff = 0
     pair_cache = {}
@@ -96,7 +102,12 @@ def tp_torch(problem, x, y, w, e3nn_style_pairs: bool = False):
         wb = w[..., woff:woff + n]
         woff += n
         mode = ins.connection_mode
-        if e3nn_style_pairs:
+        if fold_second_input and m2 == 1 and mode == "uvu":
+            folded = torch.einsum("bj,ijk->bik", ys[:, 0, :], c)          # [B, d1, d3]
+            r = torch.bmm(xs, folded)                                      # [B, m1, d3]
+            wv = wb.reshape(m1) if shared else wb.reshape(batch, m1)
+            r = r * (wv.unsqueeze(-1) if not shared else wv.reshape(1, m1, 1))
+        elif e3nn_style_pairs:
             # e3nn forms the outer product of the two inputs once per (in1, in2) pair
             key = (ins.i_in1, ins.i_in2)
             if key not in pair_cache:
@@ -118,8 +129,12 @@ def tp_torch(problem, x, y, w, e3nn_style_pairs: bool = False):
                 r = torch.einsum("buvk,uvw->bwk" if shared else "buvk,buvw->bwk", t, wv)
             else:
                 raise ValueError(f"oracle covers 'uvu' and 'uvw', got {mode!r}")
-        z[:, o3:o3 + m3 * d3] = z[:, o3:o3 + m3 * d3] + r.reshape(batch, m3 * d3)
-    return z
+        r = r.reshape(batch, m3 * d3)
+        blocks[ins.i_out] = r if blocks[ins.i_out] is None else blocks[ins.i_out] + r
+    for n, (m3, l3, _) in enumerate(out):
+        if blocks[n] is None:           # an output irrep that no instruction writes is zero
+            blocks[n] = x.new_zeros(batch, m3 * (2 * l3 + 1))
+    return torch.cat(blocks, dim=1) if blocks else x.new_zeros(batch, zdim)
 
 
 def _t(a, dtype=torch.float64, grad=False):
@@ -146,9 +161,9 @@ def scatter_sum_rows(src, index, dim_size):
         0, index.unsqueeze(-1).expand_as(src), src)
 
 
-def conv_torch(problem, x, y, w, rows, cols, e3nn_style_pairs: bool = False):
+def conv_torch(problem, x, y, w, rows, cols, e3nn_style_pairs: bool = False, fold_second_input: bool = False):
     """Gather sender rows, tensor product per edge, sum into receiver rows."""
-    messages = tp_torch(problem, x[cols], y, w, e3nn_style_pairs)
+    messages = tp_torch(problem, x[cols], y, w, e3nn_style_pairs, fold_second_input)
     out = x.new_zeros(x.shape[0], messages.shape[1])
     return out.index_add(0, rows, messages)
 

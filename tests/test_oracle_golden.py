@@ -102,3 +102,14 @@ def test_e3nn_style_pairing_is_the_same_function():
     a = orc.tp_torch(p, x, y, w)
     b = orc.tp_torch(p, x, y, w, e3nn_style_pairs=True)
     np.testing.assert_allclose(a.numpy(), b.numpy(), atol=1e-12)
+
+
+def test_folded_contraction_order_is_the_same_function():
+    p = problem_by_name("cw_mixed")
+    rng = np.random.default_rng(16)
+    x = torch.as_tensor(rng.normal(size=(6, p.irreps_in1.dim)))
+    y = torch.as_tensor(rng.normal(size=(6, p.irreps_in2.dim)))
+    w = torch.as_tensor(rng.normal(size=(6, p.weight_numel)))
+    a = orc.tp_torch(p, x, y, w)
+    b = orc.tp_torch(p, x, y, w, fold_second_input=True)
+    np.testing.assert_allclose(a.numpy(), b.numpy(), atol=1e-12)
