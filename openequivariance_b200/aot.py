@@ -31,6 +31,8 @@ def named_problems():
          BATCH | DET | ATOMIC),
         ("nequip_32", lambda dt: ChannelwiseTPP("32x0e+32x1o+32x2e", "0e+1o+2e", "32x0e+32x1o+32x2e",
                                                 irrep_dtype=dt, weight_dtype=dt), BATCH | DET | ATOMIC),
+        ("uvw_64", lambda dt: FullyConnectedTPProblem("64x0e+64x1o+64x2e", "0e+1o+2e", "64x0e+64x1o+64x2e",
+                                                      irrep_dtype=dt, weight_dtype=dt), BATCH),
         ("mace_large_128", lambda dt: ChannelwiseTPP("128x0e+128x1o+128x2e+128x3o", "1x0e+1x1o+1x2e+1x3o",
                                                      "128x0e+128x1o+128x2e+128x3o", irrep_dtype=dt,
                                                      weight_dtype=dt), BATCH | DET | ATOMIC),
@@ -62,8 +64,6 @@ def _jobs():
     for n, (_, make, kinds) in enumerate(named_problems()):
         jobs.append(("named", n, "f32", kinds))
     for n, entry in enumerate(_golden_test_problems()):
-        if entry["kind"] == "fully_connected":
-            continue
         conv_ok = entry["kind"] == "channelwise" or entry["name"] == "readme"
         for dt in ("f32", "f64"):
             jobs.append(("golden", n, dt, BATCH | ((DET | ATOMIC) if conv_ok else 0)))

@@ -339,7 +339,35 @@ void emit_array(std::ostringstream& s, const char* type, const char* name, const
     s << "};\n";
 }
 
-std::string descriptor_text(const Problem& p, const Mapping& m) {
+struct UvwConfig {
+    int tile_r = 16, uvc = 64, dmax = 1, mwmax = 1, threads = 256;
+    int smem(const Problem& p, bool bwd) const {
+        auto r4 = [](long long n) { return (n + 3) / 4 * 4; };
+        long long e = r4((long long)tile_r * p.x_dim) + r4((long long)tile_r * p.y_dim) + r4((long long)tile_r * p.z_dim) +
+                      r4((long long)uvc * tile_r * dmax);
+        if (bwd)
+            e += r4((long long)tile_r * p.x_dim) + r4((long long)tile_r * p.y_dim) + r4((long long)mwmax * tile_r * dmax) +
+                 r4((long long)uvc * tile_r * dmax);
+        return (int)std::min<long long>(e * p.elem(), 1ll << 30);
+    }
+};
+
+int choose_uvw(const Problem& p, bool bwd, UvwConfig& c) {
+    for (const Irrep& r : p.out) {
+        c.dmax = std::max(c.dmax, r.dim);
+        c.mwmax = std::max(c.mwmax, r.mul);
+    }
+    int max_uv = 1;
+    for (const Instr& t : p.instr) max_uv = std::max(max_uv, p.in1[t.i1].mul * p.in2[t.i2].mul);
+    c.uvc = std::min(64, max_uv);
+    for (int tile : {16, 8, 4}) {
+        c.tile_r = tile;
+        if (c.smem(p, bwd) <= SMEM_LIMIT) return OEQ_OK;
+    }
+    return fail(OEQ_ERR_UNSUPPORTED, "'uvw' problem rows do not fit in shared memory");
+}
+
+std::string descriptor_text(const Problem& p, const Mapping& m, const UvwConfig* uvw = nullptr) {
     std::ostringstream s;
     s.precision(17);
     s << "// problem descriptor (tables only; kernel bodies are in the included headers)\n";
@@ -395,6 +423,9 @@ std::string descriptor_text(const Problem& p, const Mapping& m) {
     emit_array(s, "int", "ZR_OFF", m.zr_off, put_int);
     emit_array(s, "int", "XR_OFF", m.xr_off, put_int);
     s << "constexpr int ZPC_MAX = " << m.zpc_max << ", XPC = " << m.xpc << ";\n";
+    if (uvw)
+        s << "constexpr int TILE_R = " << uvw->tile_r << ", UVC = " << uvw->uvc << ", DMAX = " << uvw->dmax
+          << ", MWMAX = " << uvw->mwmax << ", UVW_THREADS = " << uvw->threads << ";\n";
     s << "}  // namespace oeqd\n";
     return s.str();
 }
@@ -485,6 +516,8 @@ int compile_kernel(const std::string& descriptor, const std::string& main_header
 
 struct Kernel {
     Mapping map;
+    UvwConfig uvw;
+    bool is_uvw = false;
     Compiled code;
     bool compiled = false, loaded = false;
     cudaLibrary_t lib = nullptr;
@@ -499,6 +532,66 @@ int build_uvu(const Problem& p, int kind, Kernel& k) {
     if (rc) return rc;
     k.compiled = true;
     return OEQ_OK;
+}
+
+constexpr int K_UVW_FWD = 10, K_UVW_BWD = 11;
+
+int build_uvw(const Problem& p, int kind, Kernel& k) {
+    k.is_uvw = true;
+    int rc = choose_uvw(p, kind == K_UVW_BWD, k.uvw);
+    if (rc) return rc;
+    // the uvu mapping tables are emitted with neutral values so that one descriptor format serves both
+    k.map.part_of_out.assign(p.out.size(), 0);
+    k.map.part_of_instr.assign(p.instr.size(), 0);
+    k.map.zr_off.assign(p.out.size(), 0);
+    k.map.xr_off.assign(p.in1.size(), 0);
+    rc = compile_kernel(descriptor_text(p, k.map, &k.uvw), "uvw_kernels.cuh", kind, k.code);
+    if (rc) return rc;
+    k.compiled = true;
+    return OEQ_OK;
+}
+
+int build_tp(const Problem& p, bool bwd, Kernel& k) {
+    if (p.mode == OEQ_MODE_UVW) return build_uvw(p, bwd ? K_UVW_BWD : K_UVW_FWD, k);
+    return build_uvu(p, bwd ? K_BWD_BATCH : K_FWD_BATCH, k);
+}
+
+int load_uvw(Kernel& k, const Problem& p, bool bwd) {
+    if (k.loaded) return OEQ_OK;
+    OEQ_CUDA(cudaLibraryLoadData(&k.lib, k.code.cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0));
+    OEQ_CUDA(cudaLibraryGetKernel(&k.fn, k.lib, "oeq_uvw_kernel"));
+    OEQ_CUDA(cudaLibraryGetKernel(&k.reduce_fn, k.lib, "oeq_reduce_partials"));
+    int dev = 0;
+    OEQ_CUDA(cudaGetDevice(&dev));
+    OEQ_CUDA(cudaDeviceGetAttribute(&k.sm_count, cudaDevAttrMultiProcessorCount, dev));
+    k.smem = k.uvw.smem(p, bwd);
+    OEQ_CUDA(cudaFuncSetAttribute((const void*)k.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, k.smem));
+    cudaFuncAttributes attr;
+    if (cudaFuncGetAttributes(&attr, (const void*)k.fn) == cudaSuccess) k.regs = attr.numRegs;
+    else (void)cudaGetLastError();
+    int occ = 1;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, (const void*)k.fn, k.uvw.threads, k.smem) != cudaSuccess) {
+        (void)cudaGetLastError();
+        occ = 1;
+    }
+    k.ctas_per_sm = std::max(1, std::min(occ, 2));
+    k.map.ng = 1;
+    k.loaded = true;
+    return OEQ_OK;
+}
+
+// Mirror of oeq::UvwParams (uvw_kernels.cuh).
+struct UvwParams {
+    const void* X; const void* Y; const void* W; void* Z;
+    const void* dZ; void* dX; void* dY; void* dW;
+    void* ws;
+    long long batch;
+    int* status;
+};
+
+long long uvw_grid(const Kernel& k, long long batch) {
+    const long long tiles = (batch + k.uvw.tile_r - 1) / k.uvw.tile_r;
+    return std::max<long long>(1, std::min<long long>((long long)k.sm_count * k.ctas_per_sm, tiles));
 }
 
 int load_kernel(Kernel& k, const char* entry, bool want_reduce) {
@@ -610,7 +703,12 @@ int oeq_precompile(const oeq_problem_desc* desc, int kinds) {
     Problem p;
     int rc = ingest(desc, p);
     if (rc) return rc;
-    if (p.mode != OEQ_MODE_UVU) return fail(OEQ_ERR_UNSUPPORTED, "'uvw' kernels are not available in this build");
+    if (p.mode == OEQ_MODE_UVW) {
+        if (kinds & 6) return fail(OEQ_ERR_UNSUPPORTED, "fused convolution supports 'uvu' problems only");
+        Kernel f, b;
+        if ((rc = build_tp(p, false, f)) || (rc = build_tp(p, true, b))) return rc;
+        return OEQ_OK;
+    }
     auto one = [&](int kind) {
         Kernel k;
         return build_uvu(p, kind, k);
@@ -637,9 +735,8 @@ int oeq_tp_create(const oeq_problem_desc* desc, oeq_tp** out) {
     *out = nullptr;
     oeq_tp* h = new oeq_tp();
     int rc = ingest(desc, h->prob);
-    if (!rc && h->prob.mode != OEQ_MODE_UVU) rc = fail(OEQ_ERR_UNSUPPORTED, "'uvw' kernels are not available in this build");
-    if (!rc) rc = build_uvu(h->prob, K_FWD_BATCH, h->fwd);
-    if (!rc) rc = build_uvu(h->prob, K_BWD_BATCH, h->bwd);
+    if (!rc) rc = build_tp(h->prob, false, h->fwd);
+    if (!rc) rc = build_tp(h->prob, true, h->bwd);
     if (rc) {
         delete h;
         return rc;
@@ -672,19 +769,35 @@ int oeq_tp_forward(oeq_tp* h, int64_t batch, const void* X, const void* Y, const
     if (batch == 0) return OEQ_OK;
     if (!X || !Y || !W || !Z) return fail(OEQ_ERR_INVALID, "null buffer");
     int rc = ensure_status(&h->d_status);
-    if (!rc) rc = load_kernel(h->fwd, "oeq_uvu_kernel", false);
     if (rc) return rc;
+    h->last_stream = (cudaStream_t)stream;
+    if (h->prob.mode == OEQ_MODE_UVW) {
+        if ((rc = load_uvw(h->fwd, h->prob, false))) return rc;
+        UvwParams up{};
+        up.X = X; up.Y = Y; up.W = W; up.Z = Z; up.batch = batch; up.status = h->d_status;
+        void* args[] = {&up};
+        OEQ_CUDA(cudaLaunchKernel((const void*)h->fwd.fn, dim3((unsigned)uvw_grid(h->fwd, batch)),
+                                  dim3((unsigned)h->fwd.uvw.threads), args, (size_t)h->fwd.smem, (cudaStream_t)stream));
+        return OEQ_OK;
+    }
+    if ((rc = load_kernel(h->fwd, "oeq_uvu_kernel", false))) return rc;
     UvuParams prm{};
     prm.X = X; prm.Y = Y; prm.W = W; prm.Z = Z;
     prm.n_items = batch; prm.n_nodes = batch; prm.status = h->d_status;
-    h->last_stream = (cudaStream_t)stream;
     return launch_uvu(h->fwd, h->prob, prm, (cudaStream_t)stream);
 }
 
 size_t oeq_tp_workspace_bytes(const oeq_tp* h, int64_t batch) {
     if (!h || !h->prob.shared || batch <= 0) return 0;
-    // one partial weight gradient per group of the backward launch (upper bound over devices: 256 SMs)
-    const long long groups = 256ll * 4 * h->bwd.map.ng;
+    // one partial weight gradient per group (uvu) or per CTA (uvw) of the backward launch; sized for the
+    // largest grid the launch can use on any device (256 SMs)
+    long long groups;
+    if (h->prob.mode == OEQ_MODE_UVW) {
+        const long long tiles = (batch + h->bwd.uvw.tile_r - 1) / h->bwd.uvw.tile_r;
+        groups = std::min<long long>(tiles, 256ll * 2);
+    } else {
+        groups = 256ll * 4 * h->bwd.map.ng;
+    }
     return (size_t)groups * h->prob.w_numel * h->prob.elem();
 }
 
@@ -700,8 +813,31 @@ int oeq_tp_backward(oeq_tp* h, int64_t batch, const void* X, const void* Y, cons
     }
     if (!X || !Y || !W || !dZ || !dX || !dY || !dW) return fail(OEQ_ERR_INVALID, "null buffer");
     int rc = ensure_status(&h->d_status);
-    if (!rc) rc = load_kernel(h->bwd, "oeq_uvu_kernel", true);
     if (rc) return rc;
+    if (p.mode == OEQ_MODE_UVW) {
+        if ((rc = load_uvw(h->bwd, p, true))) return rc;
+        long long ctas = uvw_grid(h->bwd, batch);
+        if (p.shared) {
+            const size_t need = (size_t)ctas * p.w_numel * p.elem();
+            if (!workspace || workspace_bytes < need)
+                return fail(OEQ_ERR_INVALID, "workspace too small for the shared-weight gradient (see oeq_tp_workspace_bytes)");
+        }
+        UvwParams up{};
+        up.X = X; up.Y = Y; up.W = W; up.dZ = dZ; up.dX = dX; up.dY = dY; up.dW = dW; up.ws = workspace;
+        up.batch = batch; up.status = h->d_status;
+        h->last_stream = st;
+        void* args[] = {&up};
+        OEQ_CUDA(cudaLaunchKernel((const void*)h->bwd.fn, dim3((unsigned)ctas), dim3((unsigned)h->bwd.uvw.threads), args,
+                                  (size_t)h->bwd.smem, st));
+        if (p.shared) {
+            int n = p.w_numel;
+            const void* ws = workspace;
+            void* rargs[] = {&ws, &dW, &n, &ctas};
+            OEQ_CUDA(cudaLaunchKernel((const void*)h->bwd.reduce_fn, dim3((n + 127) / 128), dim3(128), rargs, 0, st));
+        }
+        return OEQ_OK;
+    }
+    if ((rc = load_kernel(h->bwd, "oeq_uvu_kernel", true))) return rc;
     UvuParams prm{};
     prm.X = X; prm.Y = Y; prm.W = W; prm.dZ = dZ; prm.dX = dX; prm.dY = dY; prm.dW = dW;
     prm.n_items = batch; prm.n_nodes = batch; prm.status = h->d_status;
@@ -739,7 +875,7 @@ static int check_status(int* d_status, cudaStream_t st) {
 int oeq_tp_check(oeq_tp* h) { return h ? check_status(h->d_status, h->last_stream) : fail(OEQ_ERR_INVALID, "null handle"); }
 
 static int launch_info(const Kernel& k, int* threads, int* ng, int* ps, int* stages, int* smem, int* regs) {
-    if (threads) *threads = k.map.threads();
+    if (threads) *threads = k.is_uvw ? k.uvw.threads : k.map.threads();
     if (ng) *ng = k.map.ng;
     if (ps) *ps = k.map.ps;
     if (stages) *stages = k.stages;

@@ -1,0 +1,98 @@
+"""Receiver-sharded convolution: partition logic and the two exchange steps, on CPU ranks (gloo).
+
+The local kernel is replaced by the CPU oracle so that only the host-side plan and the
+collectives are under test; the GPU kernels are covered by the gpu-marked tests."""
+import os
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import tp_oracle as orc
+from conftest import problem_by_name
+from helpers import conv_inputs, random_graph, rel_err
+from openequivariance_b200.dist import ShardPlan, ShardedTensorProductConv
+
+
+class OracleLocalConv:
+    """Stand-in with the two methods the sharded layer calls on its local convolution."""
+
+    def __init__(self, problem):
+        self.problem = problem
+
+    def _forward_impl(self, x, y, w, rows, cols, perm=None, n_out=None):
+        msg = orc.tp_torch(self.problem, x[cols], y, w)
+        return torch.zeros(n_out, msg.shape[1], dtype=x.dtype).index_add(0, rows, msg)
+
+    def _backward_impl(self, x, y, w, dz, rows, cols, perm=None):
+        with torch.enable_grad():    # called from inside autograd's backward, where grad mode is off
+            x, y, w = (t.detach().clone().requires_grad_(True) for t in (x, y, w))
+            z = self._forward_impl(x, y, w, rows, cols, n_out=dz.shape[0])
+            z.backward(dz)
+        return x.grad, y.grad, w.grad
+
+
+def test_plan_partitions_nodes_and_edges():
+    rows, cols = random_graph(37, 400, seed=1)
+    rows, cols, _, _ = orc.coord_graph(rows, cols)
+    for world in (1, 2, 3, 8):
+        plans = [ShardPlan(rows, cols, 37, r, world) for r in range(world)]
+        assert plans[0].node_lo == 0 and plans[-1].node_hi == 37
+        assert sum(p.owned for p in plans) == 37
+        assert plans[0].edge_lo == 0 and plans[-1].edge_hi == len(rows)
+        for a, b in zip(plans, plans[1:]):
+            assert a.node_hi == b.node_lo and a.edge_hi == b.edge_lo
+        for p in plans:
+            assert np.all((p.local_rows >= 0) & (p.local_rows < max(p.owned, 1)))
+            assert np.all(np.diff(p.local_cols[p.local_perm]) >= 0)      # sender order
+            assert p.padded_nodes >= 37 and p.padded_nodes % world == 0
+    with pytest.raises(ValueError):
+        ShardPlan(rows[::-1], cols, 37, 0, 2)
+    with pytest.raises(ValueError):
+        ShardPlan(rows, cols, 37, 2, 2)
+
+
+def _worker(rank, world, port, nodes, result):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        p = problem_by_name("cw_mixed", irrep_dtype=np.float64, weight_dtype=np.float64)
+        rows, cols = random_graph(nodes, 300, seed=2)
+        rows, cols, order, _ = orc.coord_graph(rows, cols)
+        x, y, w, dz = conv_inputs(p, nodes, len(rows), 3)
+        conv = ShardedTensorProductConv(p, rows, cols, nodes, device="cpu", local_conv=OracleLocalConv(p))
+        plan = conv.plan
+        xs = torch.from_numpy(x[plan.node_lo:plan.node_hi]).requires_grad_(True)
+        ys = torch.from_numpy(y[plan.edge_lo:plan.edge_hi]).requires_grad_(True)
+        ws = torch.from_numpy(w[plan.edge_lo:plan.edge_hi]).requires_grad_(True)
+        dzs = torch.from_numpy(dz[plan.node_lo:plan.node_hi])
+        z = conv(xs, ys, ws)
+        z.backward(dzs)
+        z_ref = orc.conv_forward(p, x, y, w, rows, cols)
+        rx, ry, rw = orc.conv_backward(p, x, y, w, dz, rows, cols)
+        errs = [rel_err(z.detach().numpy(), z_ref[plan.node_lo:plan.node_hi]),
+                rel_err(xs.grad.numpy(), rx[plan.node_lo:plan.node_hi]),
+                rel_err(ys.grad.numpy(), ry[plan.edge_lo:plan.edge_hi]),
+                rel_err(ws.grad.numpy(), rw[plan.edge_lo:plan.edge_hi])]
+        z2, dx2, dy2, dw2 = conv.forward_backward(xs.detach(), ys.detach(), ws.detach(), dzs)
+        errs.append(rel_err(dx2.numpy(), rx[plan.node_lo:plan.node_hi]))
+        result[rank] = max(errs)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("nodes", [40, 41])          # even split and a padded last shard
+def test_two_rank_conv_matches_the_single_process_oracle(nodes):
+    world = 2
+    port = 29600 + nodes
+    ctx = mp.get_context("spawn")
+    result = ctx.Manager().dict()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, nodes, result)) for r in range(world)]
+    for pr in procs:
+        pr.start()
+    for pr in procs:
+        pr.join(timeout=240)
+        assert pr.exitcode == 0
+    assert len(result) == world and max(result.values()) < 1e-12

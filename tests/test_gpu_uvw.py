@@ -1,0 +1,79 @@
+"""Fully connected ('uvw') batch tensor product on the GPU (through the C ABI) vs the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+import openequivariance_b200 as oeq
+from oracle import tp_oracle as orc
+from conftest import problem_by_name
+from helpers import REL_TOL, rel_err, tp_inputs, to_oeq, to_e3nn
+
+pytestmark = pytest.mark.gpu
+
+CASES = [("uvw_small", 100), ("uvw_small", 3), ("uvw_mul40", 37), ("uvw_rowweights", 50), ("uvw_64", 70)]
+
+
+def run_case(name, batch, dtype, seed=11111):
+    p = problem_by_name(name, irrep_dtype=dtype, weight_dtype=dtype)
+    tp = oeq.TensorProduct(p, torch_op=True)
+    x, y, w, dz = tp_inputs(p, batch, seed)
+    if p.shared_weights:
+        w = (w / 8).astype(dtype)
+    w_oeq = to_oeq(p, w)                      # the documented reordering of 'uvw' weights
+    xt, yt, wt, dzt = (torch.from_numpy(a).cuda() for a in (x, y, w_oeq, dz))
+    z = tp(xt, yt, wt)
+    dx, dy, dw = tp.backward_helper(xt, yt, wt, dzt)
+    torch.cuda.synchronize()
+    tp.check_device_status()
+    tol = REL_TOL[dtype]
+    assert rel_err(z.cpu().numpy(), orc.tp_forward(p, x, y, w)) < tol
+    rx, ry, rw = orc.tp_backward(p, x, y, w, dz)
+    assert rel_err(dx.cpu().numpy(), rx) < tol
+    assert rel_err(dy.cpu().numpy(), ry) < tol
+    assert rel_err(to_e3nn(p, dw.cpu().numpy()), rw) < tol
+    return tp, (xt, yt, wt, dzt), dw
+
+
+@pytest.mark.parametrize("name,batch", CASES, ids=[f"{n}-{b}" for n, b in CASES])
+def test_forward_backward_fp32(name, batch):
+    run_case(name, batch, np.float32)
+
+
+@pytest.mark.parametrize("name,batch", [("uvw_small", 41), ("uvw_mul40", 19), ("uvw_rowweights", 23), ("uvw_64", 33)],
+                         ids=["uvw_small", "uvw_mul40", "uvw_rowweights", "uvw_64"])
+def test_forward_backward_fp64(name, batch):
+    run_case(name, batch, np.float64)
+
+
+def test_shared_weight_gradient_is_reproducible_and_host_entry_points_reorder():
+    tp, (xt, yt, wt, dzt), dw = run_case("uvw_64", 1000, np.float32)
+    for _ in range(3):
+        assert torch.equal(dw, tp.backward_helper(xt, yt, wt, dzt)[2])
+    # host entry points take e3nn-ordered weights and return the e3nn-ordered gradient
+    p = tp.config
+    x, y, w, dz = tp_inputs(p, 64, 5)
+    w = (w / 8).astype(np.float32)
+    z = np.zeros((64, p.irreps_out.dim), dtype=np.float32)
+    tp.forward_cpu(x, y, z, w)
+    assert rel_err(z, orc.tp_forward(p, x, y, w)) < 1e-5
+    gx, gy, gw = np.zeros_like(x), np.zeros_like(y), np.zeros_like(w)
+    tp.backward_cpu(x, gx, y, gy, dz, w, gw)
+    assert rel_err(gw, orc.tp_backward(p, x, y, w, dz)[2]) < 1e-5
+
+
+def test_full_batch_linearity_and_sampled_rows():
+    """Benchmark batch size: linear in X, and sampled rows against the oracle."""
+    p = problem_by_name("uvw_64")
+    tp = oeq.TensorProduct(p, torch_op=True)
+    batch = 100000
+    gen = torch.Generator(device="cuda").manual_seed(2)
+    x1 = torch.randn(batch, p.irreps_in1.dim, device="cuda", generator=gen)
+    x2 = torch.randn(batch, p.irreps_in1.dim, device="cuda", generator=gen)
+    y = torch.randn(batch, p.irreps_in2.dim, device="cuda", generator=gen)
+    w = torch.randn(p.weight_numel, device="cuda", generator=gen) / 8
+    z1, z2, z12 = tp(x1, y, w), tp(x2, y, w), tp(x1 - 3 * x2, y, w)
+    assert ((z12 - (z1 - 3 * z2)).abs().max() / z12.abs().max()).item() < 1e-5
+    idx = torch.arange(0, batch, 1999, device="cuda")
+    w_e3nn = to_e3nn(p, w.cpu().numpy())
+    ref = orc.tp_forward(p, x1[idx].cpu().numpy(), y[idx].cpu().numpy(), w_e3nn)
+    assert rel_err(z1[idx].cpu().numpy(), ref) < 1e-5
