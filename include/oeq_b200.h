@@ -104,6 +104,21 @@ size_t oeq_tp_workspace_bytes(const oeq_tp* h, int64_t batch);
 int oeq_tp_backward(oeq_tp* h, int64_t batch, const void* X, const void* Y, const void* W, const void* dZ,
                     void* dX, void* dY, void* dW, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Same result as oeq_tp_backward for a shared-weight problem, for callers that may not allocate device
+ * memory and so cannot hand over scratch: code running where the surrounding framework owns all
+ * allocation (a memory pool that must not be bypassed, a real-time loop after its set-up phase).
+ * It has no counterpart in the reference.  The partial weight gradients go to a fixed 8 MiB array
+ * inside the library image (held by every GPU that loads the library); the launch is narrowed until
+ * its partials fit, and a weight tensor larger than the array is refused with OEQ_ERR_UNSUPPORTED.
+ * The call itself makes no cudaMalloc / cudaFree; the first call on a device (and the first call on
+ * a handle) does one-time set-up -- the array's address is looked up, the kernels are loaded -- so
+ * make that call before any stream capture.  All calls share the array, which keeps whatever the last
+ * call left; every call rewrites the part it reads, but two calls that overlap on the GPU race.  A
+ * bounded wait that runs out is recorded only if the handle already owns a status word (any earlier
+ * oeq_tp_forward / oeq_tp_backward creates it). */
+int oeq_tp_backward_noalloc(oeq_tp* h, int64_t batch, const void* X, const void* Y, const void* W, const void* dZ,
+                            void* dX, void* dY, void* dW, void* stream);
+
 /* Reads the handle's device status word (synchronises the stream it last ran on):
  * OEQ_OK, or OEQ_ERR_DEVICE_WAIT if a kernel abandoned a bounded wait. */
 int oeq_tp_check(oeq_tp* h);

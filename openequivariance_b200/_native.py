@@ -62,6 +62,7 @@ SYMBOLS = {
     "oeq_tp_forward": (_INT, [_P, _I64, _P, _P, _P, _P, _P]),
     "oeq_tp_workspace_bytes": (_SZ, [_P, _I64]),
     "oeq_tp_backward": (_INT, [_P, _I64, _P, _P, _P, _P, _P, _P, _P, _P, _SZ, _P]),
+    "oeq_tp_backward_noalloc": (_INT, [_P, _I64, _P, _P, _P, _P, _P, _P, _P, _P]),
     "oeq_tp_check": (_INT, [_P]),
     "oeq_conv_create": (_INT, [C.POINTER(_ProblemDesc), _INT, C.POINTER(_P)]),
     "oeq_conv_destroy": (_INT, [_P]),

@@ -888,6 +888,86 @@ int oeq_tp_launch_info(const oeq_tp* h, int which, int* threads, int* ng, int* p
     return launch_info(which ? h->bwd : h->fwd, threads, ng, ps, stages, smem, regs);
 }
 
+// ---------------------------------------------------------------- backward pass that allocates nothing
+
+// Scratch for oeq_tp_backward_noalloc: lives in the library image, so every GPU that loads the
+// library holds these bytes until the process exits.
+constexpr size_t NOALLOC_SCRATCH_BYTES = 8u << 20;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
+// In host code the array's name only stands for the symbol; the device address is looked up
+// once per device (with that device current) and remembered here.
+static void* g_noalloc_scratch_addr[64] = {nullptr};
+
+static int noalloc_scratch(void** out) {
+    int dev = 0;
+    OEQ_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(OEQ_ERR_INVALID, "device ordinal out of range");
+    if (!g_noalloc_scratch_addr[dev]) {
+        void* ptr = nullptr;
+        OEQ_CUDA(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+        g_noalloc_scratch_addr[dev] = ptr;
+    }
+    *out = g_noalloc_scratch_addr[dev];
+    return OEQ_OK;
+}
+
+int oeq_tp_backward_noalloc(oeq_tp* h, int64_t batch, const void* X, const void* Y, const void* W, const void* dZ,
+                            void* dX, void* dY, void* dW, void* stream) {
+    if (!h) return fail(OEQ_ERR_INVALID, "null handle");
+    const Problem& p = h->prob;
+    if (!p.shared)
+        return fail(OEQ_ERR_INVALID, "per-row weights need no scratch: call oeq_tp_backward with a null workspace");
+    if (batch <= 0) return fail(OEQ_ERR_INVALID, "batch must be positive");
+    if (!X || !Y || !W || !dZ || !dX || !dY || !dW) return fail(OEQ_ERR_INVALID, "null buffer");
+    const size_t slice = (size_t)p.w_numel * p.elem();
+    if (slice == 0 || slice > NOALLOC_SCRATCH_BYTES)
+        return fail(OEQ_ERR_UNSUPPORTED, "weight tensor of " + std::to_string(slice) + " bytes exceeds the built-in scratch of " +
+                                             std::to_string(NOALLOC_SCRATCH_BYTES) + " bytes; use oeq_tp_backward with caller scratch");
+    const long long max_slices = (long long)(NOALLOC_SCRATCH_BYTES / slice);
+    cudaStream_t st = (cudaStream_t)stream;
+    void* scratch = nullptr;
+    int rc = noalloc_scratch(&scratch);
+    if (rc) return rc;
+    if (p.mode == OEQ_MODE_UVW) {
+        if ((rc = load_uvw(h->bwd, p, true))) return rc;
+        long long ctas = std::min(uvw_grid(h->bwd, batch), max_slices);
+        UvwParams up{};
+        up.X = X; up.Y = Y; up.W = W; up.dZ = dZ; up.dX = dX; up.dY = dY; up.dW = dW; up.ws = scratch;
+        up.batch = batch; up.status = h->d_status;
+        void* args[] = {&up};
+        OEQ_CUDA(cudaLaunchKernel((const void*)h->bwd.fn, dim3((unsigned)ctas), dim3((unsigned)h->bwd.uvw.threads), args,
+                                  (size_t)h->bwd.smem, st));
+        int n = p.w_numel;
+        const void* ws = scratch;
+        void* rargs[] = {&ws, &dW, &n, &ctas};
+        OEQ_CUDA(cudaLaunchKernel((const void*)h->bwd.reduce_fn, dim3((n + 127) / 128), dim3(128), rargs, 0, st));
+        return OEQ_OK;
+    }
+    if ((rc = load_kernel(h->bwd, "oeq_uvu_kernel", true))) return rc;
+    Kernel& k = h->bwd;
+    const long long grid = std::min(uvu_grid(k, batch), max_slices / k.map.ng);
+    if (grid < 1)
+        return fail(OEQ_ERR_UNSUPPORTED, "one CTA's partial gradients exceed the built-in scratch; use oeq_tp_backward");
+    UvuParams prm{};
+    prm.X = X; prm.Y = Y; prm.W = W; prm.dZ = dZ; prm.dX = dX; prm.dY = dY; prm.dW = dW;
+    prm.n_items = batch; prm.n_nodes = batch; prm.status = h->d_status; prm.ws = scratch;
+    const int e = p.elem();
+    int flags = 0;
+    if ((p.x_dim * e) % 16 == 0 && aligned16(X)) flags |= 1;
+    if ((p.y_dim * e) % 16 == 0 && aligned16(Y)) flags |= 2;
+    if ((p.z_dim * e) % 16 == 0 && aligned16(dZ)) flags |= 8;
+    prm.flags = flags;
+    prm.stages = k.stages;
+    void* args[] = {&prm};
+    OEQ_CUDA(cudaLaunchKernel((const void*)k.fn, dim3((unsigned)grid), dim3((unsigned)k.map.threads()), args, (size_t)k.smem, st));
+    long long groups = grid * k.map.ng;
+    int n = p.w_numel;
+    const void* ws = scratch;
+    void* rargs[] = {&ws, &dW, &n, &groups};
+    OEQ_CUDA(cudaLaunchKernel((const void*)k.reduce_fn, dim3((n + 127) / 128), dim3(128), rargs, 0, st));
+    return OEQ_OK;
+}
+
 // ---------------------------------------------------------------- fused convolution
 
 int oeq_conv_create(const oeq_problem_desc* desc, int deterministic, oeq_conv** out) {
