@@ -208,8 +208,8 @@ struct Mapping {
     std::vector<int> part_of_out, part_of_instr, zr_off, xr_off;
     int zpc_max = 1, xpc = 1;
     int stage_bytes = 0, extra_bytes = 0, sw_bytes = 0;
-    int threads() const { return ng * mulg * ps + 32; }
-    int fixed_bytes(int stages) const { return ng * stages * 48 + pad16((2 * ng + 2) * 8) + sw_bytes; }
+    int threads() const { return ng * mulg * ps; }
+    int fixed_bytes(int stages) const { return pad16(ng * stages * 8) + ng * stages * 32 + ng * 16 + sw_bytes; }
     int smem(int stages) const { return fixed_bytes(stages) + ng * (stages * stage_bytes + extra_bytes); }
     int max_stages() const {
         int s = 0;
@@ -285,37 +285,38 @@ int choose_mapping(const Problem& p, int kind, Mapping& m) {
         if (!bwd) return batch ? 2 * zb : 0;
         return ps * xb + 2 * warps * yb + (p.shared ? pad16(p.w_numel * e) : 0);
     };
-    int best_ps = 0, best_ng = 0;
-    long long best_score = -1;
-    for (int ps : {1, 2, 4}) {
-        if (ps > 1 && ps > units) break;
-        const int g = m.mulg * ps;
-        if (g > 512) break;
-        if (!bwd && !batch && zpc * m.nch / ps > 64 && ps < 4 && ps * 2 <= units) continue;  // register pressure
+    // Measured on B200: these kernels are bound by instruction issue, so the mapping that wins is the
+    // one with the least per-thread overhead -- as few path partitions as the register file allows, and
+    // moderate CTAs (several per SM) rather than one wide one.
+    int xpc = 0;
+    for (const Irrep& r : p.in1) xpc += r.dim;
+    int best_ps = 1;
+    if (!bwd) {
+        auto regs = [&](int ps) { return zpc * m.nch / ps + xpc * m.nch + std::min(p.y_dim, 32) + 56; };
+        while (regs(best_ps) > 232 && best_ps < 4 && best_ps * 2 <= units) best_ps *= 2;
+    } else {
+        const int g_target = m.stage_bytes > 32768 ? 256 : 64;
+        while (m.mulg * best_ps * 2 <= g_target && best_ps < 4 && best_ps * 2 <= units) best_ps *= 2;
+    }
+    int best_ng = 0;
+    {
         Mapping t = m;
-        t.ps = ps;
-        t.extra_bytes = extra(ps);
-        int ng = 0;
-        for (int cand = 1; cand <= 8; ++cand) {
+        t.ps = best_ps;
+        t.extra_bytes = extra(best_ps);
+        const int g = m.mulg * best_ps;
+        const int want = std::max(1, std::min(8, (bwd ? 512 : (g >= 128 ? 128 : 256)) / g));
+        for (int cand = want; cand >= 1; --cand) {
             t.ng = cand;
-            if (cand * g > 512) break;
-            if (t.smem(2) > SMEM_LIMIT) break;
-            ng = cand;
-        }
-        if (ng == 0) continue;
-        const long long threads = (long long)ng * g;
-        // enough threads to hide latency first, then as few partitions as possible
-        const long long score = std::min<long long>(threads, 512) * 8 - ps;
-        if (score > best_score) {
-            best_score = score;
-            best_ps = ps;
-            best_ng = ng;
+            if (t.smem(bwd ? 2 : 3) <= SMEM_LIMIT || (cand == 1 && t.smem(2) <= SMEM_LIMIT)) {
+                best_ng = cand;
+                break;
+            }
         }
     }
-    if (best_ps == 0)
+    if (best_ng == 0)
         return fail(OEQ_ERR_UNSUPPORTED, "problem rows do not fit in shared memory (two stages of one item exceed 227 KB)");
-    m.ps = env_int("OEQ_B200_PS", best_ps);
-    m.ng = env_int("OEQ_B200_NG", best_ng);
+    m.ps = env_int(bwd ? "OEQ_B200_PS_BWD" : "OEQ_B200_PS_FWD", env_int("OEQ_B200_PS", best_ps));
+    m.ng = env_int(bwd ? "OEQ_B200_NG_BWD" : "OEQ_B200_NG_FWD", env_int("OEQ_B200_NG", best_ng));
     m.extra_bytes = extra(m.ps);
     if (m.smem(2) > SMEM_LIMIT || m.ng * m.mulg * m.ps > 992 || m.ng < 1 || m.ng > 8)
         return fail(OEQ_ERR_INVALID, "OEQ_B200_PS / OEQ_B200_NG override does not fit");
@@ -628,7 +629,7 @@ struct UvuParams {
     long long n_items, n_nodes;
     void* ws;
     int* status;
-    int stages, flags;
+    int stages, flags, chunk;
 };
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -644,6 +645,7 @@ int launch_uvu(Kernel& k, const Problem& p, UvuParams& prm, cudaStream_t stream)
     if (env_int("OEQ_B200_NO_BULK", 0)) flags = 0;
     prm.flags = flags;
     prm.stages = k.stages;
+    prm.chunk = std::max(1, env_int("OEQ_B200_CHUNK", 64));
     long long want = (prm.n_items + k.map.ng - 1) / k.map.ng;
     long long grid = std::max<long long>(1, std::min<long long>((long long)k.sm_count * k.ctas_per_sm, want));
     void* args[] = {&prm};
@@ -958,6 +960,7 @@ int oeq_tp_backward_noalloc(oeq_tp* h, int64_t batch, const void* X, const void*
     if ((p.z_dim * e) % 16 == 0 && aligned16(dZ)) flags |= 8;
     prm.flags = flags;
     prm.stages = k.stages;
+    prm.chunk = 64;
     void* args[] = {&prm};
     OEQ_CUDA(cudaLaunchKernel((const void*)k.fn, dim3((unsigned)grid), dim3((unsigned)k.map.threads()), args, (size_t)k.smem, st));
     long long groups = grid * k.map.ng;

@@ -12,19 +12,26 @@
 //   * An "item" is one batch row or one graph edge.  A "group" of
 //     G = MULG * PS threads works on one item at a time: thread (part, u)
 //     owns channel u of the instructions assigned to partition `part`.
-//   * A CTA holds NG groups plus one producer warp.  The producer warp stages
-//     every item's rows (X gathered by sender index, Y, per-item W, and dZ
-//     gathered by receiver index in the backward pass) into a ring of shared
-//     memory stages with 1-D bulk async copies (TMA) that complete on an
-//     mbarrier; rows that break the 16-byte rule fall back to cp.async.
+//   * A CTA holds NG independent groups.  Each group runs its own ring of
+//     shared-memory stages: its first warp stages the rows of the items ahead
+//     (X gathered by sender index, Y, per-item W, and dZ gathered by receiver
+//     index in the backward pass) with 1-D bulk async copies (TMA) that
+//     complete on an mbarrier; rows that break the 16-byte rule fall back to
+//     cp.async.  Edge indices are fetched 32 at a time, one block ahead.
+//   * Work is dealt to groups in small chunks of consecutive edges, round
+//     robin over all groups of the grid, so that at any moment the whole GPU
+//     works on one neighbourhood of the (sorted) edge list and gathered rows
+//     are re-used from L2.
 //   * Clebsch-Gordan coefficients times path weights are compile-time
 //     constants; the contraction is fully unrolled straight-line FMA code.
-//   * Deterministic convolution: every group owns a contiguous, node-aligned
-//     slice of the sorted edge list, accumulates a node's sum in registers
-//     and writes each output row exactly once (rows without edges are written
-//     as zeros), so no scratch buffer or fix-up pass exists.
-//   * All waits are bounded; a wait that runs out sets *status and the CTA
-//     drains its copies and returns.
+//   * Deterministic convolution: chunk boundaries are moved forward to the next
+//     segment boundary (receiver runs in the forward pass, sender runs in
+//     sender_perm order in the backward pass), a group accumulates a node's
+//     sum in registers and writes each output row exactly once (rows without
+//     edges are written as zeros), so no scratch buffer or fix-up pass exists
+//     and the summation order is fixed.
+//   * All waits are bounded; a wait that runs out sets *status and the group
+//     stops consuming.
 #pragma once
 #include "oeq_common.cuh"
 
@@ -48,7 +55,8 @@ struct UvuParams {
     T* ws;                  // scratch: per-group partial sums of shared-weight gradients
     int* status;
     int stages;             // shared-memory stages per group
-    int flags;              // bit0 X bulk-able, bit1 Y, bit2 W, bit3 Z/dZ, bit4 dX rows bulk-able
+    int flags;              // bit0 X bulk-able, bit1 Y, bit2 W, bit3 Z/dZ
+    int chunk;              // edges per work chunk (convolution modes)
 };
 
 constexpr int MODE_BATCH = 0;
@@ -56,8 +64,7 @@ constexpr int MODE_DET = 1;
 constexpr int MODE_ATOMIC = 2;
 
 constexpr int G = MULG * PS;
-constexpr int NCONSUMERS = NG * G;
-constexpr int NTHREADS = NCONSUMERS + 32;
+constexpr int NTHREADS = NG * G;
 constexpr int WARPS_PER_GROUP = G / 32;
 
 // ---------------------------------------------------------------- helpers on the descriptor
@@ -87,6 +94,16 @@ constexpr bool bwd_part_uses_in1(int q, int a) {
         if (BWD_PART_OF_INSTR[p] == q && I_IN1[p] == a) return true;
     return false;
 }
+constexpr bool fwd_part_uses_in2(int q, int b) {
+    for (int p = 0; p < N_INSTR; ++p)
+        if (FWD_PART_OF_OUT[I_OUT[p]] == q && I_IN2[p] == b) return true;
+    return false;
+}
+constexpr bool bwd_part_uses_in2(int q, int b) {
+    for (int p = 0; p < N_INSTR; ++p)
+        if (BWD_PART_OF_INSTR[p] == q && I_IN2[p] == b) return true;
+    return false;
+}
 constexpr bool any_part_uses_in1(int a) {
     for (int p = 0; p < N_INSTR; ++p)
         if (I_IN1[p] == a) return true;
@@ -97,7 +114,24 @@ constexpr bool all_in2_mul_one() {
         if (IN2_MUL[I_IN2[p]] != 1) return false;
     return true;
 }
+constexpr int next_pow2(int n) {
+    int p = 1;
+    while (p < n) p *= 2;
+    return p;
+}
 constexpr int CHANNELS = MULG * NCH;
+// second-input rows are kept in registers when every multiplicity is 1 and the row is short
+constexpr bool Y_IN_REGS = all_in2_mul_one() && Y_DIM <= 32;
+
+// Same (i, j) pair as the previous / next Clebsch-Gordan entry of the same instruction?
+template <int P, int N>
+constexpr bool cg_pair_first() {
+    return N == CG_BEGIN[P] || CG_I[N] != CG_I[N - 1] || CG_J[N] != CG_J[N - 1];
+}
+template <int P, int N>
+constexpr bool cg_pair_last() {
+    return N == CG_BEGIN[P + 1] - 1 || CG_I[N] != CG_I[N + 1] || CG_J[N] != CG_J[N + 1];
+}
 
 // Offset of weight (u, v) of instruction P in the kernel weight layout: the
 // multiplicity axes are cut into 32-wide chunks, chunks are ordered u-chunk
@@ -115,29 +149,67 @@ __device__ __forceinline__ int weight_offset(int u, int v) {
     }
 }
 
-// t[k] += sum_n c_n * x[i_n] * y[j_n] over the nonzeros of instruction P.
+// t[k] += sum_n c_n * (x[i_n] * y[j_n]); the product of a pair is formed once.
 template <int P, class XA, class YA, class TA>
 __device__ __forceinline__ void cg_forward(const XA& x, const YA& y, TA& t) {
+    T xy = (T)0;
     sfor<CG_BEGIN[P], CG_BEGIN[P + 1]>([&](auto n) {
         constexpr int N = n;
-        t[CG_K[N]] = fma(x[CG_I[N]] * y[CG_J[N]], (T)CG_V[N], t[CG_K[N]]);
+        if constexpr (cg_pair_first<P, N>()) xy = x[CG_I[N]] * y[CG_J[N]];
+        t[CG_K[N]] = fma(xy, (T)CG_V[N], t[CG_K[N]]);
     });
 }
 
-// Backward of the above for one (u, v): with g = dZ block of the channel,
-//   dxl[i] += c g[k] y[j];  dyl[j] += c g[k] x[i];  returns sum c g[k] x[i] y[j].
-template <int P, class XA, class YA, class GA, class DXA, class DYA>
-__device__ __forceinline__ T cg_backward(const XA& x, const YA& y, const GA& g, DXA& dxl, DYA& dyl) {
-    T tw = (T)0;
+// Backward of the above for one (u, v) with g = dZ block of the channel:
+//   P_ij = sum_k c_ijk g_k;  a_i += y_j P_ij;  b_j += x_i P_ij
+// so that dX_i = w a_i, dY_j = w b_j and dW = sum_i x_i a_i.
+template <int P, class XA, class YA, class GA, class AA, class BA>
+__device__ __forceinline__ void cg_backward(const XA& x, const YA& y, const GA& g, AA& a, BA& b) {
+    T pij = (T)0;
     sfor<CG_BEGIN[P], CG_BEGIN[P + 1]>([&](auto n) {
         constexpr int N = n;
-        const T q = (T)CG_V[N] * g[CG_K[N]];
-        const T qx = q * x[CG_I[N]];
-        dxl[CG_I[N]] = fma(q, y[CG_J[N]], dxl[CG_I[N]]);
-        dyl[CG_J[N]] += qx;
-        tw = fma(qx, y[CG_J[N]], tw);
+        if constexpr (cg_pair_first<P, N>()) pij = (T)CG_V[N] * g[CG_K[N]];
+        else pij = fma((T)CG_V[N], g[CG_K[N]], pij);
+        if constexpr (cg_pair_last<P, N>()) {
+            a[CG_I[N]] = fma(y[CG_J[N]], pij, a[CG_I[N]]);
+            b[CG_J[N]] = fma(x[CG_I[N]], pij, b[CG_J[N]]);
+        }
     });
-    return tw;
+}
+
+// Sum each of v[0..N) over the 32 lanes in a fixed order with N + log-many shuffles
+// (recursive halving); afterwards lane L holds the total of index L >> (5 - log2(NP)) in v[0].
+template <int N, class VA>
+__device__ __forceinline__ void warp_reduce_vector(VA& v, int lane) {
+    constexpr int NP = next_pow2(N);
+    T w[NP];
+#pragma unroll
+    for (int i = 0; i < NP; ++i) w[i] = i < N ? v[i] : (T)0;
+    int count = NP;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        if (count > 1) {
+            const int half = count / 2;
+            const bool upper = (lane & off) != 0;
+#pragma unroll
+            for (int m = 0; m < NP / 2; ++m) {
+                if (m < half) {
+                    const T send = upper ? w[m] : w[m + half];
+                    const T keep = upper ? w[m + half] : w[m];
+                    w[m] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+                }
+            }
+            count = half;
+        } else {
+            w[0] += __shfl_xor_sync(0xffffffffu, w[0], off);
+        }
+    }
+    v[0] = w[0];
+}
+constexpr int log2_int(int n) {
+    int l = 0;
+    while ((1 << l) < n) ++l;
+    return l;
 }
 
 // ---------------------------------------------------------------- shared memory map
@@ -156,16 +228,15 @@ struct Smem {
     int stages;
     __device__ Smem(unsigned char* b, int s) : base(b), stages(s) {}
     __device__ unsigned long long* full(int g, int s) const {
-        return reinterpret_cast<unsigned long long*>(base) + (g * stages + s) * 2;
+        return reinterpret_cast<unsigned long long*>(base) + (g * stages + s);
     }
-    __device__ unsigned long long* empty(int g, int s) const { return full(g, s) + 1; }
     __device__ long long* hdr(int g, int s) const {
-        return reinterpret_cast<long long*>(base + NG * stages * 16) + (g * stages + s) * 4;
+        return reinterpret_cast<long long*>(base + pad16(NG * stages * 8)) + (g * stages + s) * 4;
     }
-    __device__ long long* bounds() const {  // [0..NG] edge bounds, [NG+1 .. 2NG+1] node bounds
-        return reinterpret_cast<long long*>(base + NG * stages * 48);
+    __device__ long long* total(int g) const {   // number of items of the group, -1 until known
+        return reinterpret_cast<long long*>(base + pad16(NG * stages * 8) + NG * stages * 32) + g * 2;
     }
-    __device__ unsigned char* shared_w() const { return base + NG * stages * 48 + pad16((2 * NG + 2) * 8); }
+    __device__ unsigned char* shared_w() const { return base + pad16(NG * stages * 8) + NG * stages * 32 + NG * 16; }
     __device__ unsigned char* group_base(int g) const {
         return shared_w() + SWB + (long long)g * (stages * L::BYTES + EXTRA);
     }
@@ -173,7 +244,7 @@ struct Smem {
     __device__ unsigned char* extra(int g) const { return group_base(g) + stages * L::BYTES; }
 };
 
-// ---------------------------------------------------------------- producer warp
+// ---------------------------------------------------------------- work assignment and staging
 
 template <int MODE, bool BWD>
 __device__ __forceinline__ long long item_key(const UvuParams& p, long long k) {
@@ -201,107 +272,147 @@ __device__ long long align_forward(const UvuParams& p, long long t, int lane) {
     return n;
 }
 
+// The sequence of items of one group, walked by the group's first warp (all 32 lanes in step).
+// Batch mode: rows gid, gid + groups, ...  Convolution modes: chunks gid, gid + groups, ... of
+// `chunk` consecutive edges each (deterministic: chunk ends moved to segment boundaries).
 template <int MODE, bool BWD>
-__device__ void producer(const UvuParams& p, const Smem<BWD, MODE>& sm, int lane) {
-    using L = StageLayout<BWD>;
-    const int S = sm.stages;
-    const long long total_groups = (long long)gridDim.x * NG;
-    const long long gid0 = (long long)blockIdx.x * NG;
-    const bool xb = p.flags & 1, yb = p.flags & 2, wb = p.flags & 4, zb = p.flags & 8;
-    const long long* bnd = sm.bounds();
+struct ItemWalker {
+    const UvuParams& p;
+    long long groups, gid;
+    int lane;
+    // batch
+    long long next_row;
+    // convolution: current chunk [pos, end), chunk index, node range of the chunk
+    long long chunk_index, pos, end, node_lo, node_hi, n_chunks;
+    bool first_in_chunk;
+    // indices of up to 32 items starting at block_base, one per lane
+    long long block_base, ie, is_, ir;
 
-    long long first[NG], count[NG];
-#pragma unroll
-    for (int g = 0; g < NG; ++g) {
+    __device__ ItemWalker(const UvuParams& p_, long long groups_, long long gid_, int lane_)
+        : p(p_), groups(groups_), gid(gid_), lane(lane_) {
+        next_row = gid;
+        n_chunks = (p.n_items + p.chunk - 1) / p.chunk;
+        chunk_index = gid - groups;
+        pos = end = 0;
+        node_lo = node_hi = 0;
+        first_in_chunk = false;
+        block_base = -1;
+        ie = is_ = ir = 0;
+    }
+
+    __device__ long long chunk_start(long long c) const {
+        const long long t = c * p.chunk;
+        if constexpr (MODE == MODE_DET) return align_forward<MODE, BWD>(p, t, lane);
+        return t < p.n_items ? t : p.n_items;
+    }
+    __device__ long long node_bound(long long c, long long e) const {
+        if (c <= 0) return 0;
+        if (e >= p.n_items) return p.n_nodes;
+        return item_key<MODE, BWD>(p, e);
+    }
+
+    // Advance to the next non-empty chunk; false when the group's work is exhausted.
+    __device__ bool next_chunk() {
+        for (;;) {
+            chunk_index += groups;
+            if (chunk_index >= n_chunks) return false;
+            pos = chunk_start(chunk_index);
+            end = chunk_index + 1 >= n_chunks ? p.n_items : chunk_start(chunk_index + 1);
+            if constexpr (MODE == MODE_DET) {
+                node_lo = node_bound(chunk_index, pos);
+                node_hi = chunk_index + 1 >= n_chunks ? p.n_nodes : node_bound(chunk_index + 1, end);
+            }
+            if (end > pos) {
+                first_in_chunk = true;
+                block_base = -1;
+                return true;
+            }
+        }
+    }
+
+    // Next item: edge/row index e, sender s, receiver r, and the chunk's node range when the
+    // item opens (lo >= 0) or closes (hi >= 0) a chunk.  Returns false at the end.
+    __device__ bool next(long long& e, long long& s, long long& r, long long& lo, long long& hi) {
+        lo = hi = -1;
         if constexpr (MODE == MODE_BATCH) {
-            first[g] = gid0 + g;
-            count[g] = first[g] < p.n_items ? (p.n_items - first[g] + total_groups - 1) / total_groups : 0;
+            if (next_row >= p.n_items) return false;
+            e = s = r = next_row;
+            next_row += groups;
+            return true;
         } else {
-            first[g] = bnd[g];
-            count[g] = bnd[g + 1] - bnd[g];
+            if (pos >= end) {
+                if (!next_chunk()) return false;
+            }
+            if (block_base < 0 || pos >= block_base + 32) {
+                block_base = pos;
+                const long long k = pos + lane;
+                long long le = 0, ls = 0, lr = 0;
+                if (k < end) {
+                    le = (BWD && MODE == MODE_DET) ? p.perm[k] : k;
+                    ls = p.cols[le];
+                    lr = p.rows[le];
+                }
+                ie = le; is_ = ls; ir = lr;
+            }
+            const int src = (int)(pos - block_base);
+            e = __shfl_sync(0xffffffffu, ie, src);
+            s = __shfl_sync(0xffffffffu, is_, src);
+            r = __shfl_sync(0xffffffffu, ir, src);
+            if (first_in_chunk) {
+                lo = node_lo;
+                first_in_chunk = false;
+            }
+            ++pos;
+            if (pos >= end) hi = node_hi;
+            return true;
         }
     }
-    long long max_count = 0;
-#pragma unroll
-    for (int g = 0; g < NG; ++g) max_count = count[g] > max_count ? count[g] : max_count;
+};
 
-    // per-lane prefetched indices of a block of 32 items, per group
-    long long ie[NG], is_[NG], ir[NG];
-    bool ok = true;
-    for (long long it = 0; it < max_count && ok; ++it) {
-#pragma unroll
-        for (int g = 0; g < NG; ++g) {
-            if (it >= count[g] || !ok) continue;
-            const int stage = (int)(it % S);
-            const long long use = it / S;
-            if constexpr (MODE != MODE_BATCH) {
-                if ((it & 31) == 0) {
-                    const long long k = first[g] + it + lane;
-                    long long e = 0, s = 0, r = 0;
-                    if (k < first[g] + count[g]) {
-                        e = (BWD && MODE == MODE_DET) ? p.perm[k] : k;
-                        s = p.cols[e];
-                        r = p.rows[e];
-                    }
-                    ie[g] = e; is_[g] = s; ir[g] = r;
-                }
-            }
-            long long e, s, r;
-            if constexpr (MODE == MODE_BATCH) {
-                e = s = r = first[g] + it * total_groups;
-            } else {
-                const int src = (int)(it & 31);
-                e = __shfl_sync(0xffffffffu, ie[g], src);
-                s = __shfl_sync(0xffffffffu, is_[g], src);
-                r = __shfl_sync(0xffffffffu, ir[g], src);
-            }
-            if (use > 0) {
-                if (!mbar_wait(sm.empty(g, stage), (unsigned)((use - 1) & 1), p.status, ERR_WAIT_EMPTY)) {
-                    ok = false;
-                    continue;
-                }
-            }
-            unsigned char* st = sm.stage(g, stage);
-            unsigned long long* full = sm.full(g, stage);
-            const T* xsrc = p.X + s * X_DIM;
-            const T* ysrc = p.Y + e * Y_DIM;
-            const T* wsrc = SHARED_W ? nullptr : p.W + e * (long long)W_NUMEL;
-            const T* zsrc = BWD ? p.dZ + r * (long long)Z_DIM : nullptr;
-            if (lane == 0) {
-                long long* h = sm.hdr(g, stage);
-                h[0] = e; h[1] = s; h[2] = r;
-                unsigned bytes = 0;
-                if (xb) bytes += XB;
-                if (yb) bytes += YB;
-                if (wb && !SHARED_W) bytes += WB;
-                if (BWD && zb) bytes += ZB;
-                mbar_arrive_expect_tx(full, bytes);
-                if (xb) bulk_g2s(st + L::OFF_X, xsrc, XB, full);
-                if (yb) bulk_g2s(st + L::OFF_Y, ysrc, YB, full);
-                if (wb && !SHARED_W) bulk_g2s(st + L::OFF_W, wsrc, WB, full);
-                if (BWD && zb) bulk_g2s(st + L::OFF_DZ, zsrc, ZB, full);
-            }
-            const bool any_elem = !xb || !yb || (!wb && !SHARED_W) || (BWD && !zb);
-            if (any_elem) {
-                if (!xb) for (int i = lane; i < X_DIM; i += 32) cp_async_elem<ELEM>((T*)(st + L::OFF_X) + i, xsrc + i);
-                if (!yb) for (int i = lane; i < Y_DIM; i += 32) cp_async_elem<ELEM>((T*)(st + L::OFF_Y) + i, ysrc + i);
-                if constexpr (!SHARED_W) {
-                    if (!wb) for (int i = lane; i < W_NUMEL; i += 32) cp_async_elem<ELEM>((T*)(st + L::OFF_W) + i, wsrc + i);
-                }
-                if constexpr (BWD) {
-                    if (!zb) for (int i = lane; i < Z_DIM; i += 32) cp_async_elem<ELEM>((T*)(st + L::OFF_DZ) + i, zsrc + i);
-                }
-                cp_async_arrive_noinc(full);
-            }
-        }
+// Stage one item into ring slot `stage` (executed by the group's first warp).
+template <int MODE, bool BWD>
+__device__ __forceinline__ void issue_item(const UvuParams& p, const Smem<BWD, MODE>& sm, int g, int stage, int lane,
+                                           long long e, long long s, long long r, long long lo, long long hi) {
+    using L = StageLayout<BWD>;
+    const bool xb = p.flags & 1, yb = p.flags & 2, wb = p.flags & 4, zb = p.flags & 8;
+    unsigned char* st = sm.stage(g, stage);
+    unsigned long long* full = sm.full(g, stage);
+    const T* xsrc = p.X + s * X_DIM;
+    const T* ysrc = p.Y + e * Y_DIM;
+    const T* wsrc = SHARED_W ? nullptr : p.W + e * (long long)W_NUMEL;
+    const T* zsrc = BWD ? p.dZ + r * (long long)Z_DIM : nullptr;
+    if (lane == 0) {
+        long long* h = sm.hdr(g, stage);
+        h[0] = e;
+        h[1] = BWD ? s : r;
+        h[2] = lo;
+        h[3] = hi;
+        unsigned bytes = 0;
+        if (xb) bytes += XB;
+        if (yb) bytes += YB;
+        if (wb && !SHARED_W) bytes += WB;
+        if (BWD && zb) bytes += ZB;
+        mbar_arrive_expect_tx(full, bytes);
+        if (BWD && zb) bulk_g2s(st + L::OFF_DZ, zsrc, ZB, full);
+        if (wb && !SHARED_W) bulk_g2s(st + L::OFF_W, wsrc, WB, full);
+        if (xb) bulk_g2s(st + L::OFF_X, xsrc, XB, full);
+        if (yb) bulk_g2s(st + L::OFF_Y, ysrc, YB, full);
     }
-    if (!ok) {
-        // a consumer stopped releasing stages: let the copies already issued land, then leave
-        asm volatile("cp.async.wait_all;" ::: "memory");
+    const bool any_elem = !xb || !yb || (!wb && !SHARED_W) || (BWD && !zb);
+    if (any_elem) {
+        if (!xb) for (int i = lane; i < X_DIM; i += 32) cp_async_elem<ELEM>((T*)(st + L::OFF_X) + i, xsrc + i);
+        if (!yb) for (int i = lane; i < Y_DIM; i += 32) cp_async_elem<ELEM>((T*)(st + L::OFF_Y) + i, ysrc + i);
+        if constexpr (!SHARED_W) {
+            if (!wb) for (int i = lane; i < W_NUMEL; i += 32) cp_async_elem<ELEM>((T*)(st + L::OFF_W) + i, wsrc + i);
+        }
+        if constexpr (BWD) {
+            if (!zb) for (int i = lane; i < Z_DIM; i += 32) cp_async_elem<ELEM>((T*)(st + L::OFF_DZ) + i, zsrc + i);
+        }
+        cp_async_arrive_noinc(full);
     }
 }
 
-// ---------------------------------------------------------------- consumer: forward
+// ---------------------------------------------------------------- forward
 
 template <int Q, int C, class ZA>
 __device__ __forceinline__ void forward_item(const T* __restrict__ sX, const T* __restrict__ sY,
@@ -316,31 +427,43 @@ __device__ __forceinline__ void forward_item(const T* __restrict__ sX, const T* 
             for (int i = 0; i < IN1_D[a]; ++i) xr[XR_OFF[a] + i] = live ? sX[IN1_OFF[a] + u * IN1_D[a] + i] : (T)0;
         }
     });
+    T yr[Y_IN_REGS ? Y_DIM : 1];
+    if constexpr (Y_IN_REGS) {
+        sfor<0, N_IN2>([&](auto b_) {
+            constexpr int b = b_;
+            if constexpr (fwd_part_uses_in2(Q, b)) {
+#pragma unroll
+                for (int j = 0; j < IN2_D[b]; ++j) yr[IN2_OFF[b] + j] = sY[IN2_OFF[b] + j];
+            }
+        });
+    }
     sfor<0, N_OUT>([&](auto o_) {
         constexpr int o = o_;
         if constexpr (FWD_PART_OF_OUT[o] == Q) {
             constexpr int D3 = OUT_D[o];
-            T acc[D3];
-#pragma unroll
-            for (int k = 0; k < D3; ++k) acc[k] = (T)0;
             sfor<0, N_INSTR>([&](auto p_) {
                 constexpr int P = p_;
                 if constexpr (I_OUT[P] == o) {
                     constexpr int a = I_IN1[P], b = I_IN2[P];
-                    constexpr int D1 = IN1_D[a], D2 = IN2_D[b], M2 = IN2_MUL[b];
+                    constexpr int D2 = IN2_D[b], M2 = IN2_MUL[b];
                     if ((IN1_MUL[a] == CHANNELS) || (u < IN1_MUL[a])) {
                         const T* x = xr + XR_OFF[a];
                         if constexpr (M2 == 1) {
-                            T y[D2];
-#pragma unroll
-                            for (int j = 0; j < D2; ++j) y[j] = sY[IN2_OFF[b] + j];
                             T t[D3];
 #pragma unroll
                             for (int k = 0; k < D3; ++k) t[k] = (T)0;
-                            cg_forward<P>(x, y, t);
+                            if constexpr (Y_IN_REGS) {
+                                cg_forward<P>(x, yr + IN2_OFF[b], t);
+                            } else {
+                                T y[D2];
+#pragma unroll
+                                for (int j = 0; j < D2; ++j) y[j] = sY[IN2_OFF[b] + j];
+                                cg_forward<P>(x, y, t);
+                            }
                             const T w = sWt[weight_offset<P>(u, 0)];
 #pragma unroll
-                            for (int k = 0; k < D3; ++k) acc[k] = fma(w, t[k], acc[k]);
+                            for (int k = 0; k < D3; ++k)
+                                zacc[C * ZPC_MAX + ZR_OFF[o] + k] = fma(w, t[k], zacc[C * ZPC_MAX + ZR_OFF[o] + k]);
                         } else {
 #pragma unroll 1
                             for (int v = 0; v < M2; ++v) {
@@ -353,14 +476,13 @@ __device__ __forceinline__ void forward_item(const T* __restrict__ sX, const T* 
                                 cg_forward<P>(x, y, t);
                                 const T w = sWt[weight_offset<P>(u, v)];
 #pragma unroll
-                                for (int k = 0; k < D3; ++k) acc[k] = fma(w, t[k], acc[k]);
+                                for (int k = 0; k < D3; ++k)
+                                    zacc[C * ZPC_MAX + ZR_OFF[o] + k] = fma(w, t[k], zacc[C * ZPC_MAX + ZR_OFF[o] + k]);
                             }
                         }
                     }
                 }
             });
-#pragma unroll
-            for (int k = 0; k < D3; ++k) zacc[C * ZPC_MAX + ZR_OFF[o] + k] += acc[k];
         }
     });
 }
@@ -380,22 +502,17 @@ __device__ __forceinline__ void for_each_out(int u, F&& f) {
 }
 
 template <int MODE>
-__device__ void consumer_forward(const UvuParams& p, const Smem<false, MODE>& sm, int g, int tg) {
+__device__ void run_forward(const UvuParams& p, const Smem<false, MODE>& sm, int g, int tg) {
     using L = StageLayout<false>;
     const int S = sm.stages;
     const int part = tg / MULG;
     const int u0 = tg % MULG;
+    const int lane = tg & 31;
+    const bool issuer = tg < 32;
     const long long total_groups = (long long)gridDim.x * NG;
     const long long gid = (long long)blockIdx.x * NG + g;
-    const long long* bnd = sm.bounds();
     const int bar_id = 1 + g;
 
-    long long count;
-    if constexpr (MODE == MODE_BATCH) {
-        count = gid < p.n_items ? (p.n_items - gid + total_groups - 1) / total_groups : 0;
-    } else {
-        count = bnd[g + 1] - bnd[g];
-    }
     const T* sWshared = reinterpret_cast<const T*>(sm.shared_w());
     T* zbuf = reinterpret_cast<T*>(sm.extra(g));
     const bool z_bulk = p.flags & 8;
@@ -428,28 +545,53 @@ __device__ void consumer_forward(const UvuParams& p, const Smem<false, MODE>& sm
         }
     };
 
-    long long prev = -1;
-    long long next_unwritten = 0;  // deterministic mode: first node of this group's range not yet written
-    if constexpr (MODE == MODE_DET) next_unwritten = bnd[NG + 1 + g];
-    bool ok = true;
-
-    for (long long it = 0; it < count; ++it) {
-        const int stage = (int)(it % S);
-        const long long use = it / S;
-        if (!mbar_wait(sm.full(g, stage), (unsigned)(use & 1), p.status, ERR_WAIT_FULL)) {
-            ok = false;
-            break;
+    // the group's first warp walks the item sequence S - 1 items ahead of the consumers
+    ItemWalker<MODE, false> walker(p, total_groups, gid, lane);
+    long long issued = 0;
+    bool more = true;
+    volatile long long* total = sm.total(g);
+    auto issue_next = [&]() {
+        if (!more) return;
+        long long e, s, r, lo, hi;
+        more = walker.next(e, s, r, lo, hi);
+        if (more) {
+            issue_item<MODE, false>(p, sm, g, (int)(issued % S), lane, e, s, r, lo, hi);
+            ++issued;
+        } else if (lane == 0) {
+            *total = issued;
         }
-        const unsigned char* st = sm.stage(g, stage);
+    };
+    if (issuer) {
+        for (int i = 0; i < S - 1; ++i) issue_next();
+    }
+    group_sync(bar_id, G);
+
+    long long prev = -1;
+    long long next_unwritten = 0;
+    for (long long it = 0;; ++it) {
+        const int stage = (int)(it % S);
+        // Whether item `it` exists was settled S - 1 iterations ago (the issuer runs that far ahead), so
+        // the count, once written, is already visible through the barrier that ended the last iteration.
+        {
+            const long long n = *total;
+            if (n >= 0 && it >= n) break;
+        }
+        // stage (it + S - 1) % S was released by the barrier that ended the previous iteration
+        if (issuer) issue_next();
+        if (!mbar_wait(sm.full(g, stage), (unsigned)((it / S) & 1), p.status, ERR_WAIT_FULL)) break;
         const long long* h = sm.hdr(g, stage);
-        const long long node = h[2];
+        const unsigned char* st = sm.stage(g, stage);
+        const long long node = h[1];
+        const long long lo = h[2], hi = h[3];
         if constexpr (MODE != MODE_BATCH) {
+            if (lo >= 0) next_unwritten = lo;   // a new chunk starts: its first node is unwritten
             if (prev >= 0 && node != prev) {
                 flush(prev);
-                if constexpr (MODE == MODE_DET) next_unwritten = prev + 1;
+                if constexpr (MODE == MODE_DET) next_unwritten = prev + 1 > next_unwritten ? prev + 1 : next_unwritten;
             }
             if constexpr (MODE == MODE_DET) {
-                if (node != prev && next_unwritten < node) zero_nodes(next_unwritten, node);
+                if (next_unwritten < node) zero_nodes(next_unwritten, node);
+                next_unwritten = node + 1;
             }
             prev = node;
         }
@@ -465,8 +607,13 @@ __device__ void consumer_forward(const UvuParams& p, const Smem<false, MODE>& sm
                 });
             }
         });
-        mbar_arrive(sm.empty(g, stage));
-
+        if constexpr (MODE != MODE_BATCH) {
+            if (hi >= 0) {                       // the chunk ends: close its last node and its empty tail
+                flush(node);
+                prev = -1;
+                if constexpr (MODE == MODE_DET) zero_nodes(node + 1, hi);
+            }
+        }
         if constexpr (MODE == MODE_BATCH) {
             T* zb = zbuf + (it & 1) * (ZB / ELEM);
             // the bulk store that last read this buffer (two items ago) must be done
@@ -495,16 +642,10 @@ __device__ void consumer_forward(const UvuParams& p, const Smem<false, MODE>& sm
             } else {
                 group_sync(bar_id, G);
                 for (int i = tg; i < Z_DIM; i += G) zrow[i] = zb[i];
+                group_sync(bar_id, G);
             }
-        }
-    }
-    if constexpr (MODE != MODE_BATCH) {
-        if (ok && prev >= 0) {
-            flush(prev);
-            if constexpr (MODE == MODE_DET) next_unwritten = prev + 1;
-        }
-        if constexpr (MODE == MODE_DET) {
-            if (ok) zero_nodes(next_unwritten, bnd[NG + 2 + g]);
+        } else {
+            group_sync(bar_id, G);   // every thread is done with this stage: it may be refilled
         }
     }
     if constexpr (MODE == MODE_BATCH) {
@@ -512,7 +653,7 @@ __device__ void consumer_forward(const UvuParams& p, const Smem<false, MODE>& sm
     }
 }
 
-// ---------------------------------------------------------------- consumer: backward
+// ---------------------------------------------------------------- backward
 
 template <int Q, int C, class DXA, class DYA>
 __device__ __forceinline__ void backward_item(const T* __restrict__ sX, const T* __restrict__ sY,
@@ -528,6 +669,17 @@ __device__ __forceinline__ void backward_item(const T* __restrict__ sX, const T*
             for (int i = 0; i < IN1_D[a]; ++i) xr[XR_OFF[a] + i] = live ? sX[IN1_OFF[a] + u * IN1_D[a] + i] : (T)0;
         }
     });
+    T yr[Y_IN_REGS ? Y_DIM : 1];
+    if constexpr (Y_IN_REGS) {
+        sfor<0, N_IN2>([&](auto b_) {
+            constexpr int b = b_;
+            if constexpr (bwd_part_uses_in2(Q, b)) {
+#pragma unroll
+                for (int j = 0; j < IN2_D[b]; ++j) yr[IN2_OFF[b] + j] = sY[IN2_OFF[b] + j];
+            }
+        });
+    }
+    T* dwrow = SHARED_W ? dw_acc : p.dW + item * (long long)W_NUMEL;
     sfor<0, N_INSTR>([&](auto p_) {
         constexpr int P = p_;
         if constexpr (BWD_PART_OF_INSTR[P] == Q) {
@@ -538,57 +690,77 @@ __device__ __forceinline__ void backward_item(const T* __restrict__ sX, const T*
 #pragma unroll
             for (int k = 0; k < D3; ++k) gz[k] = live ? sdZ[OUT_OFF[o] + u * D3 + k] : (T)0;
             const T* x = xr + XR_OFF[a];
-            T dxl[D1];
-#pragma unroll
-            for (int i = 0; i < D1; ++i) dxl[i] = (T)0;
             if constexpr (M2 == 1) {
-                T y[D2], dyl[D2];
+                T av[D1], bv[D2];
 #pragma unroll
-                for (int j = 0; j < D2; ++j) { y[j] = sY[IN2_OFF[b] + j]; dyl[j] = (T)0; }
+                for (int i = 0; i < D1; ++i) av[i] = (T)0;
+#pragma unroll
+                for (int j = 0; j < D2; ++j) bv[j] = (T)0;
                 const T w = live ? sWt[weight_offset<P>(u, 0)] : (T)0;
-                const T tw = cg_backward<P>(x, y, gz, dxl, dyl);
-                if (live) {
-                    if constexpr (SHARED_W) dw_acc[weight_offset<P>(u, 0)] += tw;
-                    else p.dW[item * (long long)W_NUMEL + weight_offset<P>(u, 0)] = tw;
+                if constexpr (Y_IN_REGS) {
+                    cg_backward<P>(x, yr + IN2_OFF[b], gz, av, bv);
+                } else {
+                    T y[D2];
+#pragma unroll
+                    for (int j = 0; j < D2; ++j) y[j] = sY[IN2_OFF[b] + j];
+                    cg_backward<P>(x, y, gz, av, bv);
                 }
+                T tw = (T)0;
 #pragma unroll
-                for (int i = 0; i < D1; ++i) dxacc[C * XPC + XR_OFF[a] + i] = fma(w, dxl[i], dxacc[C * XPC + XR_OFF[a] + i]);
+                for (int i = 0; i < D1; ++i) {
+                    tw = fma(x[i], av[i], tw);
+                    dxacc[C * XPC + XR_OFF[a] + i] = fma(w, av[i], dxacc[C * XPC + XR_OFF[a] + i]);
+                }
+                if (live) {
+                    if constexpr (SHARED_W) dwrow[weight_offset<P>(u, 0)] += tw;
+                    else dwrow[weight_offset<P>(u, 0)] = tw;
+                }
+                if constexpr (Y_IN_REGS) {
 #pragma unroll
-                for (int j = 0; j < D2; ++j) dyreg[IN2_OFF[b] + j] = fma(w, dyl[j], dyreg[IN2_OFF[b] + j]);
+                    for (int j = 0; j < D2; ++j) dyreg[IN2_OFF[b] + j] = fma(w, bv[j], dyreg[IN2_OFF[b] + j]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < D2; ++j) {
+                        const T s = warp_sum(w * bv[j]);
+                        if (lane == 0) dy_slot[IN2_OFF[b] + j] += s;
+                    }
+                }
             } else {
 #pragma unroll 1
                 for (int v = 0; v < M2; ++v) {
-                    T y[D2], dyl[D2], dxv[D1];
+                    T y[D2], bv[D2], av[D1];
 #pragma unroll
-                    for (int j = 0; j < D2; ++j) { y[j] = sY[IN2_OFF[b] + v * D2 + j]; dyl[j] = (T)0; }
+                    for (int j = 0; j < D2; ++j) { y[j] = sY[IN2_OFF[b] + v * D2 + j]; bv[j] = (T)0; }
 #pragma unroll
-                    for (int i = 0; i < D1; ++i) dxv[i] = (T)0;
+                    for (int i = 0; i < D1; ++i) av[i] = (T)0;
                     const T w = live ? sWt[weight_offset<P>(u, v)] : (T)0;
-                    const T tw = cg_backward<P>(x, y, gz, dxv, dyl);
-                    if (live) {
-                        if constexpr (SHARED_W) dw_acc[weight_offset<P>(u, v)] += tw;
-                        else p.dW[item * (long long)W_NUMEL + weight_offset<P>(u, v)] = tw;
-                    }
+                    cg_backward<P>(x, y, gz, av, bv);
+                    T tw = (T)0;
 #pragma unroll
-                    for (int i = 0; i < D1; ++i) dxl[i] = fma(w, dxv[i], dxl[i]);
+                    for (int i = 0; i < D1; ++i) {
+                        tw = fma(x[i], av[i], tw);
+                        dxacc[C * XPC + XR_OFF[a] + i] = fma(w, av[i], dxacc[C * XPC + XR_OFF[a] + i]);
+                    }
+                    if (live) {
+                        if constexpr (SHARED_W) dwrow[weight_offset<P>(u, v)] += tw;
+                        else dwrow[weight_offset<P>(u, v)] = tw;
+                    }
                     // reduce this (instruction, v) over the warp's channels; lane 0 owns the warp's slot
 #pragma unroll
                     for (int j = 0; j < D2; ++j) {
-                        const T s = warp_sum(w * dyl[j]);
+                        const T s = warp_sum(w * bv[j]);
                         if (lane == 0) dy_slot[IN2_OFF[b] + v * D2 + j] += s;
                     }
                 }
-#pragma unroll
-                for (int i = 0; i < D1; ++i) dxacc[C * XPC + XR_OFF[a] + i] += dxl[i];
             }
         }
     });
 }
 
-constexpr int DYREG = all_in2_mul_one() ? Y_DIM : 1;
+constexpr int DYREG = Y_IN_REGS ? Y_DIM : 1;
 
 template <int MODE>
-__device__ void consumer_backward(const UvuParams& p, const Smem<true, MODE>& sm, int g, int tg) {
+__device__ void run_backward(const UvuParams& p, const Smem<true, MODE>& sm, int g, int tg) {
     using L = StageLayout<true>;
     using SM = Smem<true, MODE>;
     const int S = sm.stages;
@@ -596,17 +768,11 @@ __device__ void consumer_backward(const UvuParams& p, const Smem<true, MODE>& sm
     const int u0 = tg % MULG;
     const int lane = tg & 31;
     const int warp = tg >> 5;
+    const bool issuer = tg < 32;
     const long long total_groups = (long long)gridDim.x * NG;
     const long long gid = (long long)blockIdx.x * NG + g;
-    const long long* bnd = sm.bounds();
     const int bar_id = 1 + g;
 
-    long long count;
-    if constexpr (MODE == MODE_BATCH) {
-        count = gid < p.n_items ? (p.n_items - gid + total_groups - 1) / total_groups : 0;
-    } else {
-        count = bnd[g + 1] - bnd[g];
-    }
     const T* sWshared = reinterpret_cast<const T*>(sm.shared_w());
     unsigned char* ex = sm.extra(g);
     T* dxbuf = reinterpret_cast<T*>(ex);                           // [PS][XB/ELEM]
@@ -616,7 +782,6 @@ __device__ void consumer_backward(const UvuParams& p, const Smem<true, MODE>& sm
 
     if constexpr (SHARED_W) {
         for (int i = tg; i < W_NUMEL; i += G) dwacc[i] = (T)0;
-        group_sync(bar_id, G);
     }
 
     T dxacc[XPC * NCH];
@@ -673,29 +838,50 @@ __device__ void consumer_backward(const UvuParams& p, const Smem<true, MODE>& sm
         }
     };
 
+    ItemWalker<MODE, true> walker(p, total_groups, gid, lane);
+    long long issued = 0;
+    bool more = true;
+    volatile long long* total = sm.total(g);
+    auto issue_next = [&]() {
+        if (!more) return;
+        long long e, s, r, lo, hi;
+        more = walker.next(e, s, r, lo, hi);
+        if (more) {
+            issue_item<MODE, true>(p, sm, g, (int)(issued % S), lane, e, s, r, lo, hi);
+            ++issued;
+        } else if (lane == 0) {
+            *total = issued;
+        }
+    };
+    if (issuer) {
+        for (int i = 0; i < S - 1; ++i) issue_next();
+    }
+    group_sync(bar_id, G);
+
     long long prev = -1;
     long long next_unwritten = 0;
-    if constexpr (MODE == MODE_DET) next_unwritten = bnd[NG + 1 + g];
-    bool ok = true;
-
-    for (long long it = 0; it < count; ++it) {
+    for (long long it = 0;; ++it) {
         const int stage = (int)(it % S);
-        const long long use = it / S;
-        if (!mbar_wait(sm.full(g, stage), (unsigned)(use & 1), p.status, ERR_WAIT_FULL)) {
-            ok = false;
-            break;
+        {
+            const long long n = *total;
+            if (n >= 0 && it >= n) break;
         }
-        const unsigned char* st = sm.stage(g, stage);
+        if (issuer) issue_next();
+        if (!mbar_wait(sm.full(g, stage), (unsigned)((it / S) & 1), p.status, ERR_WAIT_FULL)) break;
         const long long* h = sm.hdr(g, stage);
+        const unsigned char* st = sm.stage(g, stage);
         const long long item = h[0];
         const long long node = h[1];  // sender
+        const long long lo = h[2], hi = h[3];
         if constexpr (MODE != MODE_BATCH) {
+            if (lo >= 0) next_unwritten = lo;
             if (prev >= 0 && node != prev) {
                 flush(prev);
-                if constexpr (MODE == MODE_DET) next_unwritten = prev + 1;
+                if constexpr (MODE == MODE_DET) next_unwritten = prev + 1 > next_unwritten ? prev + 1 : next_unwritten;
             }
             if constexpr (MODE == MODE_DET) {
-                if (node != prev && next_unwritten < node) zero_nodes(next_unwritten, node);
+                if (next_unwritten < node) zero_nodes(next_unwritten, node);
+                next_unwritten = node + 1;
             }
             prev = node;
         }
@@ -704,8 +890,10 @@ __device__ void consumer_backward(const UvuParams& p, const Smem<true, MODE>& sm
         const T* sWt = SHARED_W ? sWshared : reinterpret_cast<const T*>(st + L::OFF_W);
         const T* sdZ = reinterpret_cast<const T*>(st + L::OFF_DZ);
         T* slot = dyslots + ((it & 1) * WARPS_PER_GROUP + warp) * YS;
-        for (int j = lane; j < Y_DIM; j += 32) slot[j] = (T)0;
-        __syncwarp();
+        if constexpr (!Y_IN_REGS) {
+            for (int j = lane; j < Y_DIM; j += 32) slot[j] = (T)0;
+            __syncwarp();
+        }
 
         T dyreg[DYREG];
 #pragma unroll
@@ -719,18 +907,21 @@ __device__ void consumer_backward(const UvuParams& p, const Smem<true, MODE>& sm
                 });
             }
         });
-        mbar_arrive(sm.empty(g, stage));
-        if constexpr (all_in2_mul_one()) {
-#pragma unroll
-            for (int j = 0; j < Y_DIM; ++j) {
-                const T s = warp_sum(dyreg[j]);
-                if (lane == 0) slot[j] += s;
-            }
+        if constexpr (Y_IN_REGS) {
+            constexpr int SHIFT = 5 - log2_int(next_pow2(Y_DIM));
+            warp_reduce_vector<Y_DIM>(dyreg, lane);
+            const int j = lane >> SHIFT;
+            if ((lane & ((1 << SHIFT) - 1)) == 0 && j < Y_DIM) slot[j] = dyreg[0];
         }
         if constexpr (MODE == MODE_BATCH) {
-            flush(item);  // includes two group barriers, which also order the dY slots
+            flush(item);  // two group barriers, which also order the dY slots and release the stage
         } else {
             group_sync(bar_id, G);
+            if (hi >= 0) {
+                flush(node);
+                prev = -1;
+                if constexpr (MODE == MODE_DET) zero_nodes(node + 1, hi);
+            }
         }
         {
             const T* slots = dyslots + (it & 1) * WARPS_PER_GROUP * YS;
@@ -740,15 +931,6 @@ __device__ void consumer_backward(const UvuParams& p, const Smem<true, MODE>& sm
                 for (int w = 0; w < WARPS_PER_GROUP; ++w) s += slots[w * YS + j];
                 p.dY[item * (long long)Y_DIM + j] = s;
             }
-        }
-    }
-    if constexpr (MODE != MODE_BATCH) {
-        if (ok && prev >= 0) {
-            flush(prev);
-            if constexpr (MODE == MODE_DET) next_unwritten = prev + 1;
-        }
-        if constexpr (MODE == MODE_DET) {
-            if (ok) zero_nodes(next_unwritten, bnd[NG + 2 + g]);
         }
     }
     if constexpr (SHARED_W) {
@@ -766,55 +948,24 @@ __device__ __forceinline__ void uvu_body(const UvuParams& p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     Smem<BWD, MODE> sm(smem_raw, p.stages);
     const int tid = threadIdx.x;
-    const int lane = tid & 31;
-    const bool is_producer = tid >= NCONSUMERS;
 
     if (tid == 0) {
         const bool any_elem = !(p.flags & 1) || !(p.flags & 2) || (!(p.flags & 4) && !SHARED_W) || (BWD && !(p.flags & 8));
-        for (int g = 0; g < NG; ++g)
-            for (int s = 0; s < p.stages; ++s) {
-                mbar_init(sm.full(g, s), 1 + (any_elem ? 32 : 0));
-                mbar_init(sm.empty(g, s), G);
-            }
+        for (int g = 0; g < NG; ++g) {
+            for (int s = 0; s < p.stages; ++s) mbar_init(sm.full(g, s), 1 + (any_elem ? 32 : 0));
+            *sm.total(g) = -1;
+        }
         fence_mbar_init();
     }
-    if (is_producer) {
-        if constexpr (MODE != MODE_BATCH) {
-            long long* bnd = sm.bounds();
-            const long long total_groups = (long long)gridDim.x * NG;
-            for (int j = 0; j <= NG; ++j) {
-                const long long gidx = (long long)blockIdx.x * NG + j;
-                // 128-bit product not needed: n_items * groups stays far below 2^63
-                const long long target = gidx >= total_groups ? p.n_items : (p.n_items / total_groups) * gidx +
-                                         ((p.n_items % total_groups) * gidx) / total_groups;
-                long long e = target;
-                if constexpr (MODE == MODE_DET) e = align_forward<MODE, BWD>(p, target, lane);
-                if (lane == 0) {
-                    bnd[j] = e;
-                    if constexpr (MODE == MODE_DET) {
-                        long long nb = 0;
-                        if (e >= p.n_items) nb = p.n_nodes;
-                        else if (e > 0) nb = item_key<MODE, BWD>(p, e);
-                        if (gidx == 0) nb = 0;
-                        if (gidx >= total_groups) nb = p.n_nodes;
-                        bnd[NG + 1 + j] = nb;
-                    }
-                }
-            }
-        }
-    } else if constexpr (SHARED_W) {
+    if constexpr (SHARED_W) {
         T* sw = reinterpret_cast<T*>(sm.shared_w());
-        for (int i = tid; i < W_NUMEL; i += NCONSUMERS) sw[i] = p.W[i];
+        for (int i = tid; i < W_NUMEL; i += NTHREADS) sw[i] = p.W[i];
     }
     __syncthreads();
 
-    if (is_producer) {
-        producer<MODE, BWD>(p, sm, lane);
-    } else {
-        const int g = tid / G, tg = tid % G;
-        if constexpr (BWD) consumer_backward<MODE>(p, sm, g, tg);
-        else consumer_forward<MODE>(p, sm, g, tg);
-    }
+    const int g = tid / G, tg = tid % G;
+    if constexpr (BWD) run_backward<MODE>(p, sm, g, tg);
+    else run_forward<MODE>(p, sm, g, tg);
 }
 
 }  // namespace oeq
