@@ -204,16 +204,16 @@ constexpr int SMEM_LIMIT = 232448;  // opt-in dynamic shared memory per CTA on s
 int pad16(int b) { return (b + 15) / 16 * 16; }
 
 struct Mapping {
-    int mulg = 32, nch = 1, ps = 1, ng = 1;
+    int mulg = 32, nch = 1, ps = 1, ng = 1, producer = 0, min_ctas = 1;
     std::vector<int> part_of_out, part_of_instr, zr_off, xr_off;
     int zpc_max = 1, xpc = 1;
     int stage_bytes = 0, extra_bytes = 0, sw_bytes = 0;
-    int threads() const { return ng * mulg * ps; }
-    int fixed_bytes(int stages) const { return pad16(ng * stages * 8) + ng * stages * 32 + ng * 16 + sw_bytes; }
+    int threads() const { return ng * mulg * ps + 32 * producer; }
+    int fixed_bytes(int stages) const { return ng * stages * 48 + ng * 128 + sw_bytes; }
     int smem(int stages) const { return fixed_bytes(stages) + ng * (stages * stage_bytes + extra_bytes); }
     int max_stages() const {
         int s = 0;
-        while (s < 8 && smem(s + 1) <= SMEM_LIMIT) ++s;
+        while (s < 4 && smem(s + 1) <= SMEM_LIMIT) ++s;
         return s;
     }
 };
@@ -283,7 +283,7 @@ int choose_mapping(const Problem& p, int kind, Mapping& m) {
     auto extra = [&](int ps) {
         const int warps = m.mulg * ps / 32;
         if (!bwd) return batch ? 2 * zb : 0;
-        return ps * xb + 2 * warps * yb + (p.shared ? pad16(p.w_numel * e) : 0);
+        return ps * xb + 5 * warps * yb + (p.shared ? pad16(p.w_numel * e) : 0);
     };
     // Measured on B200: these kernels are bound by instruction issue, so the mapping that wins is the
     // one with the least per-thread overhead -- as few path partitions as the register file allows, and
@@ -318,6 +318,16 @@ int choose_mapping(const Problem& p, int kind, Mapping& m) {
     m.ps = env_int(bwd ? "OEQ_B200_PS_BWD" : "OEQ_B200_PS_FWD", env_int("OEQ_B200_PS", best_ps));
     m.ng = env_int(bwd ? "OEQ_B200_NG_BWD" : "OEQ_B200_NG_FWD", env_int("OEQ_B200_NG", best_ng));
     m.extra_bytes = extra(m.ps);
+    // a dedicated staging warp pays off for one wide group per CTA; many narrow groups stage their own items
+    m.producer = env_int("OEQ_B200_PRODUCER", (m.ng == 1 && m.mulg * m.ps >= 128) ? 1 : 0);
+    if (m.ng != 1) m.producer = 0;
+    {
+        // let the compiler budget registers for as many CTAs per SM as shared memory admits
+        const int stages = std::min(m.max_stages(), env_int("OEQ_B200_STAGES", 4));
+        const int by_smem = stages >= 2 ? SMEM_LIMIT / (m.smem(stages) + 1024) : 1;
+        const int by_threads = 2048 / m.threads();
+        m.min_ctas = env_int("OEQ_B200_MIN_CTAS", std::max(1, std::min({by_smem, by_threads, 2})));
+    }
     if (m.smem(2) > SMEM_LIMIT || m.ng * m.mulg * m.ps > 992 || m.ng < 1 || m.ng > 8)
         return fail(OEQ_ERR_INVALID, "OEQ_B200_PS / OEQ_B200_NG override does not fit");
     assign_partitions(p, bwd, m);
@@ -418,7 +428,8 @@ std::string descriptor_text(const Problem& p, const Mapping& m, const UvwConfig*
         else snprintf(buf, sizeof buf, "%af", (double)(float)v);
         o << buf;
     });
-    s << "constexpr int MULG = " << m.mulg << ", NCH = " << m.nch << ", PS = " << m.ps << ", NG = " << m.ng << ";\n";
+    s << "constexpr int MULG = " << m.mulg << ", NCH = " << m.nch << ", PS = " << m.ps << ", NG = " << m.ng
+      << ", PRODUCER = " << m.producer << ", MIN_CTAS = " << m.min_ctas << ";\n";
     emit_array(s, "int", "FWD_PART_OF_OUT", m.part_of_out, put_int);
     emit_array(s, "int", "BWD_PART_OF_INSTR", m.part_of_instr, put_int);
     emit_array(s, "int", "ZR_OFF", m.zr_off, put_int);
@@ -645,7 +656,7 @@ int launch_uvu(Kernel& k, const Problem& p, UvuParams& prm, cudaStream_t stream)
     if (env_int("OEQ_B200_NO_BULK", 0)) flags = 0;
     prm.flags = flags;
     prm.stages = k.stages;
-    prm.chunk = std::max(1, env_int("OEQ_B200_CHUNK", 64));
+    prm.chunk = std::max(1, env_int("OEQ_B200_CHUNK", 128));
     long long want = (prm.n_items + k.map.ng - 1) / k.map.ng;
     long long grid = std::max<long long>(1, std::min<long long>((long long)k.sm_count * k.ctas_per_sm, want));
     void* args[] = {&prm};

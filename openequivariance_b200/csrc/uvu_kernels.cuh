@@ -64,8 +64,13 @@ constexpr int MODE_DET = 1;
 constexpr int MODE_ATOMIC = 2;
 
 constexpr int G = MULG * PS;
-constexpr int NTHREADS = NG * G;
+constexpr int NCONSUMERS = NG * G;
+// PRODUCER = 1: one extra warp per CTA stages the items of every group and the groups never meet at a
+// per-item barrier (stages are handed back through "empty" mbarriers).  PRODUCER = 0: the first warp of
+// each group stages that group's items itself (better when a CTA holds many small groups).
+constexpr int NTHREADS = NCONSUMERS + 32 * PRODUCER;
 constexpr int WARPS_PER_GROUP = G / 32;
+constexpr int DY_RING = 5;   // per-item dY partials in flight; stages are capped at DY_RING - 1
 
 // ---------------------------------------------------------------- helpers on the descriptor
 
@@ -220,23 +225,26 @@ struct Smem {
     // per-group extras
     static constexpr int ZBUF = (!BWD && MODE == MODE_BATCH) ? 2 * ZB : 0;      // staged output rows
     static constexpr int DXBUF = BWD ? PS * XB : 0;                             // dX partials per partition
-    static constexpr int DYSLOT = BWD ? 2 * WARPS_PER_GROUP * YB : 0;           // per-warp dY partials, double buffered
+    static constexpr int DYSLOT = BWD ? DY_RING * WARPS_PER_GROUP * YB : 0;     // per-warp dY partials, a ring over items
     static constexpr int DWACC = (BWD && SHARED_W) ? pad16(W_NUMEL * ELEM) : 0; // shared-weight gradient
     static constexpr int EXTRA = ZBUF + DXBUF + DYSLOT + DWACC;
 
     unsigned char* base;
     int stages;
     __device__ Smem(unsigned char* b, int s) : base(b), stages(s) {}
+    static constexpr int CTRL = 128;   // per group: item count (8 B), then DY_RING arrival counters at +16
     __device__ unsigned long long* full(int g, int s) const {
-        return reinterpret_cast<unsigned long long*>(base) + (g * stages + s);
+        return reinterpret_cast<unsigned long long*>(base) + (g * stages + s) * 2;
     }
+    __device__ unsigned long long* empty(int g, int s) const { return full(g, s) + 1; }
     __device__ long long* hdr(int g, int s) const {
-        return reinterpret_cast<long long*>(base + pad16(NG * stages * 8)) + (g * stages + s) * 4;
+        return reinterpret_cast<long long*>(base + NG * stages * 16) + (g * stages + s) * 4;
     }
     __device__ long long* total(int g) const {   // number of items of the group, -1 until known
-        return reinterpret_cast<long long*>(base + pad16(NG * stages * 8) + NG * stages * 32) + g * 2;
+        return reinterpret_cast<long long*>(base + NG * stages * 48 + g * CTRL);
     }
-    __device__ unsigned char* shared_w() const { return base + pad16(NG * stages * 8) + NG * stages * 32 + NG * 16; }
+    __device__ int* arrivals(int g) const { return reinterpret_cast<int*>(base + NG * stages * 48 + g * CTRL + 16); }
+    __device__ unsigned char* shared_w() const { return base + NG * stages * 48 + NG * CTRL; }
     __device__ unsigned char* group_base(int g) const {
         return shared_w() + SWB + (long long)g * (stages * L::BYTES + EXTRA);
     }
@@ -393,10 +401,19 @@ __device__ __forceinline__ void issue_item(const UvuParams& p, const Smem<BWD, M
         if (wb && !SHARED_W) bytes += WB;
         if (BWD && zb) bytes += ZB;
         mbar_arrive_expect_tx(full, bytes);
-        if (BWD && zb) bulk_g2s(st + L::OFF_DZ, zsrc, ZB, full);
-        if (wb && !SHARED_W) bulk_g2s(st + L::OFF_W, wsrc, WB, full);
-        if (xb) bulk_g2s(st + L::OFF_X, xsrc, XB, full);
-        if (yb) bulk_g2s(st + L::OFF_Y, ysrc, YB, full);
+        if constexpr (MODE == MODE_BATCH) {
+            if (BWD && zb) bulk_g2s(st + L::OFF_DZ, zsrc, ZB, full);
+            if (wb && !SHARED_W) bulk_g2s(st + L::OFF_W, wsrc, WB, full);
+            if (xb) bulk_g2s(st + L::OFF_X, xsrc, XB, full);
+            if (yb) bulk_g2s(st + L::OFF_Y, ysrc, YB, full);
+        } else {
+            // gathered node rows are needed again by neighbouring edges; per-edge rows are read once
+            const unsigned long long keep = l2_policy_evict_last(), stream = l2_policy_evict_first();
+            if (BWD && zb) bulk_g2s_hint(st + L::OFF_DZ, zsrc, ZB, full, keep);
+            if (wb && !SHARED_W) bulk_g2s_hint(st + L::OFF_W, wsrc, WB, full, stream);
+            if (xb) bulk_g2s_hint(st + L::OFF_X, xsrc, XB, full, keep);
+            if (yb) bulk_g2s_hint(st + L::OFF_Y, ysrc, YB, full, stream);
+        }
     }
     const bool any_elem = !xb || !yb || (!wb && !SHARED_W) || (BWD && !zb);
     if (any_elem) {
@@ -410,6 +427,60 @@ __device__ __forceinline__ void issue_item(const UvuParams& p, const Smem<BWD, M
         }
         cp_async_arrive_noinc(full);
     }
+}
+
+
+// Producer warp of a CTA with one group: stages items as stage slots are handed back.
+template <int MODE, bool BWD>
+__device__ void run_producer(const UvuParams& p, const Smem<BWD, MODE>& sm, int lane) {
+    const int S = sm.stages;
+    ItemWalker<MODE, BWD> walker(p, (long long)gridDim.x * NG, (long long)blockIdx.x * NG, lane);
+    for (long long it = 0;; ++it) {
+        const int stage = (int)(it % S);
+        long long e, s, r, lo, hi;
+        if (!walker.next(e, s, r, lo, hi)) {
+            if (lane == 0) *reinterpret_cast<volatile long long*>(sm.total(0)) = it;
+            break;
+        }
+        if (it >= S) {
+            if (!mbar_wait(sm.empty(0, stage), (unsigned)(((it / S) - 1) & 1), p.status, ERR_WAIT_EMPTY)) {
+                if (lane == 0) *reinterpret_cast<volatile long long*>(sm.total(0)) = it;
+                break;
+            }
+        }
+        issue_item<MODE, BWD>(p, sm, 0, stage, lane, e, s, r, lo, hi);
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");
+}
+
+// Wait until item `it` of group g has landed.  0: landed, 1: the group has no such item, 2: gave up.
+template <int MODE, bool BWD>
+__device__ __forceinline__ int acquire_item(const UvuParams& p, const Smem<BWD, MODE>& sm, int g, long long it) {
+    const int S = sm.stages;
+    const int stage = (int)(it % S);
+    volatile long long* total = sm.total(g);
+    if constexpr (!PRODUCER) {
+        // the staging warp runs S - 1 items ahead, so the count (once written) is already visible through
+        // the barrier that ended the previous iteration
+        const long long n = *total;
+        if (n >= 0 && it >= n) return 1;
+        return mbar_wait(sm.full(g, stage), (unsigned)((it / S) & 1), p.status, ERR_WAIT_FULL) ? 0 : 2;
+    } else {
+        for (unsigned spin = 0; spin < WAIT_LIMIT; ++spin) {
+            if (mbar_try_wait(sm.full(g, stage), (unsigned)((it / S) & 1))) return 0;
+            const long long n = *total;
+            if (n >= 0 && it >= n) return 1;
+        }
+        if (p.status) atomicCAS(p.status, 0, ERR_WAIT_FULL);
+        return 2;
+    }
+}
+
+// Hand stage `stage` back to the producer warp (PRODUCER mode): one arrival per consumer warp.
+template <int MODE, bool BWD>
+__device__ __forceinline__ void release_stage(const Smem<BWD, MODE>& sm, int g, int stage, int lane) {
+    __syncwarp();
+    if (lane == 0) mbar_arrive(sm.empty(g, stage));
 }
 
 // ---------------------------------------------------------------- forward
@@ -545,11 +616,10 @@ __device__ void run_forward(const UvuParams& p, const Smem<false, MODE>& sm, int
         }
     };
 
-    // the group's first warp walks the item sequence S - 1 items ahead of the consumers
+    // without a producer warp the group's first warp walks the item sequence S - 1 items ahead
     ItemWalker<MODE, false> walker(p, total_groups, gid, lane);
     long long issued = 0;
     bool more = true;
-    volatile long long* total = sm.total(g);
     auto issue_next = [&]() {
         if (!more) return;
         long long e, s, r, lo, hi;
@@ -558,27 +628,25 @@ __device__ void run_forward(const UvuParams& p, const Smem<false, MODE>& sm, int
             issue_item<MODE, false>(p, sm, g, (int)(issued % S), lane, e, s, r, lo, hi);
             ++issued;
         } else if (lane == 0) {
-            *total = issued;
+            *reinterpret_cast<volatile long long*>(sm.total(g)) = issued;
         }
     };
-    if (issuer) {
-        for (int i = 0; i < S - 1; ++i) issue_next();
+    if constexpr (!PRODUCER) {
+        if (issuer) {
+            for (int i = 0; i < S - 1; ++i) issue_next();
+        }
+        group_sync(bar_id, G);
     }
-    group_sync(bar_id, G);
 
     long long prev = -1;
     long long next_unwritten = 0;
     for (long long it = 0;; ++it) {
         const int stage = (int)(it % S);
-        // Whether item `it` exists was settled S - 1 iterations ago (the issuer runs that far ahead), so
-        // the count, once written, is already visible through the barrier that ended the last iteration.
-        {
-            const long long n = *total;
-            if (n >= 0 && it >= n) break;
+        if constexpr (!PRODUCER) {
+            // stage (it + S - 1) % S was released by the barrier that ended the previous iteration
+            if (issuer) issue_next();
         }
-        // stage (it + S - 1) % S was released by the barrier that ended the previous iteration
-        if (issuer) issue_next();
-        if (!mbar_wait(sm.full(g, stage), (unsigned)((it / S) & 1), p.status, ERR_WAIT_FULL)) break;
+        if (acquire_item<MODE, false>(p, sm, g, it) != 0) break;
         const long long* h = sm.hdr(g, stage);
         const unsigned char* st = sm.stage(g, stage);
         const long long node = h[1];
@@ -644,8 +712,11 @@ __device__ void run_forward(const UvuParams& p, const Smem<false, MODE>& sm, int
                 for (int i = tg; i < Z_DIM; i += G) zrow[i] = zb[i];
                 group_sync(bar_id, G);
             }
+            if constexpr (PRODUCER) release_stage<MODE, false>(sm, g, stage, lane);
         } else {
-            group_sync(bar_id, G);   // every thread is done with this stage: it may be refilled
+            // every thread is done with this stage: it may be refilled
+            if constexpr (PRODUCER) release_stage<MODE, false>(sm, g, stage, lane);
+            else group_sync(bar_id, G);
         }
     }
     if constexpr (MODE == MODE_BATCH) {
@@ -713,7 +784,7 @@ __device__ __forceinline__ void backward_item(const T* __restrict__ sX, const T*
                 }
                 if (live) {
                     if constexpr (SHARED_W) dwrow[weight_offset<P>(u, 0)] += tw;
-                    else dwrow[weight_offset<P>(u, 0)] = tw;
+                    else __stcs(dwrow + weight_offset<P>(u, 0), tw);   // written once, never re-read here
                 }
                 if constexpr (Y_IN_REGS) {
 #pragma unroll
@@ -743,7 +814,7 @@ __device__ __forceinline__ void backward_item(const T* __restrict__ sX, const T*
                     }
                     if (live) {
                         if constexpr (SHARED_W) dwrow[weight_offset<P>(u, v)] += tw;
-                        else dwrow[weight_offset<P>(u, v)] = tw;
+                        else __stcs(dwrow + weight_offset<P>(u, v), tw);
                     }
                     // reduce this (instruction, v) over the warp's channels; lane 0 owns the warp's slot
 #pragma unroll
@@ -841,7 +912,6 @@ __device__ void run_backward(const UvuParams& p, const Smem<true, MODE>& sm, int
     ItemWalker<MODE, true> walker(p, total_groups, gid, lane);
     long long issued = 0;
     bool more = true;
-    volatile long long* total = sm.total(g);
     auto issue_next = [&]() {
         if (!more) return;
         long long e, s, r, lo, hi;
@@ -850,24 +920,25 @@ __device__ void run_backward(const UvuParams& p, const Smem<true, MODE>& sm, int
             issue_item<MODE, true>(p, sm, g, (int)(issued % S), lane, e, s, r, lo, hi);
             ++issued;
         } else if (lane == 0) {
-            *total = issued;
+            *reinterpret_cast<volatile long long*>(sm.total(g)) = issued;
         }
     };
-    if (issuer) {
-        for (int i = 0; i < S - 1; ++i) issue_next();
+    if constexpr (!PRODUCER) {
+        if (issuer) {
+            for (int i = 0; i < S - 1; ++i) issue_next();
+        }
     }
-    group_sync(bar_id, G);
+    group_sync(bar_id, G);   // also publishes the cleared shared-weight accumulator
+    int* arrivals = sm.arrivals(g);
 
     long long prev = -1;
     long long next_unwritten = 0;
     for (long long it = 0;; ++it) {
         const int stage = (int)(it % S);
-        {
-            const long long n = *total;
-            if (n >= 0 && it >= n) break;
+        if constexpr (!PRODUCER) {
+            if (issuer) issue_next();
         }
-        if (issuer) issue_next();
-        if (!mbar_wait(sm.full(g, stage), (unsigned)((it / S) & 1), p.status, ERR_WAIT_FULL)) break;
+        if (acquire_item<MODE, true>(p, sm, g, it) != 0) break;
         const long long* h = sm.hdr(g, stage);
         const unsigned char* st = sm.stage(g, stage);
         const long long item = h[0];
@@ -889,7 +960,8 @@ __device__ void run_backward(const UvuParams& p, const Smem<true, MODE>& sm, int
         const T* sY = reinterpret_cast<const T*>(st + L::OFF_Y);
         const T* sWt = SHARED_W ? sWshared : reinterpret_cast<const T*>(st + L::OFF_W);
         const T* sdZ = reinterpret_cast<const T*>(st + L::OFF_DZ);
-        T* slot = dyslots + ((it & 1) * WARPS_PER_GROUP + warp) * YS;
+        const int ring = (int)(it % DY_RING);
+        T* slot = dyslots + (ring * WARPS_PER_GROUP + warp) * YS;
         if constexpr (!Y_IN_REGS) {
             for (int j = lane; j < Y_DIM; j += 32) slot[j] = (T)0;
             __syncwarp();
@@ -913,23 +985,47 @@ __device__ void run_backward(const UvuParams& p, const Smem<true, MODE>& sm, int
             const int j = lane >> SHIFT;
             if ((lane & ((1 << SHIFT) - 1)) == 0 && j < Y_DIM) slot[j] = dyreg[0];
         }
+        const T* slots = dyslots + ring * WARPS_PER_GROUP * YS;
+        auto sum_dy = [&](int first, int step) {   // fixed order over the warps' partials
+            for (int j = first; j < Y_DIM; j += step) {
+                T s = (T)0;
+#pragma unroll
+                for (int w = 0; w < WARPS_PER_GROUP; ++w) s += slots[w * YS + j];
+                p.dY[item * (long long)Y_DIM + j] = s;
+            }
+        };
         if constexpr (MODE == MODE_BATCH) {
-            flush(item);  // two group barriers, which also order the dY slots and release the stage
-        } else {
+            if constexpr (PRODUCER) release_stage<MODE, true>(sm, g, stage, lane);
+            flush(item);  // two group barriers, which also order the dY partials (and release the stage)
+            sum_dy(tg, G);
+        } else if constexpr (!PRODUCER) {
             group_sync(bar_id, G);
             if (hi >= 0) {
                 flush(node);
                 prev = -1;
                 if constexpr (MODE == MODE_DET) zero_nodes(node + 1, hi);
             }
-        }
-        {
-            const T* slots = dyslots + (it & 1) * WARPS_PER_GROUP * YS;
-            for (int j = tg; j < Y_DIM; j += G) {
-                T s = (T)0;
-#pragma unroll
-                for (int w = 0; w < WARPS_PER_GROUP; ++w) s += slots[w * YS + j];
-                p.dY[item * (long long)Y_DIM + j] = s;
+            sum_dy(tg, G);
+        } else {
+            // no per-item barrier: the warp that arrives last sums the partials of the item
+            __syncwarp();
+            int last = 0;
+            if (lane == 0) {
+                mbar_arrive(sm.empty(g, stage));
+                __threadfence_block();
+                last = atomicAdd(arrivals + ring, 1) == WARPS_PER_GROUP - 1;
+            }
+            last = __shfl_sync(0xffffffffu, last, 0);
+            if (last) {
+                __threadfence_block();
+                sum_dy(lane, 32);
+                __syncwarp();
+                if (lane == 0) arrivals[ring] = 0;
+            }
+            if (hi >= 0) {
+                flush(node);
+                prev = -1;
+                if constexpr (MODE == MODE_DET) zero_nodes(node + 1, hi);
             }
         }
     }
@@ -952,8 +1048,12 @@ __device__ __forceinline__ void uvu_body(const UvuParams& p) {
     if (tid == 0) {
         const bool any_elem = !(p.flags & 1) || !(p.flags & 2) || (!(p.flags & 4) && !SHARED_W) || (BWD && !(p.flags & 8));
         for (int g = 0; g < NG; ++g) {
-            for (int s = 0; s < p.stages; ++s) mbar_init(sm.full(g, s), 1 + (any_elem ? 32 : 0));
+            for (int s = 0; s < p.stages; ++s) {
+                mbar_init(sm.full(g, s), 1 + (any_elem ? 32 : 0));
+                mbar_init(sm.empty(g, s), WARPS_PER_GROUP);
+            }
             *sm.total(g) = -1;
+            for (int r = 0; r < DY_RING; ++r) sm.arrivals(g)[r] = 0;
         }
         fence_mbar_init();
     }
@@ -963,6 +1063,10 @@ __device__ __forceinline__ void uvu_body(const UvuParams& p) {
     }
     __syncthreads();
 
+    if (PRODUCER && tid >= NCONSUMERS) {
+        run_producer<MODE, BWD>(p, sm, tid & 31);
+        return;
+    }
     const int g = tid / G, tg = tid % G;
     if constexpr (BWD) run_backward<MODE>(p, sm, g, tg);
     else run_forward<MODE>(p, sm, g, tg);
@@ -978,7 +1082,7 @@ __device__ __forceinline__ void uvu_body(const UvuParams& p) {
 #define OEQ_K_FWD_ATOMIC 4
 #define OEQ_K_BWD_ATOMIC 5
 
-extern "C" __global__ void __launch_bounds__(oeq::NTHREADS, 1) oeq_uvu_kernel(const oeq::UvuParams p) {
+extern "C" __global__ void __launch_bounds__(oeq::NTHREADS, oeqd::MIN_CTAS) oeq_uvu_kernel(const oeq::UvuParams p) {
 #if OEQ_KERNEL == OEQ_K_FWD_BATCH
     oeq::uvu_body<oeq::MODE_BATCH, false>(p);
 #elif OEQ_KERNEL == OEQ_K_BWD_BATCH
