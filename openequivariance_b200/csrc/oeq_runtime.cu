@@ -563,6 +563,57 @@ int build_uvw(const Problem& p, int kind, Kernel& k) {
     return OEQ_OK;
 }
 
+// ---- tensor-core forward for 'uvw' (mirrors the constexpr geometry of uvw_tc_kernels.cuh)
+constexpr int K_UVW_TC_FWD = 20;
+
+struct TcGeometry {
+    size_t packed_bytes = 0;
+    int smem = 0;
+};
+
+bool uvw_tc_geometry(const Problem& p, TcGeometry& g) {
+    if (p.mode != OEQ_MODE_UVW || !p.shared || p.dtype != OEQ_F32) return false;
+    if (!env_int("OEQ_B200_UVW_TC", 1)) return false;
+    int w_max = 0, mw_max = 16;
+    size_t total = 0;
+    for (size_t o = 0; o < p.out.size(); ++o) {
+        int blocks = 0;
+        for (const Instr& t : p.instr)
+            if (t.io == (int)o) {
+                if (p.in2[t.i2].mul != 1) return false;
+                blocks += (p.in1[t.i1].mul + 31) / 32;
+            }
+        if (blocks == 0) continue;
+        const int mw = p.out[o].mul;
+        if (mw % 16 != 0 || mw > 256 || p.out[o].dim > 64) return false;
+        const int bytes = blocks * 2 * mw * 128;
+        w_max = std::max(w_max, bytes);
+        mw_max = std::max(mw_max, mw);
+        total += bytes;
+    }
+    if (total == 0) return false;
+    const int off_w = 2 * 2 * 128 * 128;
+    const int off_stg = off_w + (w_max + 1023) / 1024 * 1024;
+    const int off_bar = off_stg + (128 * (mw_max + 1) * 4 + 15) / 16 * 16;
+    g.smem = off_bar + (2 * 2 + 2 * 32 + 2) * 8 + 16 + 1024;
+    g.packed_bytes = total;
+    return g.smem <= SMEM_LIMIT;
+}
+
+int build_uvw_tc(const Problem& p, Kernel& k) {
+    k.is_uvw = true;
+    int rc = choose_uvw(p, false, k.uvw);
+    if (rc) return rc;
+    k.map.part_of_out.assign(p.out.size(), 0);
+    k.map.part_of_instr.assign(p.instr.size(), 0);
+    k.map.zr_off.assign(p.out.size(), 0);
+    k.map.xr_off.assign(p.in1.size(), 0);
+    rc = compile_kernel(descriptor_text(p, k.map, &k.uvw), "uvw_tc_kernels.cuh", K_UVW_TC_FWD, k.code);
+    if (rc) return rc;
+    k.compiled = true;
+    return OEQ_OK;
+}
+
 int build_tp(const Problem& p, bool bwd, Kernel& k) {
     if (p.mode == OEQ_MODE_UVW) return build_uvw(p, bwd ? K_UVW_BWD : K_UVW_FWD, k);
     return build_uvu(p, bwd ? K_BWD_BATCH : K_FWD_BATCH, k);
@@ -677,6 +728,11 @@ long long uvu_grid(const Kernel& k, long long n_items) {
 struct oeq_tp {
     Problem prob;
     Kernel fwd, bwd;
+    Kernel fwd_tc;              // tensor-core forward ('uvw', shared FP32 weights), when the problem qualifies
+    bool has_tc = false;
+    TcGeometry tc;
+    void* d_packed = nullptr;   // weights split and swizzled for the tensor cores (owned by the handle)
+    cudaKernel_t pack_fn = nullptr;
     int* d_status = nullptr;
     cudaStream_t last_stream = nullptr;
 };
@@ -718,8 +774,10 @@ int oeq_precompile(const oeq_problem_desc* desc, int kinds) {
     if (rc) return rc;
     if (p.mode == OEQ_MODE_UVW) {
         if (kinds & 6) return fail(OEQ_ERR_UNSUPPORTED, "fused convolution supports 'uvu' problems only");
-        Kernel f, b;
+        Kernel f, b, tc;
         if ((rc = build_tp(p, false, f)) || (rc = build_tp(p, true, b))) return rc;
+        TcGeometry g;
+        if (uvw_tc_geometry(p, g) && (rc = build_uvw_tc(p, tc))) return rc;
         return OEQ_OK;
     }
     auto one = [&](int kind) {
@@ -750,6 +808,10 @@ int oeq_tp_create(const oeq_problem_desc* desc, oeq_tp** out) {
     int rc = ingest(desc, h->prob);
     if (!rc) rc = build_tp(h->prob, false, h->fwd);
     if (!rc) rc = build_tp(h->prob, true, h->bwd);
+    if (!rc && uvw_tc_geometry(h->prob, h->tc)) {
+        rc = build_uvw_tc(h->prob, h->fwd_tc);
+        h->has_tc = rc == OEQ_OK;
+    }
     if (rc) {
         delete h;
         return rc;
@@ -761,8 +823,10 @@ int oeq_tp_create(const oeq_problem_desc* desc, oeq_tp** out) {
 int oeq_tp_destroy(oeq_tp* h) {
     if (!h) return OEQ_OK;
     if (h->d_status) cudaFree(h->d_status);
+    if (h->d_packed) cudaFree(h->d_packed);
     if (h->fwd.lib) cudaLibraryUnload(h->fwd.lib);
     if (h->bwd.lib) cudaLibraryUnload(h->bwd.lib);
+    if (h->fwd_tc.lib) cudaLibraryUnload(h->fwd_tc.lib);
     delete h;
     return OEQ_OK;
 }
@@ -784,6 +848,35 @@ int oeq_tp_forward(oeq_tp* h, int64_t batch, const void* X, const void* Y, const
     int rc = ensure_status(&h->d_status);
     if (rc) return rc;
     h->last_stream = (cudaStream_t)stream;
+    if (h->has_tc) {
+        Kernel& k = h->fwd_tc;
+        cudaStream_t st = (cudaStream_t)stream;
+        if (!k.loaded) {
+            OEQ_CUDA(cudaLibraryLoadData(&k.lib, k.code.cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0));
+            OEQ_CUDA(cudaLibraryGetKernel(&k.fn, k.lib, "oeq_uvw_tc_kernel"));
+            OEQ_CUDA(cudaLibraryGetKernel(&h->pack_fn, k.lib, "oeq_uvw_pack_weights"));
+            int dev = 0;
+            OEQ_CUDA(cudaGetDevice(&dev));
+            OEQ_CUDA(cudaDeviceGetAttribute(&k.sm_count, cudaDevAttrMultiProcessorCount, dev));
+            k.smem = h->tc.smem;
+            OEQ_CUDA(cudaFuncSetAttribute((const void*)k.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, k.smem));
+            cudaFuncAttributes attr;
+            if (cudaFuncGetAttributes(&attr, (const void*)k.fn) == cudaSuccess) k.regs = attr.numRegs;
+            else (void)cudaGetLastError();
+            OEQ_CUDA(cudaMalloc(&h->d_packed, h->tc.packed_bytes));
+            k.loaded = true;
+        }
+        {
+            void* packed = h->d_packed;
+            void* args[] = {(void*)&W, &packed};
+            OEQ_CUDA(cudaLaunchKernel((const void*)h->pack_fn, dim3(64), dim3(256), args, 0, st));
+        }
+        struct { const void* X; const void* Y; const void* Wp; void* Z; long long batch; int* status; } tp{X, Y, h->d_packed, Z, batch, h->d_status};
+        void* args[] = {&tp};
+        const long long grid = std::max<long long>(1, std::min<long long>(k.sm_count, (batch + 23) / 24));
+        OEQ_CUDA(cudaLaunchKernel((const void*)k.fn, dim3((unsigned)grid), dim3(21 * 32), args, (size_t)k.smem, st));
+        return OEQ_OK;
+    }
     if (h->prob.mode == OEQ_MODE_UVW) {
         if ((rc = load_uvw(h->fwd, h->prob, false))) return rc;
         UvwParams up{};
@@ -898,6 +991,15 @@ static int launch_info(const Kernel& k, int* threads, int* ng, int* ps, int* sta
 }
 int oeq_tp_launch_info(const oeq_tp* h, int which, int* threads, int* ng, int* ps, int* stages, int* smem, int* regs) {
     if (!h) return fail(OEQ_ERR_INVALID, "null handle");
+    if (!which && h->has_tc) {
+        if (threads) *threads = 21 * 32;
+        if (ng) *ng = 1;
+        if (ps) *ps = 1;
+        if (stages) *stages = 2;
+        if (smem) *smem = h->fwd_tc.smem;
+        if (regs) *regs = h->fwd_tc.regs;
+        return OEQ_OK;
+    }
     return launch_info(which ? h->bwd : h->fwd, threads, ng, ps, stages, smem, regs);
 }
 

@@ -77,3 +77,35 @@ def test_full_batch_linearity_and_sampled_rows():
     w_e3nn = to_e3nn(p, w.cpu().numpy())
     ref = orc.tp_forward(p, x1[idx].cpu().numpy(), y[idx].cpu().numpy(), w_e3nn)
     assert rel_err(z1[idx].cpu().numpy(), ref) < 1e-5
+
+
+TC_SHAPES = [
+    ("64x0e+64x1o+64x2e", "0e+1o+2e", "64x0e+64x1o+64x2e", 777),       # the benchmark shape
+    ("40x0e+24x1o", "0e+1o", "16x0e+48x1o+32x2e", 301),                 # multiplicities padded to 32-wide K slices
+    ("32x1o+96x2e", "1o+2e+3o", "64x0e+16x1o+32x3o", 130),              # l = 3 output: 7 accumulator rows per batch row
+    ("8x0e+8x1o", "0e+1o", "128x0e", 50),                                # wide N, very short K
+]
+
+
+@pytest.mark.parametrize("in1,in2,out,batch", TC_SHAPES, ids=[s[2] for s in TC_SHAPES])
+def test_tensor_core_forward_matches_oracle_and_fma_path(in1, in2, out, batch, monkeypatch):
+    """Shared-weight FP32 problems run their forward pass on tcgen05 with 3xTF32 compensation; it must
+    meet the same FP32 tolerance as the FMA path, on full and ragged row chunks."""
+    p = oeq.FullyConnectedTPProblem(in1, in2, out)
+    tp = oeq.TensorProduct(p, torch_op=True)
+    assert tp.internal.launch_info(0)["threads"] == 21 * 32       # tensor-core kernel selected
+    x, y, w, dz = tp_inputs(p, batch, 21)
+    w = (w / np.sqrt(max(1, p.weight_numel / len(p.instructions)))).astype(np.float32)
+    xt, yt, wt = (torch.from_numpy(a).cuda() for a in (x, y, to_oeq(p, w)))
+    z = tp(xt, yt, wt)
+    torch.cuda.synchronize()
+    tp.check_device_status()
+    ref = orc.tp_forward(p, x, y, w)
+    assert rel_err(z.cpu().numpy(), ref) < 1e-5
+    monkeypatch.setenv("OEQ_B200_UVW_TC", "0")
+    fma = oeq.TensorProduct(p, torch_op=True)
+    assert fma.internal.launch_info(0)["threads"] == 256
+    assert rel_err(fma(xt, yt, wt).cpu().numpy(), ref) < 1e-5
+    # repeated launches reuse the accumulator ring and the packed weights
+    for _ in range(3):
+        assert torch.equal(z, tp(xt, yt, wt))
