@@ -14,7 +14,7 @@ for one forward plus one backward pass with inputs resident in HBM; ``e2e`` is t
 every input copied from pinned host memory and every output copied back inside the timed
 region.  For N > 1 the graph is split by receiver range (strong scaling): sender features are
 all-gathered before the forward kernel and their gradients reduce-scattered after the backward
-kernel, both inside the timed region.
+kernel, both inside the timed region (only halo rows -- senders owned by another rank -- move).
 """
 
 import argparse
@@ -315,10 +315,10 @@ def run_ours(args):
 
     # -- roofline of the dominant kernel (backward), rank 0's launch
     fb, bb = algorithmic_bytes(problem, owned if world > 1 else nodes, local_edges)
-    if world > 1:   # a shard reads/writes all senders' rows of X / dX once, owned rows of Z / dZ
+    if world > 1:   # a shard reads/writes its owned and halo rows of X / dX once, owned rows of Z / dZ
         xd, zd = problem.irreps_in1.dim, problem.irreps_out.dim
-        fb = local_edges * ((problem.weight_numel + problem.irreps_in2.dim) * 4 + 16) + (plan.padded_nodes * xd + owned * zd) * 4
-        bb = local_edges * (2 * (problem.weight_numel + problem.irreps_in2.dim) * 4 + 24) + (2 * plan.padded_nodes * xd + owned * zd) * 4
+        fb = local_edges * ((problem.weight_numel + problem.irreps_in2.dim) * 4 + 16) + (plan.local_nodes * xd + owned * zd) * 4
+        bb = local_edges * (2 * (problem.weight_numel + problem.irreps_in2.dim) * 4 + 24) + (2 * plan.local_nodes * xd + owned * zd) * 4
     peak, peak_kind = measured_peak()
     roofline = {"bound": "hbm", "kernel": "oeq_uvu_kernel (conv backward)", "achieved": bb / (bwd_ms * 1e-3) / 1e9,
                 "peak": peak, "peak_source": peak_kind, "unit": "GB/s", "frac": bb / (bwd_ms * 1e-3) / 1e9 / peak,

@@ -6,16 +6,22 @@ openequivariance/extension/util/backend_cuda.hpp:204,258); this layer is new.
 Partition: rank ``g`` of ``G`` owns the receiver nodes ``[g*C, min((g+1)*C, N))``
 with ``C = ceil(N / G)`` and, because edges are sorted by receiver, a contiguous
 slice of the edge list.  Edge features, weights and their gradients never leave
-their rank.  The only exchange is on node features:
+their rank.  The only exchange is on node features, and only on the *halo*: the
+sender nodes of a rank's edges that another rank owns.
 
-* forward: all-gather of the owners' ``X`` rows into a local ``[G*C, X.dim]``
-  buffer, then the local deterministic convolution writes ``Z`` for owned rows;
-* backward: the local kernel produces this rank's contribution to ``dX`` of
-  *every* sender, and a reduce-scatter (sum) leaves each rank with ``dX`` of the
-  nodes it owns.
+* forward: every rank sends the rows of ``X`` that its peers' edges read
+  (all-to-all with per-peer row lists fixed at set-up); the local deterministic
+  kernel then runs on ``[owned rows | halo rows]`` with sender ids renumbered
+  into that compact space;
+* backward: the local kernel produces ``dX`` for owned and halo rows; halo rows
+  travel back to their owners (the mirrored all-to-all) and are added to the
+  owners' rows peer by peer in rank order, so the result is reproducible.
 
-Collectives go through ``torch.distributed`` (NCCL on GPUs; gloo works for the
-host-side logic on CPU tensors when a ``local_conv`` stand-in is supplied).
+With spatially ordered node ids the halo is a thin shell, so the exchanged
+volume is a small fraction of an all-gather of ``X``.  Collectives go through
+``torch.distributed`` (NCCL on GPUs; gloo works for the host-side logic on CPU
+tensors when a ``local_conv`` stand-in is supplied).  Every rank builds the
+plan of every rank from the global edge list, so set-up needs no communication.
 """
 
 from __future__ import annotations
@@ -25,8 +31,13 @@ import torch
 import torch.distributed as dist
 
 
+def _owned_range(nodes: int, rank: int, world: int):
+    chunk = -(-nodes // world) if nodes else 0
+    return min(rank * chunk, nodes), min((rank + 1) * chunk, nodes)
+
+
 class ShardPlan:
-    """Which nodes and edges a rank owns, and its local index arrays."""
+    """Which nodes and edges a rank owns, its halo, and its local index arrays."""
 
     def __init__(self, rows: np.ndarray, cols: np.ndarray, nodes: int, rank: int, world: int):
         rows = np.asarray(rows, dtype=np.int64)
@@ -36,39 +47,63 @@ class ShardPlan:
         if not (0 <= rank < world):
             raise ValueError("rank out of range")
         self.nodes, self.rank, self.world = int(nodes), rank, world
-        self.chunk = -(-self.nodes // world) if nodes else 0
-        self.node_lo = min(rank * self.chunk, self.nodes)
-        self.node_hi = min((rank + 1) * self.chunk, self.nodes)
+        self.node_lo, self.node_hi = _owned_range(self.nodes, rank, world)
         self.edge_lo = int(np.searchsorted(rows, self.node_lo, side="left"))
         self.edge_hi = int(np.searchsorted(rows, self.node_hi, side="left"))
-        self.local_rows = rows[self.edge_lo:self.edge_hi] - self.node_lo     # receivers, local numbering
-        self.local_cols = cols[self.edge_lo:self.edge_hi].copy()             # senders, global numbering
-        # k-th local edge in (sender, receiver) order
+        local_cols = cols[self.edge_lo:self.edge_hi]
+        senders = np.unique(local_cols)
+        outside = (senders < self.node_lo) | (senders >= self.node_hi)
+        self.halo = senders[outside]                               # global ids, ascending
+        # compact sender numbering: owned nodes first, then the halo in ascending global order
+        halo_pos = np.searchsorted(self.halo, local_cols)
+        is_owned = (local_cols >= self.node_lo) & (local_cols < self.node_hi)
+        self.local_cols = np.where(is_owned, local_cols - self.node_lo, self.owned + halo_pos).astype(np.int64)
+        self.local_rows = rows[self.edge_lo:self.edge_hi] - self.node_lo
+        # k-th local edge in (sender, receiver) order of the compact numbering
         self.local_perm = np.lexsort((self.local_rows, self.local_cols)).astype(np.int64)
+        # halo rows grouped by owner (owners hold contiguous id ranges, so this is a split of self.halo)
+        bounds = [_owned_range(self.nodes, q, world)[0] for q in range(world)] + [self.nodes]
+        self.recv_counts = [int(np.searchsorted(self.halo, bounds[q + 1]) - np.searchsorted(self.halo, bounds[q]))
+                            for q in range(world)]
+        self.send_rows = None     # filled by build_exchange
 
     @property
     def owned(self) -> int:
         return self.node_hi - self.node_lo
 
     @property
-    def padded_nodes(self) -> int:
-        return self.chunk * self.world
+    def local_nodes(self) -> int:
+        return self.owned + int(self.halo.size)
+
+    @staticmethod
+    def build_all(rows, cols, nodes, world):
+        """Plans of all ranks with their send lists (rows each rank ships to each peer)."""
+        plans = [ShardPlan(rows, cols, nodes, r, world) for r in range(world)]
+        for me in plans:
+            me.send_rows = []
+            for peer in plans:
+                if peer.rank == me.rank:
+                    me.send_rows.append(np.zeros(0, dtype=np.int64))
+                    continue
+                wanted = peer.halo[(peer.halo >= me.node_lo) & (peer.halo < me.node_hi)]
+                me.send_rows.append((wanted - me.node_lo).astype(np.int64))
+        return plans
 
 
 class _ShardedConvFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, module, x_owned, y, w):
-        x_full = module.gather_senders(x_owned)
+        x_local = module.gather_senders(x_owned)
         ctx.module = module
-        ctx.save_for_backward(x_full, y, w)
-        return module.local_forward(x_full, y, w)
+        ctx.save_for_backward(x_local, y, w)
+        return module.local_forward(x_local, y, w)
 
     @staticmethod
     def backward(ctx, dz):
         module = ctx.module
-        x_full, y, w = ctx.saved_tensors
-        dx_all, dy, dw = module.local_backward(x_full, y, w, dz.contiguous())
-        return None, module.scatter_sender_grads(dx_all), dy, dw
+        x_local, y, w = ctx.saved_tensors
+        dx_local, dy, dw = module.local_backward(x_local, y, w, dz.contiguous())
+        return None, module.scatter_sender_grads(dx_local), dy, dw
 
 
 class ShardedTensorProductConv:
@@ -83,7 +118,7 @@ class ShardedTensorProductConv:
         self.group = group
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
-        self.plan = ShardPlan(rows, cols, nodes, self.rank, self.world)
+        self.plan = ShardPlan.build_all(rows, cols, nodes, self.world)[self.rank]
         self.problem = problem
         self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
         if local_conv is None:
@@ -91,45 +126,60 @@ class ShardedTensorProductConv:
             local_conv = TensorProductConv(problem, torch_op=True, deterministic=True)
         self.conv = local_conv
         as_dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(self.device)
-        self.rows = as_dev(self.plan.local_rows)
-        self.cols = as_dev(self.plan.local_cols)
-        self.perm = as_dev(self.plan.local_perm)
-        self._x_full = None
+        plan = self.plan
+        self.rows = as_dev(plan.local_rows)
+        self.cols = as_dev(plan.local_cols)
+        self.perm = as_dev(plan.local_perm)
+        self.send_counts = [int(s.size) for s in plan.send_rows]
+        self.recv_counts = list(plan.recv_counts)
+        self.send_index = as_dev(np.concatenate(plan.send_rows)) if self.world > 1 else None
+        self.send_index_per_peer = [as_dev(s) for s in plan.send_rows] if self.world > 1 else []
+        self._x_local = None
 
     # ---- exchange steps -------------------------------------------------------------
 
     def gather_senders(self, x_owned: torch.Tensor) -> torch.Tensor:
-        """All-gather of the owned rows of X into ``[world*chunk, X.dim]`` (tail ranks zero-padded)."""
+        """``[owned rows | halo rows]`` of X: one all-to-all of the rows the peers' edges read."""
         plan = self.plan
         if x_owned.shape[0] != plan.owned:
             raise ValueError(f"rank {self.rank} owns {plan.owned} nodes, got {x_owned.shape[0]} rows")
         if self.world == 1:
             return x_owned.contiguous()
-        buf = self._x_full
+        buf = self._x_local
         if buf is None or buf.dtype != x_owned.dtype or buf.shape[1] != x_owned.shape[1]:
-            buf = self._x_full = torch.zeros((plan.padded_nodes, x_owned.shape[1]), dtype=x_owned.dtype,
-                                             device=x_owned.device)
-        send = buf[self.rank * plan.chunk:(self.rank + 1) * plan.chunk]
-        send[:plan.owned].copy_(x_owned)
-        dist.all_gather_into_tensor(buf, send, group=self.group)
+            buf = self._x_local = torch.empty((plan.local_nodes, x_owned.shape[1]), dtype=x_owned.dtype,
+                                              device=x_owned.device)
+        buf[:plan.owned].copy_(x_owned)
+        send = x_owned.index_select(0, self.send_index)
+        dist.all_to_all_single(buf[plan.owned:], send, output_split_sizes=self.recv_counts,
+                               input_split_sizes=self.send_counts, group=self.group)
         return buf
 
-    def scatter_sender_grads(self, dx_all: torch.Tensor) -> torch.Tensor:
-        """Reduce-scatter (sum) of the per-rank dX contributions; returns the owned rows."""
+    def scatter_sender_grads(self, dx_local: torch.Tensor) -> torch.Tensor:
+        """Halo rows of dX go back to their owners and are added peer by peer in rank order."""
         plan = self.plan
+        dx_owned = dx_local[:plan.owned]
         if self.world == 1:
-            return dx_all[:plan.owned]
-        out = torch.empty((plan.chunk, dx_all.shape[1]), dtype=dx_all.dtype, device=dx_all.device)
-        dist.reduce_scatter_tensor(out, dx_all, op=dist.ReduceOp.SUM, group=self.group)
-        return out[:plan.owned]
+            return dx_owned
+        recv = torch.empty((sum(self.send_counts), dx_local.shape[1]), dtype=dx_local.dtype, device=dx_local.device)
+        dist.all_to_all_single(recv, dx_local[plan.owned:].contiguous(), output_split_sizes=self.send_counts,
+                               input_split_sizes=self.recv_counts, group=self.group)
+        out = dx_owned.clone()
+        start = 0
+        for peer, count in enumerate(self.send_counts):      # fixed order; indices are unique within a peer
+            if count:
+                idx = self.send_index_per_peer[peer]
+                out[idx] = out[idx] + recv[start:start + count]
+                start += count
+        return out
 
     # ---- local kernels -----------------------------------------------------------------
 
-    def local_forward(self, x_full, y, w):
-        return self.conv._forward_impl(x_full, y, w, self.rows, self.cols, self.perm, n_out=self.plan.owned)
+    def local_forward(self, x_local, y, w):
+        return self.conv._forward_impl(x_local, y, w, self.rows, self.cols, self.perm, n_out=self.plan.owned)
 
-    def local_backward(self, x_full, y, w, dz):
-        return self.conv._backward_impl(x_full, y, w, dz, self.rows, self.cols, self.perm)
+    def local_backward(self, x_local, y, w, dz):
+        return self.conv._backward_impl(x_local, y, w, dz, self.rows, self.cols, self.perm)
 
     # ---- public ------------------------------------------------------------------------
 
@@ -140,7 +190,7 @@ class ShardedTensorProductConv:
 
     def forward_backward(self, x_owned, y, w, dz):
         """One fused step without autograd bookkeeping: returns (Z, dX_owned, dY, dW)."""
-        x_full = self.gather_senders(x_owned)
-        z = self.local_forward(x_full, y, w)
-        dx_all, dy, dw = self.local_backward(x_full, y, w, dz)
-        return z, self.scatter_sender_grads(dx_all), dy, dw
+        x_local = self.gather_senders(x_owned)
+        z = self.local_forward(x_local, y, w)
+        dx_local, dy, dw = self.local_backward(x_local, y, w, dz)
+        return z, self.scatter_sender_grads(dx_local), dy, dw

@@ -38,7 +38,7 @@ def test_plan_partitions_nodes_and_edges():
     rows, cols = random_graph(37, 400, seed=1)
     rows, cols, _, _ = orc.coord_graph(rows, cols)
     for world in (1, 2, 3, 8):
-        plans = [ShardPlan(rows, cols, 37, r, world) for r in range(world)]
+        plans = ShardPlan.build_all(rows, cols, 37, world)
         assert plans[0].node_lo == 0 and plans[-1].node_hi == 37
         assert sum(p.owned for p in plans) == 37
         assert plans[0].edge_lo == 0 and plans[-1].edge_hi == len(rows)
@@ -47,7 +47,19 @@ def test_plan_partitions_nodes_and_edges():
         for p in plans:
             assert np.all((p.local_rows >= 0) & (p.local_rows < max(p.owned, 1)))
             assert np.all(np.diff(p.local_cols[p.local_perm]) >= 0)      # sender order
-            assert p.padded_nodes >= 37 and p.padded_nodes % world == 0
+            # the compact sender numbering maps back to the global ids: owned rows first, then the halo
+            to_global = np.concatenate([np.arange(p.node_lo, p.node_hi), p.halo])
+            assert np.array_equal(to_global[p.local_cols], cols[p.edge_lo:p.edge_hi])
+            assert np.all((p.halo < p.node_lo) | (p.halo >= p.node_hi)) and np.all(np.diff(p.halo) > 0)
+            assert sum(p.recv_counts) == p.halo.size and p.recv_counts[p.rank] == 0
+        # what rank a sends to rank b is exactly what b expects from a, in b's halo order
+        for a in plans:
+            for b in plans:
+                assert len(a.send_rows[b.rank]) == b.recv_counts[a.rank]
+                if a.rank != b.rank:
+                    first = sum(b.recv_counts[:a.rank])
+                    assert np.array_equal(a.send_rows[b.rank] + a.node_lo,
+                                          b.halo[first:first + b.recv_counts[a.rank]])
     with pytest.raises(ValueError):
         ShardPlan(rows[::-1], cols, 37, 0, 2)
     with pytest.raises(ValueError):
