@@ -7,6 +7,7 @@ Workloads (``--workload``):
   mace_large  MACE-large irreps 128x(0e+1o+2e+3o), spherical harmonics to l=3, periodic radius
               graph of 200 000 nodes at mean degree 30 (about 6 M edges); deterministic variant.
               The default: it is the configuration the headline metric is quoted on.
+  mace        MACE irreps 128x(0e+1o+2e), harmonics to l=3, 100 000 nodes at degree 30.
   nequip      Nequip irreps 32x(0e+1o+2e), harmonics to l=2, 20 000 nodes at degree 40.
 
 One JSON line is printed by rank 0.  ``value`` is edges processed per second by the whole job
@@ -37,6 +38,8 @@ WORKLOADS = {
     "mace_large": dict(in1="128x0e+128x1o+128x2e+128x3o", in2="1x0e+1x1o+1x2e+1x3o",
                        out="128x0e+128x1o+128x2e+128x3o", lmax=3, nodes=200_000, degree=30.0,
                        cpu_sample_edges=20_000),
+    "mace": dict(in1="128x0e+128x1o+128x2e", in2="1x0e+1x1o+1x2e+1x3o", out="128x0e+128x1o+128x2e", lmax=3,
+                 nodes=100_000, degree=30.0, cpu_sample_edges=50_000),
     "nequip": dict(in1="32x0e+32x1o+32x2e", in2="0e+1o+2e", out="32x0e+32x1o+32x2e", lmax=2, nodes=20_000,
                    degree=40.0, cpu_sample_edges=100_000),
 }

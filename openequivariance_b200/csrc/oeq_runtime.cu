@@ -205,10 +205,13 @@ int pad16(int b) { return (b + 15) / 16 * 16; }
 
 struct Mapping {
     int mulg = 32, nch = 1, ps = 1, ng = 1, producer = 0, min_ctas = 1;
+    int nph = 1;                              // backward staging in phases (see uvu_kernels.cuh)
+    std::vector<int> z_ph_begin, w_ph_begin;  // nph + 1 column / weight boundaries
+    std::vector<int> phase_of_instr;
     std::vector<int> part_of_out, part_of_instr, zr_off, xr_off;
     int zpc_max = 1, xpc = 1;
     int stage_bytes = 0, extra_bytes = 0, sw_bytes = 0;
-    int threads() const { return ng * mulg * ps + 32 * producer; }
+    int threads() const { return ng * mulg * ps + 32 * ng * producer; }
     int fixed_bytes(int stages) const { return ng * stages * 48 + ng * 128 + sw_bytes; }
     int smem(int stages) const { return fixed_bytes(stages) + ng * (stages * stage_bytes + extra_bytes); }
     int max_stages() const {
@@ -286,30 +289,93 @@ int choose_mapping(const Problem& p, int kind, Mapping& m) {
         return ps * xb + 5 * warps * yb + (p.shared ? pad16(p.w_numel * e) : 0);
     };
     // Measured on B200: these kernels are bound by instruction issue, so the mapping that wins is the
-    // one with the least per-thread overhead -- as few path partitions as the register file allows, and
-    // moderate CTAs (several per SM) rather than one wide one.
+    // one with the least per-thread overhead and the most independent groups per SM: one path
+    // partition unless registers force more, and as many groups as shared memory admits.
     int xpc = 0;
     for (const Irrep& r : p.in1) xpc += r.dim;
     int best_ps = 1;
     if (!bwd) {
         auto regs = [&](int ps) { return zpc * m.nch / ps + xpc * m.nch + std::min(p.y_dim, 32) + 56; };
         while (regs(best_ps) > 232 && best_ps < 4 && best_ps * 2 <= units) best_ps *= 2;
-    } else {
-        const int g_target = m.stage_bytes > 32768 ? 256 : 64;
-        while (m.mulg * best_ps * 2 <= g_target && best_ps < 4 && best_ps * 2 <= units) best_ps *= 2;
     }
-    int best_ng = 0;
-    {
-        Mapping t = m;
-        t.ps = best_ps;
-        t.extra_bytes = extra(best_ps);
-        const int g = m.mulg * best_ps;
+    auto groups_that_fit = [&](const Mapping& base, int ps) {
+        Mapping t = base;
+        t.ps = ps;
+        t.extra_bytes = extra(ps);
+        const int g = m.mulg * ps;
         const int want = std::max(1, std::min(8, (bwd ? 512 : (g >= 128 ? 128 : 256)) / g));
         for (int cand = want; cand >= 1; --cand) {
             t.ng = cand;
-            if (t.smem(bwd ? 2 : 3) <= SMEM_LIMIT || (cand == 1 && t.smem(2) <= SMEM_LIMIT)) {
-                best_ng = cand;
-                break;
+            if (t.smem(cand > 1 ? 2 : (bwd ? 2 : 3)) <= SMEM_LIMIT || (cand == 1 && t.smem(2) <= SMEM_LIMIT)) return cand;
+        }
+        return 0;
+    };
+    m.phase_of_instr.assign(p.instr.size(), 0);
+    int best_ng = groups_that_fit(m, best_ps);
+    m.nph = 1;
+    m.z_ph_begin = {0, p.z_dim};
+    m.w_ph_begin = {0, p.w_numel};
+    const int max_phases = env_int("OEQ_B200_PHASES", 2);
+    if (bwd && !batch && !p.shared) {
+        // One or two groups per SM leave the issue slots half empty.  Stage the output-gradient row (the
+        // bulk of a backward stage) in slices: cut the output irreps into nph runs of about equal width at
+        // boundaries where the weights (ordered by instruction) split the same way; keep the largest
+        // group count, preferring fewer phases.
+        // (measured: going from one group to two pays; slicing further to reach three or four does not)
+        const int target_groups = std::max(1, std::min(env_int("OEQ_B200_PHASE_GROUPS", 2), 512 / (m.mulg * best_ps)));
+        for (int nph = 2; nph <= max_phases && best_ng < target_groups; ++nph) {
+            std::vector<int> cut = {0};          // output irrep index where each phase starts
+            for (int q = 1; q < nph; ++q) {
+                const int want = (int)((long long)p.z_dim * q / nph);
+                int best = -1;
+                for (size_t os = cut.back() + 1; os < p.out.size(); ++os)
+                    if (best < 0 || std::abs(p.out[os].off - want) < std::abs(p.out[best].off - want)) best = (int)os;
+                if (best < 0) break;
+                cut.push_back(best);
+            }
+            if ((int)cut.size() != nph) continue;
+            cut.push_back((int)p.out.size());
+            std::vector<int> zb(nph + 1), wbeg(nph + 1);
+            bool ok = true;
+            for (int q = 0; q <= nph; ++q) zb[q] = q == nph ? p.z_dim : p.out[cut[q]].off;
+            // weights of phase q must be the contiguous run [wbeg[q], wbeg[q+1])
+            wbeg[0] = 0;
+            wbeg[nph] = p.w_numel;
+            for (int q = 1; q < nph && ok; ++q) {
+                int lo = p.w_numel;
+                for (const Instr& t : p.instr)
+                    if (t.io >= cut[q]) lo = std::min(lo, t.w_off);
+                wbeg[q] = lo;
+            }
+            std::vector<int> phase(p.instr.size(), 0);
+            for (size_t i = 0; i < p.instr.size() && ok; ++i) {
+                const Instr& t = p.instr[i];
+                int q = 0;
+                while (q + 1 < nph && t.io >= cut[q + 1]) ++q;
+                phase[i] = q;
+                const int size = p.in1[t.i1].mul * p.in2[t.i2].mul;
+                if (t.w_off < wbeg[q] || t.w_off + size > wbeg[q + 1]) ok = false;
+            }
+            for (int q = 0; q <= nph && ok; ++q)
+                if ((zb[q] * e) % 16 || (wbeg[q] * e) % 16) ok = false;
+            for (int q = 0; q < nph && ok; ++q)
+                if (zb[q + 1] <= zb[q] || wbeg[q + 1] <= wbeg[q]) ok = false;
+            if (!ok) continue;
+            int wmax = 0, zmax = 0;
+            for (int q = 0; q < nph; ++q) {
+                wmax = std::max(wmax, wbeg[q + 1] - wbeg[q]);
+                zmax = std::max(zmax, zb[q + 1] - zb[q]);
+            }
+            Mapping t = m;
+            t.stage_bytes = xb + yb + pad16(wmax * e) + pad16(zmax * e);
+            const int ng = groups_that_fit(t, best_ps);
+            if (ng > best_ng) {
+                best_ng = ng;
+                m.stage_bytes = t.stage_bytes;
+                m.nph = nph;
+                m.z_ph_begin = zb;
+                m.w_ph_begin = wbeg;
+                m.phase_of_instr = phase;
             }
         }
     }
@@ -319,8 +385,8 @@ int choose_mapping(const Problem& p, int kind, Mapping& m) {
     m.ng = env_int(bwd ? "OEQ_B200_NG_BWD" : "OEQ_B200_NG_FWD", env_int("OEQ_B200_NG", best_ng));
     m.extra_bytes = extra(m.ps);
     // a dedicated staging warp pays off for one wide group per CTA; many narrow groups stage their own items
-    m.producer = env_int("OEQ_B200_PRODUCER", (m.ng == 1 && m.mulg * m.ps >= 128) ? 1 : 0);
-    if (m.ng != 1) m.producer = 0;
+    m.producer = env_int("OEQ_B200_PRODUCER", (m.ng <= 4 && m.mulg * m.ps >= 128) ? 1 : 0);
+    if (m.ng > 4) m.producer = 0;
     {
         // let the compiler budget registers for as many CTAs per SM as shared memory admits
         const int stages = std::min(m.max_stages(), env_int("OEQ_B200_STAGES", 4));
@@ -434,6 +500,23 @@ std::string descriptor_text(const Problem& p, const Mapping& m, const UvwConfig*
     emit_array(s, "int", "BWD_PART_OF_INSTR", m.part_of_instr, put_int);
     emit_array(s, "int", "ZR_OFF", m.zr_off, put_int);
     emit_array(s, "int", "XR_OFF", m.xr_off, put_int);
+    {
+        std::vector<int> ph = m.phase_of_instr;
+        ph.resize(p.instr.size(), 0);
+        emit_array(s, "int", "BWD_PHASE_OF_INSTR", ph, put_int);
+        s << "constexpr int BWD_NPH = " << m.nph << ";\n";
+        std::vector<int> zb = m.z_ph_begin, wb2 = m.w_ph_begin;
+        if (zb.empty()) zb = {0, p.z_dim};
+        if (wb2.empty()) wb2 = {0, p.w_numel};
+        emit_array(s, "int", "Z_PH_BEGIN", zb, put_int);
+        emit_array(s, "int", "W_PH_BEGIN", wb2, put_int);
+        // the same tables again with device storage, for run-time indexing by phase
+        s << "__device__ const int Z_PH_BEGIN_DEV[] = {";
+        for (size_t i = 0; i < zb.size(); ++i) s << (i ? ", " : "") << zb[i];
+        s << "};\n__device__ const int W_PH_BEGIN_DEV[] = {";
+        for (size_t i = 0; i < wb2.size(); ++i) s << (i ? ", " : "") << wb2[i];
+        s << "};\n";
+    }
     s << "constexpr int ZPC_MAX = " << m.zpc_max << ", XPC = " << m.xpc << ";\n";
     if (uvw)
         s << "constexpr int TILE_R = " << uvw->tile_r << ", UVC = " << uvw->uvc << ", DMAX = " << uvw->dmax

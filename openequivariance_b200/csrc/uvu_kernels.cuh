@@ -65,10 +65,10 @@ constexpr int MODE_ATOMIC = 2;
 
 constexpr int G = MULG * PS;
 constexpr int NCONSUMERS = NG * G;
-// PRODUCER = 1: one extra warp per CTA stages the items of every group and the groups never meet at a
+// PRODUCER = 1: one extra warp per group stages that group's items and the group's warps never meet at a
 // per-item barrier (stages are handed back through "empty" mbarriers).  PRODUCER = 0: the first warp of
 // each group stages that group's items itself (better when a CTA holds many small groups).
-constexpr int NTHREADS = NCONSUMERS + 32 * PRODUCER;
+constexpr int NTHREADS = NCONSUMERS + 32 * NG * PRODUCER;   // one staging warp per group
 constexpr int WARPS_PER_GROUP = G / 32;
 constexpr int DY_RING = 5;   // per-item dY partials in flight; stages are capped at DY_RING - 1
 
@@ -80,13 +80,27 @@ constexpr int XB = pad16(X_DIM * ELEM), YB = pad16(Y_DIM * ELEM), ZB = pad16(Z_D
 constexpr int WB = SHARED_W ? 0 : pad16(W_NUMEL * ELEM);
 constexpr int SWB = SHARED_W ? pad16(W_NUMEL * ELEM) : 0;
 
+// Backward staging in phases: with NPH > 1 an edge is staged as NPH items.  Phase q carries the weights
+// [W_PH_BEGIN[q], W_PH_BEGIN[q+1]) and the output-gradient columns [Z_PH_BEGIN[q], Z_PH_BEGIN[q+1]) of
+// the instructions assigned to it; X and Y travel with phase 0.  A stage then holds only a slice of the
+// (large) output-gradient row, so several groups fit per SM.
+constexpr int NPH = BWD_NPH;
+constexpr int imax(int a, int b) { return a > b ? a : b; }
+constexpr int max_phase_width(const int* begin) {
+    int m = 0;
+    for (int q = 0; q < NPH; ++q) m = imax(m, begin[q + 1] - begin[q]);
+    return m;
+}
+constexpr int WPHB = SHARED_W ? 0 : pad16(max_phase_width(W_PH_BEGIN) * ELEM);
+constexpr int ZPHB = pad16(max_phase_width(Z_PH_BEGIN) * ELEM);
+
 template <bool BWD>
 struct StageLayout {
     static constexpr int OFF_X = 0;
     static constexpr int OFF_Y = OFF_X + XB;
     static constexpr int OFF_W = OFF_Y + YB;
-    static constexpr int OFF_DZ = OFF_W + WB;
-    static constexpr int BYTES = OFF_DZ + (BWD ? ZB : 0);
+    static constexpr int OFF_DZ = OFF_W + (BWD ? WPHB : WB);
+    static constexpr int BYTES = OFF_DZ + (BWD ? ZPHB : 0);
 };
 
 constexpr bool fwd_part_uses_in1(int q, int a) {
@@ -380,15 +394,21 @@ struct ItemWalker {
 // Stage one item into ring slot `stage` (executed by the group's first warp).
 template <int MODE, bool BWD>
 __device__ __forceinline__ void issue_item(const UvuParams& p, const Smem<BWD, MODE>& sm, int g, int stage, int lane,
-                                           long long e, long long s, long long r, long long lo, long long hi) {
+                                           long long e, long long s, long long r, long long lo, long long hi,
+                                           int ph = 0) {
     using L = StageLayout<BWD>;
+    const bool first = ph == 0;                       // X and Y travel with the first phase only
     const bool xb = p.flags & 1, yb = p.flags & 2, wb = p.flags & 4, zb = p.flags & 8;
     unsigned char* st = sm.stage(g, stage);
     unsigned long long* full = sm.full(g, stage);
     const T* xsrc = p.X + s * X_DIM;
     const T* ysrc = p.Y + e * Y_DIM;
-    const T* wsrc = SHARED_W ? nullptr : p.W + e * (long long)W_NUMEL;
-    const T* zsrc = BWD ? p.dZ + r * (long long)Z_DIM : nullptr;
+    // weights and output gradient: the whole row, or this phase's part of it
+    const int w_lo = BWD ? W_PH_BEGIN_DEV[ph] : 0, w_n = BWD ? W_PH_BEGIN_DEV[ph + 1] - w_lo : W_NUMEL;
+    const int z_lo = BWD ? Z_PH_BEGIN_DEV[ph] : 0, z_n = BWD ? Z_PH_BEGIN_DEV[ph + 1] - z_lo : Z_DIM;
+    const T* wsrc = SHARED_W ? nullptr : p.W + e * (long long)W_NUMEL + w_lo;
+    const T* zsrc = BWD ? p.dZ + r * (long long)Z_DIM + z_lo : nullptr;
+    const unsigned wbytes = (unsigned)pad16(w_n * ELEM), zbytes = (unsigned)pad16(z_n * ELEM);
     if (lane == 0) {
         long long* h = sm.hdr(g, stage);
         h[0] = e;
@@ -396,60 +416,58 @@ __device__ __forceinline__ void issue_item(const UvuParams& p, const Smem<BWD, M
         h[2] = lo;
         h[3] = hi;
         unsigned bytes = 0;
-        if (xb) bytes += XB;
-        if (yb) bytes += YB;
-        if (wb && !SHARED_W) bytes += WB;
-        if (BWD && zb) bytes += ZB;
+        if (xb && first) bytes += XB;
+        if (yb && first) bytes += YB;
+        if (wb && !SHARED_W) bytes += wbytes;
+        if (BWD && zb) bytes += zbytes;
         mbar_arrive_expect_tx(full, bytes);
         if constexpr (MODE == MODE_BATCH) {
-            if (BWD && zb) bulk_g2s(st + L::OFF_DZ, zsrc, ZB, full);
-            if (wb && !SHARED_W) bulk_g2s(st + L::OFF_W, wsrc, WB, full);
-            if (xb) bulk_g2s(st + L::OFF_X, xsrc, XB, full);
-            if (yb) bulk_g2s(st + L::OFF_Y, ysrc, YB, full);
+            if (BWD && zb) bulk_g2s(st + L::OFF_DZ, zsrc, zbytes, full);
+            if (wb && !SHARED_W) bulk_g2s(st + L::OFF_W, wsrc, wbytes, full);
+            if (xb && first) bulk_g2s(st + L::OFF_X, xsrc, XB, full);
+            if (yb && first) bulk_g2s(st + L::OFF_Y, ysrc, YB, full);
         } else {
             // gathered node rows are needed again by neighbouring edges; per-edge rows are read once
             const unsigned long long keep = l2_policy_evict_last(), stream = l2_policy_evict_first();
-            if (BWD && zb) bulk_g2s_hint(st + L::OFF_DZ, zsrc, ZB, full, keep);
-            if (wb && !SHARED_W) bulk_g2s_hint(st + L::OFF_W, wsrc, WB, full, stream);
-            if (xb) bulk_g2s_hint(st + L::OFF_X, xsrc, XB, full, keep);
-            if (yb) bulk_g2s_hint(st + L::OFF_Y, ysrc, YB, full, stream);
+            if (BWD && zb) bulk_g2s_hint(st + L::OFF_DZ, zsrc, zbytes, full, keep);
+            if (wb && !SHARED_W) bulk_g2s_hint(st + L::OFF_W, wsrc, wbytes, full, stream);
+            if (xb && first) bulk_g2s_hint(st + L::OFF_X, xsrc, XB, full, keep);
+            if (yb && first) bulk_g2s_hint(st + L::OFF_Y, ysrc, YB, full, stream);
         }
     }
     const bool any_elem = !xb || !yb || (!wb && !SHARED_W) || (BWD && !zb);
     if (any_elem) {
-        if (!xb) for (int i = lane; i < X_DIM; i += 32) cp_async_elem<ELEM>((T*)(st + L::OFF_X) + i, xsrc + i);
-        if (!yb) for (int i = lane; i < Y_DIM; i += 32) cp_async_elem<ELEM>((T*)(st + L::OFF_Y) + i, ysrc + i);
+        if (!xb && first) for (int i = lane; i < X_DIM; i += 32) cp_async_elem<ELEM>((T*)(st + L::OFF_X) + i, xsrc + i);
+        if (!yb && first) for (int i = lane; i < Y_DIM; i += 32) cp_async_elem<ELEM>((T*)(st + L::OFF_Y) + i, ysrc + i);
         if constexpr (!SHARED_W) {
-            if (!wb) for (int i = lane; i < W_NUMEL; i += 32) cp_async_elem<ELEM>((T*)(st + L::OFF_W) + i, wsrc + i);
+            if (!wb) for (int i = lane; i < w_n; i += 32) cp_async_elem<ELEM>((T*)(st + L::OFF_W) + i, wsrc + i);
         }
         if constexpr (BWD) {
-            if (!zb) for (int i = lane; i < Z_DIM; i += 32) cp_async_elem<ELEM>((T*)(st + L::OFF_DZ) + i, zsrc + i);
+            if (!zb) for (int i = lane; i < z_n; i += 32) cp_async_elem<ELEM>((T*)(st + L::OFF_DZ) + i, zsrc + i);
         }
         cp_async_arrive_noinc(full);
     }
 }
 
-
-// Producer warp of a CTA with one group: stages items as stage slots are handed back.
+// Producer warp of group g: stages the group's items as stage slots are handed back.
 template <int MODE, bool BWD>
-__device__ void run_producer(const UvuParams& p, const Smem<BWD, MODE>& sm, int lane) {
+__device__ void run_producer(const UvuParams& p, const Smem<BWD, MODE>& sm, int g, int lane) {
     const int S = sm.stages;
-    ItemWalker<MODE, BWD> walker(p, (long long)gridDim.x * NG, (long long)blockIdx.x * NG, lane);
-    for (long long it = 0;; ++it) {
-        const int stage = (int)(it % S);
+    ItemWalker<MODE, BWD> walker(p, (long long)gridDim.x * NG, (long long)blockIdx.x * NG + g, lane);
+    constexpr int PHASES = BWD ? NPH : 1;
+    volatile long long* total = sm.total(g);
+    long long it = 0;
+    bool ok = true;
+    while (ok) {
         long long e, s, r, lo, hi;
-        if (!walker.next(e, s, r, lo, hi)) {
-            if (lane == 0) *reinterpret_cast<volatile long long*>(sm.total(0)) = it;
-            break;
+        if (!walker.next(e, s, r, lo, hi)) break;
+        for (int ph = 0; ph < PHASES && ok; ++ph, ++it) {
+            const int stage = (int)(it % S);
+            if (it >= S) ok = mbar_wait(sm.empty(g, stage), (unsigned)(((it / S) - 1) & 1), p.status, ERR_WAIT_EMPTY);
+            if (ok) issue_item<MODE, BWD>(p, sm, g, stage, lane, e, s, r, lo, hi, ph);
         }
-        if (it >= S) {
-            if (!mbar_wait(sm.empty(0, stage), (unsigned)(((it / S) - 1) & 1), p.status, ERR_WAIT_EMPTY)) {
-                if (lane == 0) *reinterpret_cast<volatile long long*>(sm.total(0)) = it;
-                break;
-            }
-        }
-        issue_item<MODE, BWD>(p, sm, 0, stage, lane, e, s, r, lo, hi);
     }
+    if (lane == 0) *total = it - (ok ? 0 : 1);
     asm volatile("cp.async.wait_all;" ::: "memory");
 }
 
@@ -726,21 +744,19 @@ __device__ void run_forward(const UvuParams& p, const Smem<false, MODE>& sm, int
 
 // ---------------------------------------------------------------- backward
 
-template <int Q, int C, class DXA, class DYA>
-__device__ __forceinline__ void backward_item(const T* __restrict__ sX, const T* __restrict__ sY,
-                                              const T* __restrict__ sWt, const T* __restrict__ sdZ, int u,
-                                              long long item, const UvuParams& p, T* __restrict__ dw_acc,
-                                              T* __restrict__ dy_slot, int lane, DXA& dxacc, DYA& dyreg) {
-    T xr[XPC];
+// Channel u's inputs, read once per edge (phase 0) and kept in registers across the phases.
+template <int Q, int C, class XR, class YR>
+__device__ __forceinline__ void backward_load_inputs(const T* __restrict__ sX, const T* __restrict__ sY, int u,
+                                                     XR& xr, YR& yr) {
     sfor<0, N_IN1>([&](auto a_) {
         constexpr int a = a_;
         if constexpr (bwd_part_uses_in1(Q, a)) {
             const bool live = (IN1_MUL[a] == CHANNELS) || (u < IN1_MUL[a]);
 #pragma unroll
-            for (int i = 0; i < IN1_D[a]; ++i) xr[XR_OFF[a] + i] = live ? sX[IN1_OFF[a] + u * IN1_D[a] + i] : (T)0;
+            for (int i = 0; i < IN1_D[a]; ++i)
+                xr[C * XPC + XR_OFF[a] + i] = live ? sX[IN1_OFF[a] + u * IN1_D[a] + i] : (T)0;
         }
     });
-    T yr[Y_IN_REGS ? Y_DIM : 1];
     if constexpr (Y_IN_REGS) {
         sfor<0, N_IN2>([&](auto b_) {
             constexpr int b = b_;
@@ -750,26 +766,36 @@ __device__ __forceinline__ void backward_item(const T* __restrict__ sX, const T*
             }
         });
     }
+}
+
+// Instructions of partition Q that are staged in phase PH.  sWt / sdZ point at the stage's weight and
+// output-gradient parts, which start at weight W_PH_BEGIN[PH] / column Z_PH_BEGIN[PH] of the full rows.
+template <int Q, int C, int PH, class XR, class YR, class DXA, class DYA>
+__device__ __forceinline__ void backward_item(const XR& xr, const YR& yr, const T* __restrict__ sY,
+                                              const T* __restrict__ sWt, const T* __restrict__ sdZ, int u,
+                                              long long item, const UvuParams& p, T* __restrict__ dw_acc,
+                                              T* __restrict__ dy_slot, int lane, DXA& dxacc, DYA& dyreg) {
+    constexpr int WBASE = W_PH_BEGIN[PH], ZBASE = Z_PH_BEGIN[PH];
     T* dwrow = SHARED_W ? dw_acc : p.dW + item * (long long)W_NUMEL;
     sfor<0, N_INSTR>([&](auto p_) {
         constexpr int P = p_;
-        if constexpr (BWD_PART_OF_INSTR[P] == Q) {
+        if constexpr (BWD_PART_OF_INSTR[P] == Q && BWD_PHASE_OF_INSTR[P] == PH) {
             constexpr int a = I_IN1[P], b = I_IN2[P], o = I_OUT[P];
             constexpr int D1 = IN1_D[a], D2 = IN2_D[b], D3 = OUT_D[o], M2 = IN2_MUL[b];
             const bool live = (IN1_MUL[a] == CHANNELS) || (u < IN1_MUL[a]);
             T gz[D3];
 #pragma unroll
-            for (int k = 0; k < D3; ++k) gz[k] = live ? sdZ[OUT_OFF[o] + u * D3 + k] : (T)0;
-            const T* x = xr + XR_OFF[a];
+            for (int k = 0; k < D3; ++k) gz[k] = live ? sdZ[OUT_OFF[o] - ZBASE + u * D3 + k] : (T)0;
+            const T* x = &xr[C * XPC + XR_OFF[a]];
             if constexpr (M2 == 1) {
                 T av[D1], bv[D2];
 #pragma unroll
                 for (int i = 0; i < D1; ++i) av[i] = (T)0;
 #pragma unroll
                 for (int j = 0; j < D2; ++j) bv[j] = (T)0;
-                const T w = live ? sWt[weight_offset<P>(u, 0)] : (T)0;
+                const T w = live ? sWt[weight_offset<P>(u, 0) - WBASE] : (T)0;
                 if constexpr (Y_IN_REGS) {
-                    cg_backward<P>(x, yr + IN2_OFF[b], gz, av, bv);
+                    cg_backward<P>(x, &yr[IN2_OFF[b]], gz, av, bv);
                 } else {
                     T y[D2];
 #pragma unroll
@@ -804,7 +830,7 @@ __device__ __forceinline__ void backward_item(const T* __restrict__ sX, const T*
                     for (int j = 0; j < D2; ++j) { y[j] = sY[IN2_OFF[b] + v * D2 + j]; bv[j] = (T)0; }
 #pragma unroll
                     for (int i = 0; i < D1; ++i) av[i] = (T)0;
-                    const T w = live ? sWt[weight_offset<P>(u, v)] : (T)0;
+                    const T w = live ? sWt[weight_offset<P>(u, v) - WBASE] : (T)0;
                     cg_backward<P>(x, y, gz, av, bv);
                     T tw = (T)0;
 #pragma unroll
@@ -847,7 +873,7 @@ __device__ void run_backward(const UvuParams& p, const Smem<true, MODE>& sm, int
     const T* sWshared = reinterpret_cast<const T*>(sm.shared_w());
     unsigned char* ex = sm.extra(g);
     T* dxbuf = reinterpret_cast<T*>(ex);                           // [PS][XB/ELEM]
-    T* dyslots = reinterpret_cast<T*>(ex + SM::DXBUF);             // [2][WARPS_PER_GROUP][YB/ELEM]
+    T* dyslots = reinterpret_cast<T*>(ex + SM::DXBUF);             // [DY_RING][WARPS_PER_GROUP][YB/ELEM]
     T* dwacc = reinterpret_cast<T*>(ex + SM::DXBUF + SM::DYSLOT);  // [W_NUMEL] (shared weights)
     constexpr int XS = XB / ELEM, YS = YB / ELEM;
 
@@ -858,6 +884,9 @@ __device__ void run_backward(const UvuParams& p, const Smem<true, MODE>& sm, int
     T dxacc[XPC * NCH];
 #pragma unroll
     for (int i = 0; i < XPC * NCH; ++i) dxacc[i] = (T)0;
+    T xr[XPC * NCH];
+    T yr[Y_IN_REGS ? Y_DIM : 1];
+    T dyreg[DYREG];
 
     // Combine the partitions' dX partial sums through shared memory and write the row of `node`.
     auto flush = [&](long long node) {
@@ -909,19 +938,24 @@ __device__ void run_backward(const UvuParams& p, const Smem<true, MODE>& sm, int
         }
     };
 
+    // without a producer warp the group's first warp stages items S - 1 ahead; an edge is NPH items
     ItemWalker<MODE, true> walker(p, total_groups, gid, lane);
     long long issued = 0;
     bool more = true;
+    int next_phase = 0;
+    long long ce = 0, cs = 0, cr = 0, clo = -1, chi = -1;
     auto issue_next = [&]() {
         if (!more) return;
-        long long e, s, r, lo, hi;
-        more = walker.next(e, s, r, lo, hi);
-        if (more) {
-            issue_item<MODE, true>(p, sm, g, (int)(issued % S), lane, e, s, r, lo, hi);
-            ++issued;
-        } else if (lane == 0) {
-            *reinterpret_cast<volatile long long*>(sm.total(g)) = issued;
+        if (next_phase == 0) {
+            more = walker.next(ce, cs, cr, clo, chi);
+            if (!more) {
+                if (lane == 0) *reinterpret_cast<volatile long long*>(sm.total(g)) = issued;
+                return;
+            }
         }
+        issue_item<MODE, true>(p, sm, g, (int)(issued % S), lane, ce, cs, cr, clo, chi, next_phase);
+        ++issued;
+        next_phase = (next_phase + 1) % NPH;
     };
     if constexpr (!PRODUCER) {
         if (issuer) {
@@ -935,6 +969,8 @@ __device__ void run_backward(const UvuParams& p, const Smem<true, MODE>& sm, int
     long long next_unwritten = 0;
     for (long long it = 0;; ++it) {
         const int stage = (int)(it % S);
+        const int ph = (int)(it % NPH);
+        const long long edge_it = it / NPH;
         if constexpr (!PRODUCER) {
             if (issuer) issue_next();
         }
@@ -944,41 +980,64 @@ __device__ void run_backward(const UvuParams& p, const Smem<true, MODE>& sm, int
         const long long item = h[0];
         const long long node = h[1];  // sender
         const long long lo = h[2], hi = h[3];
-        if constexpr (MODE != MODE_BATCH) {
-            if (lo >= 0) next_unwritten = lo;
-            if (prev >= 0 && node != prev) {
-                flush(prev);
-                if constexpr (MODE == MODE_DET) next_unwritten = prev + 1 > next_unwritten ? prev + 1 : next_unwritten;
-            }
-            if constexpr (MODE == MODE_DET) {
-                if (next_unwritten < node) zero_nodes(next_unwritten, node);
-                next_unwritten = node + 1;
-            }
-            prev = node;
-        }
         const T* sX = reinterpret_cast<const T*>(st + L::OFF_X);
         const T* sY = reinterpret_cast<const T*>(st + L::OFF_Y);
         const T* sWt = SHARED_W ? sWshared : reinterpret_cast<const T*>(st + L::OFF_W);
         const T* sdZ = reinterpret_cast<const T*>(st + L::OFF_DZ);
-        const int ring = (int)(it % DY_RING);
+        const int ring = (int)(edge_it % DY_RING);
         T* slot = dyslots + (ring * WARPS_PER_GROUP + warp) * YS;
-        if constexpr (!Y_IN_REGS) {
-            for (int j = lane; j < Y_DIM; j += 32) slot[j] = (T)0;
-            __syncwarp();
-        }
+        const bool last_phase = ph == NPH - 1;
 
-        T dyreg[DYREG];
+        if (ph == 0) {
+            if constexpr (MODE != MODE_BATCH) {
+                if (lo >= 0) next_unwritten = lo;
+                if (prev >= 0 && node != prev) {
+                    flush(prev);
+                    if constexpr (MODE == MODE_DET) next_unwritten = prev + 1 > next_unwritten ? prev + 1 : next_unwritten;
+                }
+                if constexpr (MODE == MODE_DET) {
+                    if (next_unwritten < node) zero_nodes(next_unwritten, node);
+                    next_unwritten = node + 1;
+                }
+                prev = node;
+            }
+            if constexpr (!Y_IN_REGS) {
+                for (int j = lane; j < Y_DIM; j += 32) slot[j] = (T)0;
+                __syncwarp();
+            }
 #pragma unroll
-        for (int j = 0; j < DYREG; ++j) dyreg[j] = (T)0;
-        sfor<0, PS>([&](auto q_) {
-            constexpr int Q = q_;
-            if (part == Q) {
-                sfor<0, NCH>([&](auto c_) {
-                    constexpr int C = c_;
-                    backward_item<Q, C>(sX, sY, sWt, sdZ, u0 + C * MULG, item, p, dwacc, slot, lane, dxacc, dyreg);
+            for (int j = 0; j < DYREG; ++j) dyreg[j] = (T)0;
+            sfor<0, PS>([&](auto q_) {
+                constexpr int Q = q_;
+                if (part == Q) {
+                    sfor<0, NCH>([&](auto c_) {
+                        constexpr int C = c_;
+                        backward_load_inputs<Q, C>(sX, sY, u0 + C * MULG, xr, yr);
+                    });
+                }
+            });
+        }
+        sfor<0, NPH>([&](auto ph_) {
+            constexpr int PH = ph_;
+            if (ph == PH) {
+                sfor<0, PS>([&](auto q_) {
+                    constexpr int Q = q_;
+                    if (part == Q) {
+                        sfor<0, NCH>([&](auto c_) {
+                            constexpr int C = c_;
+                            backward_item<Q, C, PH>(xr, yr, sY, sWt, sdZ, u0 + C * MULG, item, p, dwacc, slot, lane,
+                                                    dxacc, dyreg);
+                        });
+                    }
                 });
             }
         });
+        if (!last_phase) {
+            // more of this edge follows in the next stage; hand this one back
+            if constexpr (PRODUCER) release_stage<MODE, true>(sm, g, stage, lane);
+            else group_sync(bar_id, G);
+            continue;
+        }
         if constexpr (Y_IN_REGS) {
             constexpr int SHIFT = 5 - log2_int(next_pow2(Y_DIM));
             warp_reduce_vector<Y_DIM>(dyreg, lane);
@@ -1064,7 +1123,7 @@ __device__ __forceinline__ void uvu_body(const UvuParams& p) {
     __syncthreads();
 
     if (PRODUCER && tid >= NCONSUMERS) {
-        run_producer<MODE, BWD>(p, sm, tid & 31);
+        run_producer<MODE, BWD>(p, sm, (tid - NCONSUMERS) >> 5, tid & 31);
         return;
     }
     const int g = tid / G, tg = tid % G;
