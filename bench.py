@@ -45,6 +45,12 @@ WORKLOADS = {
 }
 
 
+# DRAM read+write bytes per edge of the deterministic backward launch, from a one-pass ncu capture
+# (dram__bytes_read.sum + dram__bytes_write.sum) of the full-size run; proportional to the edge count
+# at fixed degree, so it scales to other --nodes values of the same workload.
+NCU_BWD_DRAM_BYTES_PER_EDGE = {("mace_large", "morton"): 377.4e9 / 6004880}
+
+
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -323,9 +329,11 @@ def run_ours(args):
         fb = local_edges * ((problem.weight_numel + problem.irreps_in2.dim) * 4 + 16) + (plan.local_nodes * xd + owned * zd) * 4
         bb = local_edges * (2 * (problem.weight_numel + problem.irreps_in2.dim) * 4 + 24) + (2 * plan.local_nodes * xd + owned * zd) * 4
     peak, peak_kind = measured_peak()
+    per_edge = NCU_BWD_DRAM_BYTES_PER_EDGE.get((args.workload, args.numbering))
+    traffic = per_edge * local_edges if (per_edge is not None and world == 1 and det) else None
     roofline = {"bound": "hbm", "kernel": "oeq_uvu_kernel (conv backward)", "achieved": bb / (bwd_ms * 1e-3) / 1e9,
                 "peak": peak, "peak_source": peak_kind, "unit": "GB/s", "frac": bb / (bwd_ms * 1e-3) / 1e9 / peak,
-                "traffic": None, "algorithmic_bytes": bb, "ms": bwd_ms,
+                "traffic": traffic, "algorithmic_bytes": bb, "ms": bwd_ms,
                 "forward": {"achieved": fb / (fwd_ms * 1e-3) / 1e9, "frac": fb / (fwd_ms * 1e-3) / 1e9 / peak,
                             "algorithmic_bytes": fb, "ms": fwd_ms},
                 "fwd_bwd_frac": (fb + bb) / ((fwd_ms + bwd_ms) * 1e-3) / 1e9 / peak}
