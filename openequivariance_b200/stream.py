@@ -1,0 +1,211 @@
+"""Graph convolution on host-resident tensors, streamed through the GPU in edge slabs.
+
+The reference offers host-buffer entry points that copy everything to the device, launch, and
+copy everything back (reference: openequivariance/implementations/convolution/ConvolutionBase.py:
+111-170, ``forward_cpu`` / ``backward_cpu``).  For large graphs the per-edge arrays (weights and
+their gradient) dominate and the step is bound by the host link, so this module overlaps the three
+legs instead: while slab ``s`` is computed, slab ``s + 1`` travels to the device and the results of
+slab ``s - 1`` travel back (one copy engine per direction).
+
+A slab is a run of consecutive receiver-sorted edges cut at a receiver boundary, i.e. a receiver
+shard in time instead of in space: it owns the output rows of its receivers, reads ``X`` of any
+sender, and adds its part of ``dX`` to a running sum in slab order (so results are reproducible).
+Device memory holds ``X``, ``dX`` and two slabs, whatever the size of the graph.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+
+class Slab:
+    """Edges ``[e0, e1)``, receivers ``[r0, r1)`` and the slab's local index arrays."""
+
+    __slots__ = ("e0", "e1", "r0", "r1", "rows", "cols", "perm")
+
+    def __init__(self, e0, e1, r0, r1, rows, cols, perm):
+        self.e0, self.e1, self.r0, self.r1 = int(e0), int(e1), int(r0), int(r1)
+        self.rows, self.cols, self.perm = rows, cols, perm
+
+    @property
+    def edges(self):
+        return self.e1 - self.e0
+
+    @property
+    def receivers(self):
+        return self.r1 - self.r0
+
+
+def plan_slabs(rows, cols, nodes: int, slab_edges: int):
+    """Cut a receiver-sorted edge list into slabs of about ``slab_edges`` edges.
+
+    Cuts are moved forward to the next receiver boundary; the receiver ranges of the slabs
+    partition ``[0, nodes)`` (receivers without edges fall into the slab before the next edge).
+    ``rows`` of a slab are relative to its first receiver, ``cols`` stay global, ``perm[k]`` is
+    the slab-local position of the k-th edge in (sender, receiver) order.
+    """
+    rows = np.asarray(rows, dtype=np.int64)
+    cols = np.asarray(cols, dtype=np.int64)
+    if rows.shape != cols.shape or rows.ndim != 1:
+        raise ValueError("rows and cols must be 1-D and of equal length")
+    if rows.size and np.any(np.diff(rows) < 0):
+        raise ValueError("edges must be sorted by receiver")
+    if slab_edges < 1:
+        raise ValueError("slab_edges must be positive")
+    edges = rows.size
+    cuts = [0]
+    while cuts[-1] < edges:
+        t = cuts[-1] + slab_edges
+        if t >= edges:
+            cuts.append(edges)
+            break
+        # first edge at or after t whose receiver differs from the one before it
+        t = int(np.searchsorted(rows, rows[t - 1], side="right"))
+        cuts.append(min(t, edges))
+    if len(cuts) == 1:
+        cuts.append(0)           # no edges: one empty slab that owns every receiver
+    slabs = []
+    for s in range(len(cuts) - 1):
+        e0, e1 = cuts[s], cuts[s + 1]
+        r0 = 0 if s == 0 else int(rows[e0])
+        r1 = nodes if s == len(cuts) - 2 else int(rows[e1])
+        lr = rows[e0:e1] - r0
+        lc = cols[e0:e1]
+        perm = np.lexsort((lr, lc)).astype(np.int64)
+        slabs.append(Slab(e0, e1, r0, r1, np.ascontiguousarray(lr), np.ascontiguousarray(lc), perm))
+    return slabs
+
+
+def _host_slice(arr, index, lo, hi):
+    """``arr[lo:hi]`` of a host tensor, or ``arr(index, lo, hi)`` when the caller supplies slabs lazily
+    (for arrays that do not fit in host memory at once)."""
+    return arr(index, lo, hi) if callable(arr) else arr[lo:hi]
+
+
+class StreamedTensorProductConv:
+    """Deterministic fused convolution, forward + backward, on host tensors.
+
+    ``rows`` / ``cols``: receiver-sorted edge list (host arrays).  ``local_conv`` may replace the
+    CUDA convolution by an object with the same ``_forward_impl`` / ``_backward_impl`` (tests of
+    the host logic).
+    """
+
+    def __init__(self, problem, rows, cols, nodes: int, slab_edges: int = 1 << 18, device=None, local_conv=None):
+        self.problem = problem
+        self.nodes = int(nodes)
+        self.slabs = plan_slabs(rows, cols, nodes, slab_edges)
+        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        if local_conv is None:
+            from .conv import TensorProductConv
+            local_conv = TensorProductConv(problem, torch_op=True, deterministic=True)
+        self.conv = local_conv
+        self.on_gpu = self.device.type == "cuda"
+        pin = self.on_gpu
+        as_host = lambda a: (torch.from_numpy(a).pin_memory() if pin else torch.from_numpy(a))
+        self._idx_host = [[as_host(s.rows), as_host(s.cols), as_host(s.perm)] for s in self.slabs]
+        self.max_edges = max(s.edges for s in self.slabs)
+        self.max_receivers = max(s.receivers for s in self.slabs)
+        self._buffers = None
+        if self.on_gpu:
+            self._s_in = torch.cuda.Stream(self.device)
+            self._s_out = torch.cuda.Stream(self.device)
+
+    # bytes that cross the host link per step
+    def h2d_bytes(self, elem: int) -> int:
+        p = self.problem
+        edges = sum(s.edges for s in self.slabs)
+        return (self.nodes * (p.irreps_in1.dim + p.irreps_out.dim) * elem
+                + edges * ((p.irreps_in2.dim + p.weight_numel) * elem + 24))
+
+    def d2h_bytes(self, elem: int) -> int:
+        p = self.problem
+        edges = sum(s.edges for s in self.slabs)
+        return (self.nodes * (p.irreps_in1.dim + p.irreps_out.dim) * elem
+                + edges * (p.irreps_in2.dim + p.weight_numel) * elem)
+
+    def _alloc(self, dtype):
+        p = self.problem
+        dev = self.device
+        mk = lambda *shape, dt=dtype: torch.empty(shape, dtype=dt, device=dev)
+        self._buffers = {
+            "dtype": dtype,
+            "x": mk(self.nodes, p.irreps_in1.dim),
+            "y": [mk(self.max_edges, p.irreps_in2.dim) for _ in range(2)],
+            "w": [mk(self.max_edges, p.weight_numel) for _ in range(2)],
+            "dz": [mk(self.max_receivers, p.irreps_out.dim) for _ in range(2)],
+            "idx": [[mk(self.max_edges, dt=torch.int64) for _ in range(3)] for _ in range(2)],
+        }
+
+    def forward_backward_host(self, x_h, y_h, w_h, dz_h, z_h, dx_h, dy_h, dw_h):
+        """``Z, dX, dY, dW`` of the convolution and its backward pass for the output gradient ``dZ``.
+
+        Node arrays (``x_h``, ``dz_h``, ``z_h``, ``dx_h``) are host tensors; edge arrays (``y_h``, ``w_h``,
+        ``dy_h``, ``dw_h``) are host tensors or callables ``f(slab_index, e0, e1)`` returning the host
+        tensor of that edge range.  Pinned host memory makes the copies asynchronous.  Returns
+        after everything is enqueued; the results are complete once the current stream is."""
+        if not self.on_gpu:
+            return self._run_serial(x_h, y_h, w_h, dz_h, z_h, dx_h, dy_h, dw_h)
+        b = self._buffers
+        if b is None or b["dtype"] != x_h.dtype:
+            self._alloc(x_h.dtype)
+            b = self._buffers
+        cur = torch.cuda.current_stream(self.device)
+        s_in, s_out = self._s_in, self._s_out
+        s_in.wait_stream(cur)                      # earlier work may still read the buffers
+        s_out.wait_stream(cur)
+        with torch.cuda.stream(s_in):
+            b["x"].copy_(x_h, non_blocking=True)
+        done = [None, None]
+        dx_acc = None
+        for i, slab in enumerate(self.slabs):
+            k = i & 1
+            n, m = slab.edges, slab.receivers
+            y_d, w_d, dz_d = b["y"][k][:n], b["w"][k][:n], b["dz"][k][:m]
+            idx_d = [t[:n] for t in b["idx"][k]]
+            with torch.cuda.stream(s_in):
+                if done[k] is not None:
+                    s_in.wait_event(done[k])       # the slab that used this buffer set is computed
+                y_d.copy_(_host_slice(y_h, i, slab.e0, slab.e1), non_blocking=True)
+                w_d.copy_(_host_slice(w_h, i, slab.e0, slab.e1), non_blocking=True)
+                dz_d.copy_(dz_h[slab.r0:slab.r1], non_blocking=True)
+                for dst, src in zip(idx_d, self._idx_host[i]):
+                    dst.copy_(src, non_blocking=True)
+                arrived = s_in.record_event()
+            cur.wait_event(arrived)
+            z = self.conv._forward_impl(b["x"], y_d, w_d, idx_d[0], idx_d[1], idx_d[2], n_out=m)
+            dx, dy, dw = self.conv._backward_impl(b["x"], y_d, w_d, dz_d, idx_d[0], idx_d[1], idx_d[2])
+            if dx_acc is None:
+                dx_acc = dx
+            else:
+                dx_acc += dx                        # slab order is fixed: reproducible
+            done[k] = cur.record_event()
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done[k])
+                z_h[slab.r0:slab.r1].copy_(z, non_blocking=True)
+                _host_slice(dy_h, i, slab.e0, slab.e1).copy_(dy, non_blocking=True)
+                _host_slice(dw_h, i, slab.e0, slab.e1).copy_(dw, non_blocking=True)
+                for t in (z, dy, dw):
+                    t.record_stream(s_out)
+        with torch.cuda.stream(s_out):
+            s_out.wait_stream(cur)
+            dx_h.copy_(dx_acc, non_blocking=True)
+            dx_acc.record_stream(s_out)
+        cur.wait_stream(s_out)
+        cur.wait_stream(s_in)
+
+    def _run_serial(self, x_h, y_h, w_h, dz_h, z_h, dx_h, dy_h, dw_h):
+        """The same slab sequence without streams (host-logic tests with a stand-in convolution)."""
+        dx_acc = None
+        for i, slab in enumerate(self.slabs):
+            rows, cols, perm = self._idx_host[i]
+            y = _host_slice(y_h, i, slab.e0, slab.e1)
+            w = _host_slice(w_h, i, slab.e0, slab.e1)
+            dz = dz_h[slab.r0:slab.r1]
+            z = self.conv._forward_impl(x_h, y, w, rows, cols, perm, n_out=slab.receivers)
+            dx, dy, dw = self.conv._backward_impl(x_h, y, w, dz, rows, cols, perm)
+            dx_acc = dx if dx_acc is None else dx_acc + dx
+            z_h[slab.r0:slab.r1].copy_(z)
+            _host_slice(dy_h, i, slab.e0, slab.e1).copy_(dy)
+            _host_slice(dw_h, i, slab.e0, slab.e1).copy_(dw)
+        dx_h.copy_(dx_acc)

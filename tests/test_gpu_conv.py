@@ -150,3 +150,30 @@ def test_readme_call_sequence():
     ref = orc.conv_forward(p, X.cpu().numpy(), Y.cpu().numpy(), W.cpu().numpy(), rows.cpu().numpy(),
                            cols.cpu().numpy())
     assert rel_err(Z.cpu().numpy(), ref) < 1e-5 and rel_err(Z2.cpu().numpy(), ref) < 1e-5
+
+
+@pytest.mark.parametrize("name,slab_edges", [("nequip_32", 64), ("mace_128", 500), ("cw_mixed", 10_000)])
+def test_streamed_host_tensors(name, slab_edges):
+    """Slab streaming over pinned host tensors: same Z, dY, dW as the resident deterministic
+    convolution bit for bit (same kernels, same order), dX up to the slab-wise summation order."""
+    from openequivariance_b200.stream import StreamedTensorProductConv
+    p = problem_by_name(name)
+    nodes = 120
+    rows, cols = random_graph(nodes, 1500, seed=12)
+    conv, (xt, yt, wt, dzt, index), (z, dx, dy, dw) = check_conv(p, nodes, rows, cols, 13, True)
+    rows_s, cols_s = index[0].cpu().numpy(), index[1].cpu().numpy()
+    streamed = StreamedTensorProductConv(p, rows_s, cols_s, nodes, slab_edges=slab_edges)
+    pin = lambda t: torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t)
+    x_h, y_h, w_h, dz_h = pin(xt), pin(yt), pin(wt), pin(dzt)
+    out = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True) for t in (z, dx, dy, dw)]
+    for _ in range(2):           # the second pass re-uses the device buffers
+        for t in out:
+            t.fill_(float("nan"))
+        streamed.forward_backward_host(x_h, y_h, w_h, dz_h, *out)
+        torch.cuda.synchronize()
+        conv.check_device_status()
+        streamed.conv.check_device_status()
+        assert torch.equal(out[0], z.cpu()) and torch.equal(out[2], dy.cpu()) and torch.equal(out[3], dw.cpu())
+        assert rel_err(out[1].numpy(), dx.cpu().numpy()) < REL_TOL[np.float32]
+    if slab_edges < 1500:
+        assert len(streamed.slabs) > 2
