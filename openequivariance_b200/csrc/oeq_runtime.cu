@@ -206,6 +206,7 @@ int pad16(int b) { return (b + 15) / 16 * 16; }
 struct Mapping {
     int mulg = 32, nch = 1, ps = 1, ng = 1, producer = 0, min_ctas = 1;
     int nph = 1;                              // backward staging in phases (see uvu_kernels.cuh)
+    bool tc_tables = false;                   // emit the tables of the tensor-core forward pass
     std::vector<int> z_ph_begin, w_ph_begin;  // nph + 1 column / weight boundaries
     std::vector<int> phase_of_instr;
     std::vector<int> part_of_out, part_of_instr, zr_off, xr_off;
@@ -444,6 +445,113 @@ int choose_uvw(const Problem& p, bool bwd, UvwConfig& c) {
     return fail(OEQ_ERR_UNSUPPORTED, "'uvw' problem rows do not fit in shared memory");
 }
 
+// ---- tensor-core forward pass of the 'uvu' convolution (mirrors the constexpr geometry of uvu_tc_kernels.cuh)
+// Entry e of the per-edge matrix M[(p,k)][i] = sum_j c^p_ijk y_j: where it lives in the swizzled B tile and
+// which (j, coefficient) terms it sums (dense [entry][tmax] table, coefficient 0 where an entry has fewer).
+struct UvuTcTables {
+    int n = 0, tmax = 1;
+    std::vector<int> off, term_j;
+    std::vector<double> term_c;
+    int xpc = 0;
+};
+
+// Columns of the per-edge product: the paths of consumer partition q (the partition of their output
+// irrep) are contiguous, in instruction order, and start at a multiple of 16.
+struct UvuTcColumns {
+    std::vector<int> col_begin;   // per instruction
+    std::vector<int> part_col;    // per partition, plus the padded total
+};
+
+UvuTcColumns uvu_tc_columns(const Problem& p, const std::vector<int>& part_of_out, int parts) {
+    UvuTcColumns c;
+    c.col_begin.assign(p.instr.size(), 0);
+    int cur = 0;
+    for (int q = 0; q < parts; ++q) {
+        cur = (cur + 15) / 16 * 16;
+        c.part_col.push_back(cur);
+        for (size_t i = 0; i < p.instr.size(); ++i)
+            if (part_of_out[p.instr[i].io] == q) {
+                c.col_begin[i] = cur;
+                cur += p.out[p.instr[i].io].dim;
+            }
+    }
+    c.part_col.push_back((cur + 15) / 16 * 16);
+    return c;
+}
+
+int tc_swizzle_host(int row, int col) {
+    return (row >> 3) * 1024 + (row & 7) * 128 + ((((col >> 2) ^ (row & 7)) & 7) << 4) + ((col & 3) << 2);
+}
+
+UvuTcTables build_uvu_tc_tables(const Problem& p, const UvuTcColumns& cols) {
+    UvuTcTables t;
+    std::vector<int> xoff(p.in1.size(), 0);
+    for (size_t a = 0; a < p.in1.size(); ++a) {
+        xoff[a] = t.xpc;
+        t.xpc += p.in1[a].dim;
+    }
+    std::vector<std::vector<std::pair<int, double>>> terms;
+    for (size_t pi = 0; pi < p.instr.size(); ++pi) {
+        const Instr& ins = p.instr[pi];
+        const int col0 = cols.col_begin[pi];
+        const int d1 = p.in1[ins.i1].dim, d3 = p.out[ins.io].dim;
+        for (int k = 0; k < d3; ++k)
+            for (int i = 0; i < d1; ++i) {
+                std::vector<std::pair<int, double>> tt;
+                for (size_t z = 0; z < ins.ci.size(); ++z)
+                    if (ins.ci[z] == i && ins.ck[z] == k) tt.push_back({p.in2[ins.i2].off + ins.cj[z], ins.cv[z]});
+                if (tt.empty()) continue;
+                t.off.push_back(tc_swizzle_host(col0 + k, xoff[ins.i1] + i));
+                t.tmax = std::max(t.tmax, (int)tt.size());
+                terms.push_back(std::move(tt));
+            }
+    }
+    t.n = (int)t.off.size();
+    t.term_j.assign((size_t)std::max(1, t.n) * t.tmax, 0);
+    t.term_c.assign((size_t)std::max(1, t.n) * t.tmax, 0.0);
+    for (int e = 0; e < t.n; ++e)
+        for (size_t z = 0; z < terms[e].size(); ++z) {
+            t.term_j[(size_t)e * t.tmax + z] = terms[e][z].first;
+            t.term_c[(size_t)e * t.tmax + z] = terms[e][z].second;
+        }
+    if (t.off.empty()) t.off.push_back(0);
+    return t;
+}
+
+struct UvuTcGeometry {
+    int stages = 0, smem = 0;
+};
+
+// Problems the tensor-core forward pass takes: FP32 'uvu' with per-edge weights, second input of
+// multiplicity 1 and at most 32 components, widest multiplicity 65..128 (thread = channel, M = 128 rows),
+// at most 32 first-input components per channel (one swizzled 128-byte row) and 256 output columns.
+bool uvu_tc_geometry(const Problem& p, UvuTcGeometry& g, int npad = 0) {
+    if (p.mode != OEQ_MODE_UVU || p.shared || p.dtype != OEQ_F32) return false;
+    // Opt-in: measured on B200 the per-edge hand-offs between the roles make this kernel about twice as slow
+    // as the FMA kernel (MACE-large, 1.5 M edges: 14.0 ms against 7.2 ms), so the FMA kernel is the default.
+    if (!env_int("OEQ_B200_UVU_TC", 0)) return false;
+    if (p.y_dim > 32) return false;
+    int maxmul = 0, xpc = 0, ncols = 0;
+    for (const Irrep& r : p.in1) {
+        maxmul = std::max(maxmul, r.mul);
+        xpc += r.dim;
+    }
+    for (const Instr& t : p.instr) {
+        if (p.in2[t.i2].mul != 1) return false;
+        ncols += p.out[t.io].dim;
+    }
+    if (maxmul <= 64 || maxmul > 128 || xpc > 32 || ncols > 224 || ncols == 0) return false;
+    if ((p.x_dim * 4) % 16 || (p.w_numel * 4) % 16) return false;
+    if (npad == 0) npad = (ncols + 15) / 16 * 16 + 16;      // upper bound: one padding gap between two partitions
+    if (npad > 256) return false;
+    const int off_stage = 2 * 2 * 128 * 128 + 2 * 2 * npad * 128 + 512;
+    const int stage = pad16(p.x_dim * 4) + pad16(p.w_numel * 4) + pad16(p.y_dim * 4);
+    g.stages = std::min(4, (SMEM_LIMIT - 1024 - off_stage) / stage);
+    if (g.stages < 3) return false;
+    g.smem = 1024 + off_stage + g.stages * stage;
+    return true;
+}
+
 std::string descriptor_text(const Problem& p, const Mapping& m, const UvwConfig* uvw = nullptr) {
     std::ostringstream s;
     s.precision(17);
@@ -518,6 +626,27 @@ std::string descriptor_text(const Problem& p, const Mapping& m, const UvwConfig*
         s << "};\n";
     }
     s << "constexpr int ZPC_MAX = " << m.zpc_max << ", XPC = " << m.xpc << ";\n";
+    if (m.tc_tables) {
+        const UvuTcColumns cols = uvu_tc_columns(p, m.part_of_out, m.ps);
+        const UvuTcTables t = build_uvu_tc_tables(p, cols);
+        emit_array(s, "int", "TC_COL_BEGIN", cols.col_begin, put_int);
+        emit_array(s, "int", "TC_PART_COL", cols.part_col, put_int);
+        s << "constexpr int TCM_N = " << t.n << ", TCM_TMAX = " << t.tmax << ";\n";
+        auto dev_ints = [&](const char* name, const std::vector<int>& v) {
+            s << "__device__ const int " << name << "[] = {";
+            for (size_t i = 0; i < v.size(); ++i) s << (i ? ", " : "") << v[i];
+            s << "};\n";
+        };
+        dev_ints("TCM_OFF_DEV", t.off);
+        dev_ints("TCM_J_DEV", t.term_j);
+        s << "__device__ const float TCM_C_DEV[] = {";
+        for (size_t i = 0; i < t.term_c.size(); ++i) {
+            char buf[64];
+            snprintf(buf, sizeof buf, "%af", (double)(float)t.term_c[i]);
+            s << (i ? ", " : "") << buf;
+        }
+        s << "};\n";
+    }
     if (uvw)
         s << "constexpr int TILE_R = " << uvw->tile_r << ", UVC = " << uvw->uvc << ", DMAX = " << uvw->dmax
           << ", MWMAX = " << uvw->mwmax << ", UVW_THREADS = " << uvw->threads << ";\n";
@@ -555,6 +684,10 @@ int compile_kernel(const std::string& descriptor, const std::string& main_header
     std::string common, body;
     if (!read_file(dir + "/oeq_common.cuh", common) || !read_file(dir + "/" + main_header, body))
         return fail(OEQ_ERR_COMPILE, "kernel headers not found in " + dir);
+    for (const char* inc : {"tc_common.cuh", "uvu_kernels.cuh"}) {   // headers that the kernel files include
+        std::string text;
+        if (main_header != inc && read_file(dir + "/" + inc, text)) common += text;
+    }
     const std::string source = descriptor + "#define OEQ_KERNEL " + std::to_string(kernel_id) + "\n#include \"" +
                                main_header + "\"\n";
     const std::string options = "-arch=sm_100a -std=c++17 -lineinfo -default-device -diag-suppress 177";
@@ -618,12 +751,37 @@ struct Kernel {
     cudaLibrary_t lib = nullptr;
     cudaKernel_t fn = nullptr, reduce_fn = nullptr;
     int stages = 0, smem = 0, regs = 0, ctas_per_sm = 1, sm_count = 0;
+    bool is_uvu_tc = false;       // tensor-core forward of the convolution: one CTA per SM
+    UvuTcGeometry tc_geo;
+    int threads() const { return is_uvu_tc ? 128 * map.ps + 64 : map.threads(); }
 };
 
 int build_uvu(const Problem& p, int kind, Kernel& k) {
     int rc = choose_mapping(p, kind, k.map);
     if (rc) return rc;
     rc = compile_kernel(descriptor_text(p, k.map), "uvu_kernels.cuh", kind, k.code);
+    if (rc) return rc;
+    k.compiled = true;
+    return OEQ_OK;
+}
+
+constexpr int K_FWD_DET_TC = 30, K_FWD_ATOMIC_TC = 31;
+
+int build_uvu_tc(const Problem& p, bool deterministic, Kernel& k) {
+    if (!uvu_tc_geometry(p, k.tc_geo)) return fail(OEQ_ERR_UNSUPPORTED, "problem does not qualify for the tensor-core forward pass");
+    Mapping& m = k.map;
+    m.mulg = 128; m.nch = 1; m.ng = 1; m.producer = 1; m.min_ctas = 1;
+    m.ps = std::max(1, std::min({2, (int)p.out.size(), env_int("OEQ_B200_TC_PARTS", 2)}));
+    m.z_ph_begin = {0, p.z_dim};
+    m.w_ph_begin = {0, p.w_numel};
+    m.phase_of_instr.assign(p.instr.size(), 0);
+    m.tc_tables = true;
+    assign_partitions(p, false, m);
+    const UvuTcColumns cols = uvu_tc_columns(p, m.part_of_out, m.ps);
+    if (!uvu_tc_geometry(p, k.tc_geo, cols.part_col.back()))
+        return fail(OEQ_ERR_UNSUPPORTED, "problem does not fit the tensor-core forward pass");
+    k.is_uvu_tc = true;
+    int rc = compile_kernel(descriptor_text(p, m), "uvu_tc_kernels.cuh", deterministic ? K_FWD_DET_TC : K_FWD_ATOMIC_TC, k.code);
     if (rc) return rc;
     k.compiled = true;
     return OEQ_OK;
@@ -749,19 +907,21 @@ int load_kernel(Kernel& k, const char* entry, bool want_reduce) {
     OEQ_CUDA(cudaGetDevice(&dev));
     OEQ_CUDA(cudaDeviceGetAttribute(&k.sm_count, cudaDevAttrMultiProcessorCount, dev));
     int stages = std::min(k.map.max_stages(), env_int("OEQ_B200_STAGES", 4));
+    if (k.is_uvu_tc) stages = k.tc_geo.stages;
     if (stages < 2) return fail(OEQ_ERR_UNSUPPORTED, "not enough shared memory for two stages");
     k.stages = stages;
-    k.smem = k.map.smem(stages);
+    k.smem = k.is_uvu_tc ? k.tc_geo.smem : k.map.smem(stages);
     OEQ_CUDA(cudaFuncSetAttribute((const void*)k.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, k.smem));
     cudaFuncAttributes attr;
     if (cudaFuncGetAttributes(&attr, (const void*)k.fn) == cudaSuccess) k.regs = attr.numRegs;
     else (void)cudaGetLastError();
     int occ = 1;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, (const void*)k.fn, k.map.threads(), k.smem) != cudaSuccess) {
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, (const void*)k.fn, k.threads(), k.smem) != cudaSuccess) {
         (void)cudaGetLastError();
         occ = 1;
     }
     k.ctas_per_sm = std::max(1, std::min(occ, env_int("OEQ_B200_CTAS_PER_SM", 4)));
+    if (k.is_uvu_tc) k.ctas_per_sm = 1;
     k.loaded = true;
     return OEQ_OK;
 }
@@ -794,7 +954,7 @@ int launch_uvu(Kernel& k, const Problem& p, UvuParams& prm, cudaStream_t stream)
     long long want = (prm.n_items + k.map.ng - 1) / k.map.ng;
     long long grid = std::max<long long>(1, std::min<long long>((long long)k.sm_count * k.ctas_per_sm, want));
     void* args[] = {&prm};
-    OEQ_CUDA(cudaLaunchKernel((const void*)k.fn, dim3((unsigned)grid), dim3((unsigned)k.map.threads()), args,
+    OEQ_CUDA(cudaLaunchKernel((const void*)k.fn, dim3((unsigned)grid), dim3((unsigned)k.threads()), args,
                               (size_t)k.smem, stream));
     return OEQ_OK;
 }
@@ -823,6 +983,8 @@ struct oeq_conv {
     Problem prob;
     bool deterministic = false;
     Kernel fwd, bwd;
+    Kernel fwd_tc;              // tensor-core forward pass, when the problem qualifies
+    bool has_fwd_tc = false;
     int* d_status = nullptr;
     cudaStream_t last_stream = nullptr;
 };
@@ -873,11 +1035,17 @@ int oeq_precompile(const oeq_problem_desc* desc, int kinds) {
     if (kinds & 6) {
         if ((rc = check_conv_problem(p))) return rc;
     }
+    UvuTcGeometry geo;
+    const bool tc = (kinds & 6) && uvu_tc_geometry(p, geo);
     if (kinds & 2) {
         if ((rc = one(K_FWD_DET)) || (rc = one(K_BWD_DET))) return rc;
+        Kernel k;
+        if (tc && (rc = build_uvu_tc(p, true, k))) return rc;
     }
     if (kinds & 4) {
         if ((rc = one(K_FWD_ATOMIC)) || (rc = one(K_BWD_ATOMIC))) return rc;
+        Kernel k;
+        if (tc && (rc = build_uvu_tc(p, false, k))) return rc;
     }
     return OEQ_OK;
 }
@@ -1064,7 +1232,7 @@ static int check_status(int* d_status, cudaStream_t st) {
 int oeq_tp_check(oeq_tp* h) { return h ? check_status(h->d_status, h->last_stream) : fail(OEQ_ERR_INVALID, "null handle"); }
 
 static int launch_info(const Kernel& k, int* threads, int* ng, int* ps, int* stages, int* smem, int* regs) {
-    if (threads) *threads = k.is_uvw ? k.uvw.threads : k.map.threads();
+    if (threads) *threads = k.is_uvw ? k.uvw.threads : k.threads();
     if (ng) *ng = k.map.ng;
     if (ps) *ps = k.map.ps;
     if (stages) *stages = k.stages;
@@ -1178,6 +1346,11 @@ int oeq_conv_create(const oeq_problem_desc* desc, int deterministic, oeq_conv** 
     if (!rc) rc = check_conv_problem(h->prob);
     if (!rc) rc = build_uvu(h->prob, deterministic ? K_FWD_DET : K_FWD_ATOMIC, h->fwd);
     if (!rc) rc = build_uvu(h->prob, deterministic ? K_BWD_DET : K_BWD_ATOMIC, h->bwd);
+    UvuTcGeometry geo;
+    if (!rc && uvu_tc_geometry(h->prob, geo)) {
+        rc = build_uvu_tc(h->prob, h->deterministic, h->fwd_tc);
+        h->has_fwd_tc = !rc;
+    }
     if (rc) {
         delete h;
         return rc;
@@ -1191,6 +1364,7 @@ int oeq_conv_destroy(oeq_conv* h) {
     if (h->d_status) cudaFree(h->d_status);
     if (h->fwd.lib) cudaLibraryUnload(h->fwd.lib);
     if (h->bwd.lib) cudaLibraryUnload(h->bwd.lib);
+    if (h->fwd_tc.lib) cudaLibraryUnload(h->fwd_tc.lib);
     delete h;
     return OEQ_OK;
 }
@@ -1214,15 +1388,35 @@ int oeq_conv_forward(oeq_conv* h, int64_t nodes, int64_t edges, const void* X, c
         OEQ_CUDA(cudaMemsetAsync(Z, 0, (size_t)nodes * p.z_dim * p.elem(), st));
     if (edges == 0) return OEQ_OK;
     if (!X || !Y || !W || !rows || !cols) return fail(OEQ_ERR_INVALID, "null buffer");
+    // the tensor-core kernel stages rows with bulk copies only: it needs 16-byte aligned X and W
+    const bool tc = h->has_fwd_tc && aligned16(X) && aligned16(W) && !env_int("OEQ_B200_NO_BULK", 0);
     int rc = ensure_status(&h->d_status);
-    if (!rc) rc = load_kernel(h->fwd, "oeq_uvu_kernel", false);
+    if (!rc) rc = tc ? load_kernel(h->fwd_tc, "oeq_uvu_tc_kernel", false) : load_kernel(h->fwd, "oeq_uvu_kernel", false);
     if (rc) return rc;
     UvuParams prm{};
     prm.X = X; prm.Y = Y; prm.W = W; prm.Z = Z;
     prm.rows = (const long long*)rows; prm.cols = (const long long*)cols;
     prm.n_items = edges; prm.n_nodes = nodes; prm.status = h->d_status;
     h->last_stream = st;
-    return launch_uvu(h->fwd, p, prm, st);
+    if (tc && env_int("OEQ_B200_TC_PROFILE", 0)) {
+        // cycle accounting of the roles of CTA 0 (development aid): synchronous, prints to stderr
+        unsigned long long* d = nullptr;
+        OEQ_CUDA(cudaMalloc(&d, 64 * 8));
+        OEQ_CUDA(cudaMemsetAsync(d, 0, 64 * 8, st));
+        prm.ws = d;
+        rc = launch_uvu(h->fwd_tc, p, prm, st);
+        unsigned long long hbuf[64];
+        OEQ_CUDA(cudaMemcpyAsync(hbuf, d, sizeof hbuf, cudaMemcpyDeviceToHost, st));
+        OEQ_CUDA(cudaStreamSynchronize(st));
+        cudaFree(d);
+        const char* names[] = {"consumer0", "consumer1", "mma", "-", "stager"};
+        for (int r = 0; r < 5; ++r)
+            fprintf(stderr, "[oeq_b200 tc profile] %-9s total %llu  s1 %llu  s2 %llu  s3 %llu  s4 %llu  s5 %llu  s6 %llu  s7 %llu\n",
+                    names[r], hbuf[8 * r], hbuf[8 * r + 1], hbuf[8 * r + 2], hbuf[8 * r + 3], hbuf[8 * r + 4], hbuf[8 * r + 5],
+                    hbuf[8 * r + 6], hbuf[8 * r + 7]);
+        return rc;
+    }
+    return launch_uvu(tc ? h->fwd_tc : h->fwd, p, prm, st);
 }
 
 int oeq_conv_backward(oeq_conv* h, int64_t nodes, int64_t edges, const void* X, const void* Y, const void* W,
@@ -1256,7 +1450,7 @@ int oeq_conv_check(oeq_conv* h) { return h ? check_status(h->d_status, h->last_s
 
 int oeq_conv_launch_info(const oeq_conv* h, int which, int* threads, int* ng, int* ps, int* stages, int* smem, int* regs) {
     if (!h) return fail(OEQ_ERR_INVALID, "null handle");
-    return launch_info(which ? h->bwd : h->fwd, threads, ng, ps, stages, smem, regs);
+    return launch_info(which ? h->bwd : (h->has_fwd_tc && h->fwd_tc.loaded ? h->fwd_tc : h->fwd), threads, ng, ps, stages, smem, regs);
 }
 
 }  // extern "C"

@@ -1133,7 +1133,9 @@ __device__ __forceinline__ void uvu_body(const UvuParams& p) {
 
 }  // namespace oeq
 
-// One entry point per translation unit, selected by OEQ_KERNEL.
+// One entry point per translation unit, selected by OEQ_KERNEL (other kernel files include this
+// header for its building blocks and define OEQ_UVU_NO_ENTRY).
+#ifndef OEQ_UVU_NO_ENTRY
 #define OEQ_K_FWD_BATCH 0
 #define OEQ_K_BWD_BATCH 1
 #define OEQ_K_FWD_DET 2
@@ -1168,3 +1170,4 @@ extern "C" __global__ void oeq_reduce_partials(const oeqd::T* ws, oeqd::T* out, 
     for (long long g = 0; g < groups; ++g) s += ws[g * n + i];
     out[i] = s;
 }
+#endif  // OEQ_UVU_NO_ENTRY

@@ -8,7 +8,7 @@
 // parts, pre-swizzled by oeq_uvw_pack_weights) resident in shared memory and walks its share of the
 // batch in chunks of floor(128 / (2l+1)) rows:
 //
-//   * 8 producer warps form T with the Clebsch-Gordan constants unrolled, split every value into
+//   * 16 producer warps form T with the Clebsch-Gordan constants unrolled, split every value into
 //     hi = tf32(t), lo = tf32(t - hi), and store both as K-major 128-byte-swizzled [128 x 32] tiles;
 //   * one thread issues tcgen05.mma (M = 128, N = mul_out, K = 8 per instruction) three times per K step
 //     (hi.hi + hi.lo + lo.hi) into a ring of TMEM accumulator tiles, and hands shared-memory stages
@@ -21,6 +21,7 @@
 // records a code in *status and stops, and the CTA still frees its tensor memory.
 #pragma once
 #include "oeq_common.cuh"
+#include "tc_common.cuh"
 
 namespace oeq {
 using namespace oeqd;
@@ -79,46 +80,6 @@ constexpr int TC_OFF_STG = TC_OFF_W + (TC_W_MAX + 1023) / 1024 * 1024;
 constexpr int TC_OFF_BAR = TC_OFF_STG + (128 * TC_STG_PITCH * 4 + 15) / 16 * 16;
 constexpr int TC_MAX_ACC = 32;
 constexpr int TC_SMEM_BYTES = TC_OFF_BAR + (2 * TC_NA + 2 * TC_MAX_ACC + 2) * 8 + 16 + 1024;   // + alignment slack
-
-// byte offset of element (row, col) inside a [rows x 32 tf32] K-major tile with the 128-byte swizzle
-__host__ __device__ __forceinline__ int tc_swizzle(int row, int col) {
-    return (row >> 3) * 1024 + (row & 7) * 128 + ((((col >> 2) ^ (row & 7)) & 7) << 4) + ((col & 3) << 2);
-}
-
-__device__ __forceinline__ float tf32_round(float x) {
-    unsigned r;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-    return __uint_as_float(r);
-}
-
-// shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart
-__device__ __forceinline__ unsigned long long tc_smem_desc(unsigned smem_addr) {
-    unsigned long long d = 0;
-    d |= (unsigned long long)((smem_addr >> 4) & 0x3fff);        // start address
-    d |= (unsigned long long)1 << 16;                             // leading byte offset (16 B units)
-    d |= (unsigned long long)(1024 >> 4) << 32;                   // stride byte offset
-    d |= (unsigned long long)1 << 46;                             // descriptor version
-    d |= (unsigned long long)2 << 61;                             // SWIZZLE_128B
-    return d;
-}
-// instruction descriptor: TF32 x TF32 -> F32, both operands K-major, M = 128, N = n
-__host__ __device__ constexpr unsigned tc_instr_desc(int n) {
-    return (1u << 4) | (2u << 7) | (2u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(128 >> 4) << 24);
-}
-__device__ __forceinline__ void tc_mma(unsigned tmem_d, unsigned long long a, unsigned long long b, unsigned idesc,
-                                       unsigned accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-        ::"r"(tmem_d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate), "r"(0u)
-        : "memory");
-}
-__device__ __forceinline__ void tc_commit(unsigned long long* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-                 : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
 struct TcBars {
     unsigned long long* a_full;     // [TC_NA]
@@ -197,9 +158,9 @@ __device__ __forceinline__ bool tc_produce_output(const UvwTcParams& p, unsigned
 #pragma unroll
                                 for (int k = 0; k < D3; ++k) {
                                     const int off = tc_swizzle(r * D3 + k, lane);
-                                    const float th = tf32_round(t[k]);
+                                    const float th = tf32_hi(t[k]);
                                     *reinterpret_cast<float*>(hi + off) = th;
-                                    *reinterpret_cast<float*>(lo + off) = tf32_round(t[k] - th);
+                                    *reinterpret_cast<float*>(lo + off) = t[k] - th;   // exact; read as TF32 by the MMA
                                 }
                             }
                         }

@@ -177,3 +177,23 @@ def test_streamed_host_tensors(name, slab_edges):
         assert rel_err(out[1].numpy(), dx.cpu().numpy()) < REL_TOL[np.float32]
     if slab_edges < 1500:
         assert len(streamed.slabs) > 2
+
+
+@pytest.mark.parametrize("deterministic", [False, True], ids=["atomic", "deterministic"])
+@pytest.mark.parametrize("name", ["mace_128", "mace_large_128"])
+def test_tensor_core_forward(name, deterministic, monkeypatch):
+    """The opt-in tcgen05 forward pass (3xTF32) against the oracle, and against the FMA kernel's launch shape."""
+    monkeypatch.setenv("OEQ_B200_UVU_TC", "1")
+    p = problem_by_name(name)
+    nodes = 61
+    rows, cols = random_graph(nodes, 900, seed=21)
+    conv, _, _ = check_conv(p, nodes, rows, cols, 22, deterministic)
+    info = conv.internal.launch_info(0)
+    assert info["threads"] == 320 and info["partitions"] == 2      # 8 consumer warps, staging warp, MMA warp
+    if deterministic:                                               # bit-reproducible run to run
+        rows_s, cols_s, order, perm = orc.coord_graph(rows, cols)
+        x, y, w, _ = conv_inputs(p, nodes, len(rows), 22)
+        args = cuda(x, y[order], w[order], rows_s, cols_s, perm)
+        first = conv.forward(*args)
+        for _ in range(3):
+            assert torch.equal(conv.forward(*args), first)
