@@ -1122,9 +1122,23 @@ int oeq_tp_forward(oeq_tp* h, int64_t batch, const void* X, const void* Y, const
             void* args[] = {(void*)&W, &packed};
             OEQ_CUDA(cudaLaunchKernel((const void*)h->pack_fn, dim3(64), dim3(256), args, 0, st));
         }
-        struct { const void* X; const void* Y; const void* Wp; void* Z; long long batch; int* status; } tp{X, Y, h->d_packed, Z, batch, h->d_status};
+        struct { const void* X; const void* Y; const void* Wp; void* Z; long long batch; int* status; unsigned long long* prof; }
+            tp{X, Y, h->d_packed, Z, batch, h->d_status, nullptr};
         void* args[] = {&tp};
         const long long grid = std::max<long long>(1, std::min<long long>(k.sm_count, (batch + 23) / 24));
+        if (env_int("OEQ_B200_TC_PROFILE", 0)) {
+            // cycle accounting of the roles of CTA 0 (development aid): synchronous, prints to stderr
+            OEQ_CUDA(cudaMalloc(&tp.prof, 32 * 8));
+            OEQ_CUDA(cudaMemsetAsync(tp.prof, 0, 32 * 8, st));
+            OEQ_CUDA(cudaLaunchKernel((const void*)k.fn, dim3((unsigned)grid), dim3(21 * 32), args, (size_t)k.smem, st));
+            unsigned long long hb[32];
+            OEQ_CUDA(cudaMemcpyAsync(hb, tp.prof, sizeof hb, cudaMemcpyDeviceToHost, st));
+            OEQ_CUDA(cudaStreamSynchronize(st));
+            cudaFree(tp.prof);
+            fprintf(stderr, "[oeq_b200 uvw tc profile] producer: stages %llu wait %llu fill %llu | mma: wait %llu issue %llu | "
+                            "epilogue: tiles %llu wait %llu drain %llu\n", hb[2], hb[0], hb[1], hb[8], hb[9], hb[18], hb[16], hb[17]);
+            return OEQ_OK;
+        }
         OEQ_CUDA(cudaLaunchKernel((const void*)k.fn, dim3((unsigned)grid), dim3(21 * 32), args, (size_t)k.smem, st));
         return OEQ_OK;
     }

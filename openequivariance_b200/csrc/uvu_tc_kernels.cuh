@@ -184,6 +184,8 @@ __device__ void utc_stager(const UvuParams& p, unsigned char* smem, const UtcCtr
 // ---------------------------------------------------------------------------- MMA issuer (one thread)
 __device__ void utc_mma(const UvuParams& p, unsigned char* smem, const UtcCtrl& c, unsigned tmem_base) {
     constexpr unsigned IDESC = tc_instr_desc(UTC_NPAD);
+    const unsigned long long a_desc0 = tc_smem_desc(smem_u32(smem + UTC_OFF_A));
+    const unsigned long long b_desc0 = tc_smem_desc(smem_u32(smem + UTC_OFF_B));
     UtcProf prof(p, 16, true);
     const long long t_begin = clock64();
     for (long long n = 0;; ++n) {
@@ -199,18 +201,15 @@ __device__ void utc_mma(const UvuParams& p, unsigned char* smem, const UtcCtrl& 
         if (!df) break;
         prof.start();
         tc_fence_after();
-        const unsigned a_hi = smem_u32(smem + UTC_OFF_A + b * UTC_A_BYTES), a_lo = a_hi + UTC_A_HALF;
-        const unsigned b_hi = smem_u32(smem + UTC_OFF_B + b * UTC_B_BYTES), b_lo = b_hi + UTC_B_HALF;
+        // descriptors differ from the base ones only in the start-address field (16-byte units)
+        const unsigned long long da_hi = a_desc0 + (unsigned long long)((b * UTC_A_BYTES) >> 4), da_lo = da_hi + (UTC_A_HALF >> 4);
+        const unsigned long long db_hi = b_desc0 + (unsigned long long)((b * UTC_B_BYTES) >> 4), db_lo = db_hi + (UTC_B_HALF >> 4);
         const unsigned tmem_d = tmem_base + (unsigned)(b * UTC_DCOLS);
-        unsigned accumulate = 0;
 #pragma unroll
         for (int kk = 0; kk < UTC_KSTEPS; ++kk) {
-            const unsigned long long da_hi = tc_smem_desc(a_hi + kk * 32), da_lo = tc_smem_desc(a_lo + kk * 32);
-            const unsigned long long db_hi = tc_smem_desc(b_hi + kk * 32), db_lo = tc_smem_desc(b_lo + kk * 32);
-            tc_mma(tmem_d, da_hi, db_hi, IDESC, accumulate);
-            accumulate = 1;
-            tc_mma(tmem_d, da_hi, db_lo, IDESC, 1);
-            tc_mma(tmem_d, da_lo, db_hi, IDESC, 1);
+            tc_mma(tmem_d, da_hi + 2 * kk, db_hi + 2 * kk, IDESC, kk == 0 ? 0u : 1u);
+            tc_mma(tmem_d, da_hi + 2 * kk, db_lo + 2 * kk, IDESC, 1);
+            tc_mma(tmem_d, da_lo + 2 * kk, db_hi + 2 * kk, IDESC, 1);
         }
         tc_commit(c.d_ready + b);
         prof.stop(4);

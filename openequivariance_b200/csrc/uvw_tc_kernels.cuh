@@ -33,6 +33,7 @@ struct UvwTcParams {
     float* Z;
     long long batch;
     int* status;
+    unsigned long long* prof;   // optional cycle accounting of CTA 0 (development aid), else null
 };
 
 constexpr int TC_PRODUCER_WARPS = 16;
@@ -137,7 +138,10 @@ __device__ __forceinline__ bool tc_produce_output(const UvwTcParams& p, unsigned
 #pragma unroll
                         for (int j = 0; j < D2; ++j) ys[q][j] = live ? __ldg(yrow + j) : 0.f;
                     }
+                    const bool prof = p.prof && blockIdx.x == 0 && warp == 0 && lane == 0;
+                    const long long t0 = prof ? clock64() : 0;
                     if (use > 0) ok = mbar_wait(bars.a_empty + s, (unsigned)((use - 1) & 1), p.status, ERR_TC_A_EMPTY);
+                    const long long t1 = prof ? clock64() : 0;
                     if (ok) {
                         unsigned char* hi = smem + TC_OFF_A + s * TC_STAGE_BYTES;
                         unsigned char* lo = hi + TC_STAGE_HALF;
@@ -167,6 +171,12 @@ __device__ __forceinline__ bool tc_produce_output(const UvwTcParams& p, unsigned
                         fence_async_smem();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(bars.a_full + s);
+                        if (prof) {
+                            const long long t2 = clock64();
+                            atomicAdd(p.prof + 0, (unsigned long long)(t1 - t0));   // wait for the stage
+                            atomicAdd(p.prof + 1, (unsigned long long)(t2 - t1));   // loads landing, T, stores
+                            atomicAdd(p.prof + 2, 1ull);
+                        }
                     }
                     ++stage_it;
                 }
@@ -204,7 +214,8 @@ __device__ __forceinline__ bool tc_mma_output(const UvwTcParams& p, unsigned cha
     }
     if (!mbar_wait(bars.w_full, (unsigned)(w_use & 1), p.status, ERR_TC_W)) return false;
     ++w_use;
-    const unsigned w_addr = smem_u32(smem + TC_OFF_W);
+    const unsigned long long w_desc0 = tc_smem_desc(smem_u32(smem + TC_OFF_W));
+    const unsigned long long a_desc0 = tc_smem_desc(smem_u32(smem + TC_OFF_A));
     bool ok = true;
     for (long long b0 = row_lo; b0 < row_hi && ok; b0 += RPC) {
         const int t = (int)(acc_it % NACC);
@@ -220,23 +231,30 @@ __device__ __forceinline__ bool tc_mma_output(const UvwTcParams& p, unsigned cha
                 for (int h = 0; h < tc_khalves(P) && ok; ++h) {
                     const int s = (int)(stage_it % TC_NA);
                     const long long use = stage_it / TC_NA;
+                    const bool prof = p.prof && blockIdx.x == 0;
+                    const long long t0 = prof ? clock64() : 0;
                     ok = mbar_wait(bars.a_full + s, (unsigned)(use & 1), p.status, ERR_TC_A_FULL);
+                    const long long t1 = prof ? clock64() : 0;
                     if (ok) {
                         tc_fence_after();
-                        const unsigned a_hi = smem_u32(smem + TC_OFF_A + s * TC_STAGE_BYTES);
-                        const unsigned a_lo = a_hi + TC_STAGE_HALF;
-                        const unsigned b_hi = w_addr + (unsigned)((tc_blocks_before(O, P) + h) * 2 * BLOCK);
-                        const unsigned b_lo = b_hi + BLOCK;
+                        // descriptors differ from the base ones only in the start-address field (16-byte units):
+                        // one add per operand instead of rebuilding them (the issuing thread is latency bound)
+                        const unsigned long long da_hi = a_desc0 + (unsigned long long)((s * TC_STAGE_BYTES) >> 4);
+                        const unsigned long long da_lo = da_hi + (TC_STAGE_HALF >> 4);
+                        const unsigned long long db_hi = w_desc0 + (unsigned long long)(((tc_blocks_before(O, P) + h) * 2 * BLOCK) >> 4);
+                        const unsigned long long db_lo = db_hi + (BLOCK >> 4);
 #pragma unroll
                         for (int kk = 0; kk < 4; ++kk) {
-                            const unsigned long long da_hi = tc_smem_desc(a_hi + kk * 32), da_lo = tc_smem_desc(a_lo + kk * 32);
-                            const unsigned long long db_hi = tc_smem_desc(b_hi + kk * 32), db_lo = tc_smem_desc(b_lo + kk * 32);
-                            tc_mma(tmem_d, da_hi, db_hi, IDESC, accumulate);
+                            tc_mma(tmem_d, da_hi + 2 * kk, db_hi + 2 * kk, IDESC, accumulate);
                             accumulate = 1;
-                            tc_mma(tmem_d, da_hi, db_lo, IDESC, 1);
-                            tc_mma(tmem_d, da_lo, db_hi, IDESC, 1);
+                            tc_mma(tmem_d, da_hi + 2 * kk, db_lo + 2 * kk, IDESC, 1);
+                            tc_mma(tmem_d, da_lo + 2 * kk, db_hi + 2 * kk, IDESC, 1);
                         }
                         tc_commit(bars.a_empty + s);   // the stage may be refilled once these MMAs have read it
+                        if (prof) {
+                            atomicAdd(p.prof + 8, (unsigned long long)(t1 - t0));             // wait for operands
+                            atomicAdd(p.prof + 9, (unsigned long long)(clock64() - t1));      // issue
+                        }
                     }
                     ++stage_it;
                 }
@@ -276,7 +294,11 @@ __device__ __forceinline__ bool tc_epilogue_output(const UvwTcParams& p, unsigne
         const int rows = (int)(row_hi - b0 < RPC ? row_hi - b0 : RPC);
         const int t = (int)(acc_it % NACC);
         const long long use = acc_it / NACC;
+        const bool prof = p.prof && blockIdx.x == 0 && et == 0;
+        const long long t0 = prof ? clock64() : 0;
         ok = mbar_wait(bars.acc_full + t, (unsigned)(use & 1), p.status, ERR_TC_ACC_FULL);
+        if (prof) atomicAdd(p.prof + 16, (unsigned long long)(clock64() - t0));
+        const long long t1 = prof ? clock64() : 0;
         // the four warps must agree before anyone touches the staging buffer or skips a barrier
         ok = tc_epilogue_all(ok);
         if (!ok) break;
@@ -306,6 +328,10 @@ __device__ __forceinline__ bool tc_epilogue_output(const UvwTcParams& p, unsigne
             p.Z[(b0 + r) * (long long)Z_DIM + OUT_OFF[O] + j] = stg[(r * D3 + k) * TC_STG_PITCH + w];
         }
         asm volatile("bar.sync 1, %0;" ::"n"(TC_EPILOGUE_WARPS * 32) : "memory");
+        if (prof) {
+            atomicAdd(p.prof + 17, (unsigned long long)(clock64() - t1));
+            atomicAdd(p.prof + 18, 1ull);
+        }
         ++acc_it;
     }
     return ok;
