@@ -219,15 +219,6 @@ __device__ void utc_mma(const UvuParams& p, unsigned char* smem, const UtcCtrl& 
 }
 
 // ---------------------------------------------------------------------------- consumer warps
-// 16 accumulator columns of the warp's TMEM lanes
-__device__ __forceinline__ void utc_load16(unsigned taddr, unsigned* v) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-        : "r"(taddr));
-}
-
 // Partition Q: the consumers that own the output irreps with FWD_PART_OF_OUT == Q.
 template <int MODE, int Q>
 __device__ void utc_consumer(const UvuParams& p, unsigned char* smem, const UtcCtrl& c, unsigned tmem_base, int u) {
@@ -367,7 +358,7 @@ __device__ void utc_consumer(const UvuParams& p, unsigned char* smem, const UtcC
             unsigned v[16 * (NCHUNK > 0 ? NCHUNK : 1)];
             const long long t_ld = clock64();
 #pragma unroll
-            for (int q = 0; q < NCHUNK; ++q) utc_load16(taddr + (unsigned)(16 * q), v + 16 * q);
+            for (int q = 0; q < NCHUNK; ++q) tc_load16(taddr + (unsigned)(16 * q), v + 16 * q);
             if (lo >= 0) next_unwritten = lo;   // a new chunk starts: its first node is unwritten
             if (prev >= 0 && node != prev) {
                 flush(prev);

@@ -69,6 +69,16 @@ constexpr int tc_mw_max() {
     for (int o = 0; o < N_OUT; ++o) m = OUT_MUL[o] > m ? OUT_MUL[o] : m;
     return m;
 }
+constexpr bool tc_wide(int o) { return 2 * OUT_MUL[o] <= 256; }
+constexpr int tc_acc_cols(int o) { return tc_wide(o) ? 2 * OUT_MUL[o] : OUT_MUL[o]; }
+// One ring of accumulator tiles serves all output irreps: equal tile width and count for all of them, so that
+// tile index and barrier phase follow from one running counter.
+constexpr int tc_acc_cols_max() {
+    int m = 16;
+    for (int o = 0; o < N_OUT; ++o) m = tc_acc_cols(o) > m ? tc_acc_cols(o) : m;
+    return m;
+}
+constexpr int TC_ACC_COLS = tc_acc_cols_max();
 constexpr int TC_W_MAX = tc_w_max();
 constexpr int TC_MW_MAX = tc_mw_max();
 constexpr int TC_STG_PITCH = TC_MW_MAX + 1;    // floats per staged accumulator row (odd: conflict free)
@@ -80,6 +90,7 @@ constexpr int TC_OFF_W = TC_OFF_A + TC_NA * TC_STAGE_BYTES;
 constexpr int TC_OFF_STG = TC_OFF_W + (TC_W_MAX + 1023) / 1024 * 1024;
 constexpr int TC_OFF_BAR = TC_OFF_STG + (128 * TC_STG_PITCH * 4 + 15) / 16 * 16;
 constexpr int TC_MAX_ACC = 32;
+constexpr int TC_NACC = TC_TMEM_COLS / TC_ACC_COLS < TC_MAX_ACC ? TC_TMEM_COLS / TC_ACC_COLS : TC_MAX_ACC;
 constexpr int TC_SMEM_BYTES = TC_OFF_BAR + (2 * TC_NA + 2 * TC_MAX_ACC + 2) * 8 + 16 + 1024;   // + alignment slack
 
 struct TcBars {
@@ -194,8 +205,13 @@ __device__ __forceinline__ bool tc_mma_output(const UvwTcParams& p, unsigned cha
     constexpr int D3 = OUT_D[O];
     constexpr int RPC = 128 / D3;
     constexpr int MW = OUT_MUL[O];
-    constexpr int NACC = TC_TMEM_COLS / MW < TC_MAX_ACC ? TC_TMEM_COLS / MW : TC_MAX_ACC;
-    constexpr unsigned IDESC = tc_instr_desc(MW);
+    // Issuing a tcgen05.mma costs about 90 cycles whatever its size, so hi.hi and hi.lo go out as one MMA: the
+    // lo tile of the weights follows the hi tile in shared memory, and a B descriptor over 2 MW rows covers
+    // both.  The accumulator tile is then [hi.hi + lo.hi | hi.lo], summed by the epilogue.
+    constexpr bool WIDE = tc_wide(O);
+    constexpr int ACC_COLS = TC_ACC_COLS;
+    constexpr int NACC = TC_NACC;
+    constexpr unsigned IDESC = tc_instr_desc(MW), IDESC_WIDE = tc_instr_desc(2 * MW);
     constexpr int BLOCK = tc_block_bytes(O);
     if (row_lo >= row_hi) return true;
     // the weights of the previous output must not be overwritten while tensor cores still read them
@@ -223,7 +239,7 @@ __device__ __forceinline__ bool tc_mma_output(const UvwTcParams& p, unsigned cha
         if (acc_use > 0) ok = mbar_wait(bars.acc_empty + t, (unsigned)((acc_use - 1) & 1), p.status, ERR_TC_ACC_EMPTY);
         if (!ok) break;
         tc_fence_after();
-        const unsigned tmem_d = tmem_base + (unsigned)(t * MW);
+        const unsigned tmem_d = tmem_base + (unsigned)(t * ACC_COLS);
         unsigned accumulate = 0;
         sfor<0, N_INSTR>([&](auto p_) {
             constexpr int P = p_;
@@ -245,9 +261,13 @@ __device__ __forceinline__ bool tc_mma_output(const UvwTcParams& p, unsigned cha
                         const unsigned long long db_lo = db_hi + (BLOCK >> 4);
 #pragma unroll
                         for (int kk = 0; kk < 4; ++kk) {
-                            tc_mma(tmem_d, da_hi + 2 * kk, db_hi + 2 * kk, IDESC, accumulate);
+                            if constexpr (WIDE) {
+                                tc_mma(tmem_d, da_hi + 2 * kk, db_hi + 2 * kk, IDESC_WIDE, accumulate);
+                            } else {
+                                tc_mma(tmem_d, da_hi + 2 * kk, db_hi + 2 * kk, IDESC, accumulate);
+                                tc_mma(tmem_d, da_hi + 2 * kk, db_lo + 2 * kk, IDESC, 1);
+                            }
                             accumulate = 1;
-                            tc_mma(tmem_d, da_hi + 2 * kk, db_lo + 2 * kk, IDESC, 1);
                             tc_mma(tmem_d, da_lo + 2 * kk, db_hi + 2 * kk, IDESC, 1);
                         }
                         tc_commit(bars.a_empty + s);   // the stage may be refilled once these MMAs have read it
@@ -286,7 +306,9 @@ __device__ __forceinline__ bool tc_epilogue_output(const UvwTcParams& p, unsigne
     constexpr int D3 = OUT_D[O];
     constexpr int RPC = 128 / D3;
     constexpr int MW = OUT_MUL[O];
-    constexpr int NACC = TC_TMEM_COLS / MW < TC_MAX_ACC ? TC_TMEM_COLS / MW : TC_MAX_ACC;
+    constexpr bool WIDE = tc_wide(O);
+    constexpr int ACC_COLS = TC_ACC_COLS;
+    constexpr int NACC = TC_NACC;
     float* stg = reinterpret_cast<float*>(smem + TC_OFF_STG);
     const int et = ewarp * 32 + lane;
     bool ok = true;
@@ -304,18 +326,19 @@ __device__ __forceinline__ bool tc_epilogue_output(const UvwTcParams& p, unsigne
         if (!ok) break;
         tc_fence_after();
         // (ewarp is the warp's TMEM lane quarter) accumulator row m = 32 * ewarp + lane holds (row m / D3, component m % D3) for all w
-        const unsigned taddr = tmem_base + ((unsigned)(ewarp * 32) << 16) + (unsigned)(t * MW);
+        const unsigned taddr = tmem_base + ((unsigned)(ewarp * 32) << 16) + (unsigned)(t * ACC_COLS);
 #pragma unroll
         for (int c0 = 0; c0 < MW; c0 += 16) {
-            unsigned v[16];
-            asm volatile(
-                "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-                : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-                  "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-                : "r"(taddr + (unsigned)c0));
+            unsigned v[16], v2[16];
+            tc_load16(taddr + (unsigned)c0, v);
+            if constexpr (WIDE) tc_load16(taddr + (unsigned)(MW + c0), v2);   // the hi.lo half of the tile
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-            for (int c = 0; c < 16; ++c) stg[(ewarp * 32 + lane) * TC_STG_PITCH + c0 + c] = __uint_as_float(v[c]);
+            for (int c = 0; c < 16; ++c) {
+                float val = __uint_as_float(v[c]);
+                if constexpr (WIDE) val += __uint_as_float(v2[c]);
+                stg[(ewarp * 32 + lane) * TC_STG_PITCH + c0 + c] = val;
+            }
         }
         tc_fence_before();
         asm volatile("bar.sync 1, %0;" ::"n"(TC_EPILOGUE_WARPS * 32) : "memory");

@@ -109,3 +109,24 @@ def test_tensor_core_forward_matches_oracle_and_fma_path(in1, in2, out, batch, m
     # repeated launches reuse the accumulator ring and the packed weights
     for _ in range(3):
         assert torch.equal(z, tp(xt, yt, wt))
+
+
+@pytest.mark.parametrize("in1,in2,out,batch", [s[:3] + (40_000,) for s in TC_SHAPES[1:3]], ids=[s[2] for s in TC_SHAPES[1:3]])
+def test_tensor_core_forward_many_tiles_mixed_multiplicities(in1, in2, out, batch, monkeypatch):
+    """Every CTA walks many row chunks of every output irrep, so the accumulator ring wraps within and
+    across output irreps of different multiplicity; compared with the FMA kernel on all rows and with the
+    oracle on sampled rows."""
+    p = oeq.FullyConnectedTPProblem(in1, in2, out)
+    tp = oeq.TensorProduct(p, torch_op=True)
+    assert tp.internal.launch_info(0)["threads"] == 21 * 32
+    x, y, w, _ = tp_inputs(p, batch, 23)
+    w = (w / np.sqrt(max(1, p.weight_numel / len(p.instructions)))).astype(np.float32)
+    xt, yt, wt = (torch.from_numpy(a).cuda() for a in (x, y, to_oeq(p, w)))
+    z = tp(xt, yt, wt)
+    torch.cuda.synchronize()
+    tp.check_device_status()
+    monkeypatch.setenv("OEQ_B200_UVW_TC", "0")
+    fma = oeq.TensorProduct(p, torch_op=True)
+    assert rel_err(z.cpu().numpy(), fma(xt, yt, wt).cpu().numpy()) < 1e-5
+    rows = np.arange(0, batch, 997)
+    assert rel_err(z.cpu().numpy()[rows], orc.tp_forward(p, x[rows], y[rows], w)) < 1e-5
