@@ -56,6 +56,13 @@ def test_fp64(deterministic):
     check_conv(p, 40, rows, cols, 10, deterministic, dtype=np.float64)
 
 
+def test_fp64_widest_rows():
+    """MACE-large rows in FP64: a backward stage only fits because the output-gradient row is staged in phases."""
+    p = problem_by_name("mace_large_128", irrep_dtype=np.float64, weight_dtype=np.float64)
+    rows, cols = random_graph(19, 120, seed=5)
+    check_conv(p, 19, rows, cols, 12, True, dtype=np.float64)
+
+
 @pytest.mark.parametrize("deterministic", [False, True], ids=["atomic", "deterministic"])
 def test_isolated_nodes_and_hubs(deterministic):
     """Receivers without edges must come out as zero rows; one node receives most edges."""
