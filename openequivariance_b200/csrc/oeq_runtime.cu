@@ -855,6 +855,43 @@ int build_uvw_tc(const Problem& p, Kernel& k) {
     return OEQ_OK;
 }
 
+// ---- tensor-core backward for 'uvw' (mirrors the constexpr geometry of uvw_tc_bwd_kernels.cuh)
+constexpr int K_UVW_TC_DW = 21;
+
+struct TcBwdGeometry {
+    int dw_smem = 0;
+};
+
+bool uvw_tc_bwd_geometry(const Problem& p, TcBwdGeometry& g) {
+    TcGeometry fwd;
+    if (!uvw_tc_geometry(p, fwd)) return false;          // same class of problems as the forward pass
+    if (!env_int("OEQ_B200_UVW_TC_BWD", 1)) return false;
+    int mw_max = 16;
+    for (const Irrep& r : p.out) mw_max = std::max(mw_max, r.mul);
+    for (const Instr& t : p.instr)
+        if (p.in1[t.i1].mul > 128) return false;
+    if (mw_max > 128) return false;
+    const int stage = 2 * 128 * 128 + 2 * mw_max * 128;
+    const int stages = std::min(4, (200 * 1024) / stage);
+    if (stages < 2) return false;
+    g.dw_smem = stages * stage + (2 * stages + 4) * 8 + 16 + 1024;
+    return g.dw_smem <= SMEM_LIMIT;
+}
+
+int build_uvw_tc_bwd(const Problem& p, int kernel_id, Kernel& k) {
+    k.is_uvw = true;
+    int rc = choose_uvw(p, true, k.uvw);
+    if (rc) return rc;
+    k.map.part_of_out.assign(p.out.size(), 0);
+    k.map.part_of_instr.assign(p.instr.size(), 0);
+    k.map.zr_off.assign(p.out.size(), 0);
+    k.map.xr_off.assign(p.in1.size(), 0);
+    rc = compile_kernel(descriptor_text(p, k.map, &k.uvw), "uvw_tc_bwd_kernels.cuh", kernel_id, k.code);
+    if (rc) return rc;
+    k.compiled = true;
+    return OEQ_OK;
+}
+
 int build_tp(const Problem& p, bool bwd, Kernel& k) {
     if (p.mode == OEQ_MODE_UVW) return build_uvw(p, bwd ? K_UVW_BWD : K_UVW_FWD, k);
     return build_uvu(p, bwd ? K_BWD_BATCH : K_FWD_BATCH, k);
@@ -891,6 +928,7 @@ struct UvwParams {
     void* ws;
     long long batch;
     int* status;
+    int skip_dw;      // the shared-weight gradient comes from the tensor-core kernel
 };
 
 long long uvw_grid(const Kernel& k, long long batch) {
@@ -973,6 +1011,9 @@ struct oeq_tp {
     Kernel fwd, bwd;
     Kernel fwd_tc;              // tensor-core forward ('uvw', shared FP32 weights), when the problem qualifies
     bool has_tc = false;
+    Kernel bwd_dw_tc;           // tensor-core weight gradient of the same class of problems
+    bool has_bwd_tc = false;
+    TcBwdGeometry tc_bwd;
     TcGeometry tc;
     void* d_packed = nullptr;   // weights split and swizzled for the tensor cores (owned by the handle)
     cudaKernel_t pack_fn = nullptr;
@@ -1023,6 +1064,9 @@ int oeq_precompile(const oeq_problem_desc* desc, int kinds) {
         if ((rc = build_tp(p, false, f)) || (rc = build_tp(p, true, b))) return rc;
         TcGeometry g;
         if (uvw_tc_geometry(p, g) && (rc = build_uvw_tc(p, tc))) return rc;
+        TcBwdGeometry gb;
+        Kernel dw;
+        if (uvw_tc_bwd_geometry(p, gb) && (rc = build_uvw_tc_bwd(p, K_UVW_TC_DW, dw))) return rc;
         return OEQ_OK;
     }
     auto one = [&](int kind) {
@@ -1062,6 +1106,10 @@ int oeq_tp_create(const oeq_problem_desc* desc, oeq_tp** out) {
     if (!rc && uvw_tc_geometry(h->prob, h->tc)) {
         rc = build_uvw_tc(h->prob, h->fwd_tc);
         h->has_tc = rc == OEQ_OK;
+    }
+    if (!rc && uvw_tc_bwd_geometry(h->prob, h->tc_bwd)) {
+        rc = build_uvw_tc_bwd(h->prob, K_UVW_TC_DW, h->bwd_dw_tc);
+        h->has_bwd_tc = rc == OEQ_OK;
     }
     if (rc) {
         delete h;
@@ -1165,7 +1213,7 @@ size_t oeq_tp_workspace_bytes(const oeq_tp* h, int64_t batch) {
     long long groups;
     if (h->prob.mode == OEQ_MODE_UVW) {
         const long long tiles = (batch + h->bwd.uvw.tile_r - 1) / h->bwd.uvw.tile_r;
-        groups = std::min<long long>(tiles, 256ll * 2);
+        groups = std::max<long long>(std::min<long long>(tiles, 256ll * 2), h->has_bwd_tc ? 256ll : 0ll);
     } else {
         groups = 256ll * 4 * h->bwd.map.ng;
     }
@@ -1197,10 +1245,39 @@ int oeq_tp_backward(oeq_tp* h, int64_t batch, const void* X, const void* Y, cons
         up.X = X; up.Y = Y; up.W = W; up.dZ = dZ; up.dX = dX; up.dY = dY; up.dW = dW; up.ws = workspace;
         up.batch = batch; up.status = h->d_status;
         h->last_stream = st;
+        if (h->has_bwd_tc) {
+            // weight gradient on the tensor cores (per-CTA partial sums in the workspace, then the fixed-order
+            // reduction); the FMA kernel computes dX and dY only
+            Kernel& k = h->bwd_dw_tc;
+            if (!k.loaded) {
+                OEQ_CUDA(cudaLibraryLoadData(&k.lib, k.code.cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0));
+                OEQ_CUDA(cudaLibraryGetKernel(&k.fn, k.lib, "oeq_uvw_tc_dw_kernel"));
+                OEQ_CUDA(cudaLibraryGetKernel(&k.reduce_fn, k.lib, "oeq_reduce_partials"));
+                int dev = 0;
+                OEQ_CUDA(cudaGetDevice(&dev));
+                OEQ_CUDA(cudaDeviceGetAttribute(&k.sm_count, cudaDevAttrMultiProcessorCount, dev));
+                k.smem = h->tc_bwd.dw_smem;
+                OEQ_CUDA(cudaFuncSetAttribute((const void*)k.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, k.smem));
+                k.loaded = true;
+            }
+            long long dw_ctas = std::max<long long>(1, std::min<long long>(k.sm_count, (batch + 31) / 32));
+            if ((size_t)dw_ctas * p.w_numel * p.elem() > workspace_bytes)
+                return fail(OEQ_ERR_INVALID, "workspace too small for the shared-weight gradient (see oeq_tp_workspace_bytes)");
+            struct { const void* X; const void* Y; const void* Wt; const void* dZ; void* dX; void* dY; void* ws; long long batch;
+                     int* status; } tp{X, Y, nullptr, dZ, dX, dY, workspace, batch, h->d_status};
+            void* targs[] = {&tp};
+            OEQ_CUDA(cudaLaunchKernel((const void*)k.fn, dim3((unsigned)dw_ctas), dim3(21 * 32), targs, (size_t)k.smem, st));
+            int n = p.w_numel;
+            const void* ws = workspace;
+            void* rargs[] = {&ws, &dW, &n, &dw_ctas};
+            OEQ_CUDA(cudaLaunchKernel((const void*)k.reduce_fn, dim3((n + 127) / 128), dim3(128), rargs, 0, st));
+            up.skip_dw = 1;
+            up.ws = nullptr;
+        }
         void* args[] = {&up};
         OEQ_CUDA(cudaLaunchKernel((const void*)h->bwd.fn, dim3((unsigned)ctas), dim3((unsigned)h->bwd.uvw.threads), args,
                                   (size_t)h->bwd.smem, st));
-        if (p.shared) {
+        if (p.shared && !h->has_bwd_tc) {
             int n = p.w_numel;
             const void* ws = workspace;
             void* rargs[] = {&ws, &dW, &n, &ctas};

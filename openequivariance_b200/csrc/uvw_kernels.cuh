@@ -31,6 +31,7 @@ struct UvwParams {
     T* ws;  // [gridDim.x][W_NUMEL] partial weight gradients (shared weights)
     long long batch;
     int* status;
+    int skip_dw;   // shared weights: the weight gradient is computed elsewhere, leave dW and ws alone
 };
 
 constexpr int NT = UVW_THREADS;
@@ -212,10 +213,13 @@ __device__ void uvw_backward(const UvwParams& p) {
     const UvwSmem s = carve(smem_raw, true);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const long long tiles = (p.batch + TILE_R - 1) / TILE_R;
-    T* wsl = SHARED_W ? p.ws + (long long)blockIdx.x * W_NUMEL : nullptr;
+    const bool with_dw = !(SHARED_W && p.skip_dw);
+    T* wsl = (SHARED_W && with_dw) ? p.ws + (long long)blockIdx.x * W_NUMEL : nullptr;
     if constexpr (SHARED_W) {
-        for (int i = tid; i < W_NUMEL; i += NT) wsl[i] = (T)0;
-        __syncthreads();
+        if (with_dw) {
+            for (int i = tid; i < W_NUMEL; i += NT) wsl[i] = (T)0;
+            __syncthreads();
+        }
     }
     for (long long tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
         const long long row0 = tile * TILE_R;
@@ -276,7 +280,7 @@ __device__ void uvw_backward(const UvwParams& p) {
                 // weight gradient
                 if constexpr (SHARED_W) {
                     // dW[uv,w] += sum_{r,k} T[uv,r,k] dZ[r,w,k]; the owning thread adds into the CTA's slice
-                    for (int item = tid; item < n * MW; item += NT) {
+                    for (int item = tid; with_dw && item < n * MW; item += NT) {
                         const int w = item % MW, l = item / MW, uv = uv0 + l;
                         const T* tsrc = s.tt + l * TILE_R * D3;
                         const T* zsrc = s.zt + w * TILE_R * D3;
