@@ -856,10 +856,12 @@ int build_uvw_tc(const Problem& p, Kernel& k) {
 }
 
 // ---- tensor-core backward for 'uvw' (mirrors the constexpr geometry of uvw_tc_bwd_kernels.cuh)
-constexpr int K_UVW_TC_DW = 21;
+constexpr int K_UVW_TC_DW = 21, K_UVW_TC_DXY = 22;
 
 struct TcBwdGeometry {
     int dw_smem = 0;
+    int dxy_smem = 0;           // 0: the dX/dY kernel does not take this problem
+    size_t wt_bytes = 0;        // transposed packed weights
 };
 
 bool uvw_tc_bwd_geometry(const Problem& p, TcBwdGeometry& g) {
@@ -875,7 +877,28 @@ bool uvw_tc_bwd_geometry(const Problem& p, TcBwdGeometry& g) {
     const int stages = std::min(4, (200 * 1024) / stage);
     if (stages < 2) return false;
     g.dw_smem = stages * stage + (2 * stages + 4) * 8 + 16 + 1024;
-    return g.dw_smem <= SMEM_LIMIT;
+    if (g.dw_smem > SMEM_LIMIT) return false;
+    // dX/dY kernel: two A stages, one path's transposed weights, the epilogue staging buffer
+    int kb_max = 1, mup_max = 16, wt_max = 0;
+    size_t wt_total = 0;
+    for (const Irrep& r : p.out) kb_max = std::max(kb_max, (r.mul + 31) / 32);
+    for (const Instr& t : p.instr) {
+        const int mup = (p.in1[t.i1].mul + 15) / 16 * 16;
+        const int bytes = ((p.out[t.io].mul + 31) / 32) * 2 * mup * 128;
+        mup_max = std::max(mup_max, mup);
+        wt_max = std::max(wt_max, bytes);
+        wt_total += bytes;
+    }
+    const int nacc = std::min(4, 512 / (2 * mup_max));
+    const int off_w = 2 * kb_max * 2 * 128 * 128;
+    const int off_stg = off_w + (wt_max + 1023) / 1024 * 1024;
+    const int off_bar = off_stg + (128 * (mup_max + 1) * 4 + 15) / 16 * 16;
+    const int dxy = off_bar + (2 * 2 + 2 * nacc + 2) * 8 + 16 + 1024;
+    if (nacc >= 1 && dxy <= SMEM_LIMIT) {
+        g.dxy_smem = dxy;
+        g.wt_bytes = wt_total;
+    }
+    return true;
 }
 
 int build_uvw_tc_bwd(const Problem& p, int kernel_id, Kernel& k) {
@@ -1012,8 +1035,11 @@ struct oeq_tp {
     Kernel fwd_tc;              // tensor-core forward ('uvw', shared FP32 weights), when the problem qualifies
     bool has_tc = false;
     Kernel bwd_dw_tc;           // tensor-core weight gradient of the same class of problems
-    bool has_bwd_tc = false;
+    Kernel bwd_dxy_tc;          // tensor-core dX / dY of the same class of problems (when its tiles fit)
+    bool has_bwd_tc = false, has_dxy_tc = false;
     TcBwdGeometry tc_bwd;
+    void* d_packed_t = nullptr; // weights transposed, split and swizzled for the dX/dY kernel
+    cudaKernel_t pack_t_fn = nullptr;
     TcGeometry tc;
     void* d_packed = nullptr;   // weights split and swizzled for the tensor cores (owned by the handle)
     cudaKernel_t pack_fn = nullptr;
@@ -1065,8 +1091,11 @@ int oeq_precompile(const oeq_problem_desc* desc, int kinds) {
         TcGeometry g;
         if (uvw_tc_geometry(p, g) && (rc = build_uvw_tc(p, tc))) return rc;
         TcBwdGeometry gb;
-        Kernel dw;
-        if (uvw_tc_bwd_geometry(p, gb) && (rc = build_uvw_tc_bwd(p, K_UVW_TC_DW, dw))) return rc;
+        Kernel dw, dxy;
+        if (uvw_tc_bwd_geometry(p, gb)) {
+            if ((rc = build_uvw_tc_bwd(p, K_UVW_TC_DW, dw))) return rc;
+            if (gb.dxy_smem > 0 && (rc = build_uvw_tc_bwd(p, K_UVW_TC_DXY, dxy))) return rc;
+        }
         return OEQ_OK;
     }
     auto one = [&](int kind) {
@@ -1110,6 +1139,10 @@ int oeq_tp_create(const oeq_problem_desc* desc, oeq_tp** out) {
     if (!rc && uvw_tc_bwd_geometry(h->prob, h->tc_bwd)) {
         rc = build_uvw_tc_bwd(h->prob, K_UVW_TC_DW, h->bwd_dw_tc);
         h->has_bwd_tc = rc == OEQ_OK;
+        if (!rc && h->tc_bwd.dxy_smem > 0 && env_int("OEQ_B200_UVW_TC_DXY", 1)) {
+            rc = build_uvw_tc_bwd(h->prob, K_UVW_TC_DXY, h->bwd_dxy_tc);
+            h->has_dxy_tc = rc == OEQ_OK;
+        }
     }
     if (rc) {
         delete h;
@@ -1273,6 +1306,29 @@ int oeq_tp_backward(oeq_tp* h, int64_t batch, const void* X, const void* Y, cons
             OEQ_CUDA(cudaLaunchKernel((const void*)k.reduce_fn, dim3((n + 127) / 128), dim3(128), rargs, 0, st));
             up.skip_dw = 1;
             up.ws = nullptr;
+            if (h->has_dxy_tc) {
+                // dX and dY on the tensor cores too: the FMA kernel is not launched at all
+                Kernel& kx = h->bwd_dxy_tc;
+                if (!kx.loaded) {
+                    OEQ_CUDA(cudaLibraryLoadData(&kx.lib, kx.code.cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0));
+                    OEQ_CUDA(cudaLibraryGetKernel(&kx.fn, kx.lib, "oeq_uvw_tc_dxy_kernel"));
+                    OEQ_CUDA(cudaLibraryGetKernel(&h->pack_t_fn, kx.lib, "oeq_uvw_pack_weights_t"));
+                    kx.sm_count = k.sm_count;
+                    kx.smem = h->tc_bwd.dxy_smem;
+                    OEQ_CUDA(cudaFuncSetAttribute((const void*)kx.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kx.smem));
+                    OEQ_CUDA(cudaMalloc(&h->d_packed_t, h->tc_bwd.wt_bytes));
+                    kx.loaded = true;
+                }
+                void* packed = h->d_packed_t;
+                void* pargs[] = {(void*)&W, &packed};
+                OEQ_CUDA(cudaLaunchKernel((const void*)h->pack_t_fn, dim3(64), dim3(256), pargs, 0, st));
+                OEQ_CUDA(cudaMemsetAsync(dX, 0, (size_t)batch * p.x_dim * p.elem(), st));
+                OEQ_CUDA(cudaMemsetAsync(dY, 0, (size_t)batch * p.y_dim * p.elem(), st));
+                tp.Wt = h->d_packed_t;
+                const long long ctas_x = std::max<long long>(1, std::min<long long>(kx.sm_count, (batch + 23) / 24));
+                OEQ_CUDA(cudaLaunchKernel((const void*)kx.fn, dim3((unsigned)ctas_x), dim3(17 * 32), targs, (size_t)kx.smem, st));
+                return OEQ_OK;
+            }
         }
         void* args[] = {&up};
         OEQ_CUDA(cudaLaunchKernel((const void*)h->bwd.fn, dim3((unsigned)ctas), dim3((unsigned)h->bwd.uvw.threads), args,

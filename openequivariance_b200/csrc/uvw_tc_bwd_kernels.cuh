@@ -357,13 +357,359 @@ __device__ void uvw_tc_dw(const UvwTcBwdParams& p) {
     }
 }
 
+// =====================================================================================================
+// dX / dY kernel.  Per output irrep o, path p into o (its weights W_p^T resident in shared memory as the
+// B operand, [u rows x w], hi tile followed by lo tile per 32-wide slice of w) and chunk of
+// RPC = floor(128 / (2l+1)) batch rows: D[(row,k), u] = sum_w dZ[row,o,w,k] W_p[u,w] on the tensor cores,
+// A = dZ gathered as [(row,k) x w] tiles.  The epilogue warps turn D (= dT) into dX and dY with the
+// Clebsch-Gordan coefficients unrolled; dX and dY are cleared by the host and accumulated path by path by
+// the CTA that owns the rows, in a fixed order.
+// =====================================================================================================
+constexpr int DX_PRODUCER_WARPS = 8;
+constexpr int DX_EPILOGUE_WARPS = 8;
+constexpr int DX_WARP_MMA = DX_PRODUCER_WARPS;
+constexpr int DX_THREADS = (DX_PRODUCER_WARPS + 1 + DX_EPILOGUE_WARPS) * 32;
+constexpr int ERR_DX_EMPTY = 41, ERR_DX_FULL = 42, ERR_DX_ACC_EMPTY = 43, ERR_DX_ACC_FULL = 44, ERR_DX_W = 45;
+
+constexpr int dx_mup(int p) { return (IN1_MUL[I_IN1[p]] + 15) / 16 * 16; }          // rows of the weight tile
+constexpr int dx_kblocks(int o) { return (OUT_MUL[o] + 31) / 32; }                   // 32-wide slices of w
+constexpr int dx_wt_bytes(int p) { return dx_kblocks(I_OUT[p]) * 2 * dx_mup(p) * 128; }
+constexpr int dx_wt_offset(int p_end) {        // byte offset of path p_end inside the packed transposed weights
+    int b = 0;
+    for (int p = 0; p < p_end; ++p) b += dx_wt_bytes(p);
+    return b;
+}
+constexpr int dx_max(int (*f)(int), int n) {
+    int m = 0;
+    for (int i = 0; i < n; ++i) m = f(i) > m ? f(i) : m;
+    return m;
+}
+constexpr int DX_KB_MAX = dx_max(dx_kblocks, N_OUT);
+constexpr int DX_MUP_MAX = dx_max(dx_mup, N_INSTR);
+constexpr int DX_WT_MAX = dx_max(dx_wt_bytes, N_INSTR);
+constexpr int DX_STAGE_BYTES = DX_KB_MAX * 2 * TB_TILE;         // per 32-wide slice of w: hi tile, lo tile
+constexpr int DX_NA = 2;
+constexpr int DX_ACC_COLS = 2 * DX_MUP_MAX;                      // [hi.hi + lo.hi | hi.lo]
+constexpr int DX_NACC = 512 / DX_ACC_COLS < 4 ? 512 / DX_ACC_COLS : 4;
+constexpr int DX_STG_PITCH = DX_MUP_MAX + 1;
+constexpr int DX_OFF_A = 0;
+constexpr int DX_OFF_W = DX_OFF_A + DX_NA * DX_STAGE_BYTES;
+constexpr int DX_OFF_STG = DX_OFF_W + (DX_WT_MAX + 1023) / 1024 * 1024;
+constexpr int DX_OFF_BAR = DX_OFF_STG + (128 * DX_STG_PITCH * 4 + 15) / 16 * 16;
+constexpr int DX_SMEM_BYTES = DX_OFF_BAR + (2 * DX_NA + 2 * DX_NACC + 2) * 8 + 16 + 1024;
+static_assert(DX_ACC_COLS <= 256, "first-input multiplicity above 128");
+
+struct DxBars {
+    unsigned long long *full, *empty, *acc_full, *acc_empty, *w_full, *w_free;
+    unsigned* tmem_slot;
+    __device__ explicit DxBars(unsigned char* smem) {
+        unsigned long long* b = reinterpret_cast<unsigned long long*>(smem + DX_OFF_BAR);
+        full = b; empty = b + DX_NA; acc_full = b + 2 * DX_NA; acc_empty = acc_full + DX_NACC;
+        w_full = acc_empty + DX_NACC; w_free = w_full + 1;
+        tmem_slot = reinterpret_cast<unsigned*>(w_free + 1);
+    }
+};
+
+// A tiles of one chunk: element (row r * D3 + k, column w) = dZ[b0 + r, o, w, k]; every element is written
+template <int O>
+__device__ __forceinline__ bool dx_produce(const UvwTcBwdParams& p, unsigned char* smem, const DxBars& bars,
+                                           long long row_lo, long long row_hi, long long& stage_it, int ptid) {
+    constexpr int D3 = OUT_D[O], RPC = 128 / D3, MW = OUT_MUL[O], KB = dx_kblocks(O);
+    constexpr int NPT = DX_PRODUCER_WARPS * 32;
+    bool ok = true;
+    for (long long b0 = row_lo; b0 < row_hi && ok; b0 += RPC) {
+        const int rows = (int)(row_hi - b0 < RPC ? row_hi - b0 : RPC);
+        const int s = (int)(stage_it % DX_NA);
+        const long long use = stage_it / DX_NA;
+        if (use > 0) ok = mbar_wait(bars.empty + s, (unsigned)((use - 1) & 1), p.status, ERR_DX_EMPTY);
+        if (!ok) break;
+        unsigned char* st = smem + DX_OFF_A + s * DX_STAGE_BYTES;
+        // values: consecutive threads read consecutive (w, k) of a batch row
+        for (int item = ptid; item < RPC * MW * D3; item += NPT) {
+            const int r = item / (MW * D3), wk = item % (MW * D3);
+            const int w = wk / D3, k = wk % D3;
+            const float g = r < rows ? __ldg(p.dZ + (b0 + r) * (long long)Z_DIM + OUT_OFF[O] + wk) : 0.f;
+            unsigned char* hi = st + (w >> 5) * 2 * TB_TILE;
+            const int off = tc_swizzle(r * D3 + k, w & 31);
+            const float gh = tf32_hi(g);
+            *reinterpret_cast<float*>(hi + off) = gh;
+            *reinterpret_cast<float*>(hi + TB_TILE + off) = g - gh;
+        }
+        // padding: rows beyond RPC * D3 and columns beyond MW
+        constexpr int PAD_ROWS = 128 - RPC * D3, PAD_COLS = KB * 32 - MW;
+        if constexpr (PAD_ROWS > 0) {
+            for (int item = ptid; item < PAD_ROWS * KB * 32; item += NPT) {
+                const int row = RPC * D3 + item / (KB * 32), col = item % (KB * 32);
+                unsigned char* hi = st + (col >> 5) * 2 * TB_TILE;
+                const int off = tc_swizzle(row, col & 31);
+                *reinterpret_cast<float*>(hi + off) = 0.f;
+                *reinterpret_cast<float*>(hi + TB_TILE + off) = 0.f;
+            }
+        }
+        if constexpr (PAD_COLS > 0) {
+            for (int item = ptid; item < RPC * D3 * PAD_COLS; item += NPT) {
+                const int row = item / PAD_COLS, col = MW + item % PAD_COLS;
+                unsigned char* hi = st + (col >> 5) * 2 * TB_TILE;
+                const int off = tc_swizzle(row, col & 31);
+                *reinterpret_cast<float*>(hi + off) = 0.f;
+                *reinterpret_cast<float*>(hi + TB_TILE + off) = 0.f;
+            }
+        }
+        fence_async_smem();
+        __syncwarp();
+        if ((ptid & 31) == 0) mbar_arrive(bars.full + s);
+        ++stage_it;
+    }
+    return ok;
+}
+
+template <int P>
+__device__ __forceinline__ bool dx_mma(const UvwTcBwdParams& p, unsigned char* smem, const DxBars& bars, long long row_lo,
+                                       long long row_hi, long long& stage_it, long long& acc_it, int& w_use, unsigned tmem_base) {
+    constexpr int O = I_OUT[P], D3 = OUT_D[O], RPC = 128 / D3, KB = dx_kblocks(O), MUP = dx_mup(P);
+    constexpr unsigned IDESC = tc_instr_desc(MUP), IDESC_WIDE = tc_instr_desc(2 * MUP);
+    if (row_lo >= row_hi) return true;
+    // the weights of the previous path must not be overwritten while tensor cores still read them
+    if (w_use > 0) {
+        tc_commit(bars.w_free);
+        if (!mbar_wait(bars.w_free, (unsigned)((w_use - 1) & 1), p.status, ERR_DX_W)) return false;
+    }
+    mbar_arrive_expect_tx(bars.w_full, (unsigned)dx_wt_bytes(P));
+    {
+        const unsigned char* src = reinterpret_cast<const unsigned char*>(p.Wt) + dx_wt_offset(P);
+        constexpr int TOTAL = dx_wt_bytes(P);
+        for (int off = 0; off < TOTAL; off += 32768) {
+            const int n = TOTAL - off < 32768 ? TOTAL - off : 32768;
+            bulk_g2s(smem + DX_OFF_W + off, src + off, (unsigned)n, bars.w_full);
+        }
+    }
+    if (!mbar_wait(bars.w_full, (unsigned)(w_use & 1), p.status, ERR_DX_W)) return false;
+    ++w_use;
+    const unsigned long long a_desc0 = tc_smem_desc(smem_u32(smem + DX_OFF_A));
+    const unsigned long long w_desc0 = tc_smem_desc(smem_u32(smem + DX_OFF_W));
+    for (long long b0 = row_lo; b0 < row_hi; b0 += RPC) {
+        const int t = (int)(acc_it % DX_NACC);
+        const long long acc_use = acc_it / DX_NACC;
+        if (acc_use > 0 && !mbar_wait(bars.acc_empty + t, (unsigned)((acc_use - 1) & 1), p.status, ERR_DX_ACC_EMPTY)) return false;
+        const int s = (int)(stage_it % DX_NA);
+        const long long use = stage_it / DX_NA;
+        if (!mbar_wait(bars.full + s, (unsigned)(use & 1), p.status, ERR_DX_FULL)) return false;
+        tc_fence_after();
+        const unsigned tmem_d = tmem_base + (unsigned)(t * DX_ACC_COLS);
+        unsigned accumulate = 0;
+#pragma unroll
+        for (int kb = 0; kb < KB; ++kb) {
+            const unsigned long long da_hi = a_desc0 + (unsigned long long)((s * DX_STAGE_BYTES + kb * 2 * TB_TILE) >> 4);
+            const unsigned long long da_lo = da_hi + (TB_TILE >> 4);
+            const unsigned long long db = w_desc0 + (unsigned long long)((kb * 2 * MUP * 128) >> 4);   // hi rows, then lo rows
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+                tc_mma(tmem_d, da_hi + 2 * kk, db + 2 * kk, IDESC_WIDE, accumulate);   // [hi.hi | hi.lo]
+                accumulate = 1;
+                tc_mma(tmem_d, da_lo + 2 * kk, db + 2 * kk, IDESC, 1);                 // lo.hi into the first half
+            }
+        }
+        tc_commit(bars.empty + s);
+        tc_commit(bars.acc_full + t);
+        ++stage_it;
+        ++acc_it;
+    }
+    return true;
+}
+
+// AND-reduction of a flag over the epilogue warps (hardware barrier 1).
+__device__ __forceinline__ bool dx_epilogue_all(bool ok) {
+    unsigned r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 q, %1, 0;\n\t"
+        "bar.red.and.pred p, 1, %2, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(r)
+        : "r"((unsigned)ok), "n"(DX_EPILOGUE_WARPS * 32)
+        : "memory");
+    return r != 0;
+}
+
+template <int P>
+__device__ __forceinline__ bool dx_epilogue(const UvwTcBwdParams& p, unsigned char* smem, const DxBars& bars,
+                                            long long row_lo, long long row_hi, long long& acc_it, unsigned tmem_base,
+                                            int ewarp, int lane) {
+    constexpr int O = I_OUT[P], a = I_IN1[P], b = I_IN2[P];
+    constexpr int D1 = IN1_D[a], D2 = IN2_D[b], D3 = OUT_D[O], RPC = 128 / D3, MU = IN1_MUL[a], MUP = dx_mup(P);
+    float* stg = reinterpret_cast<float*>(smem + DX_OFF_STG);
+    // a warp may only read the TMEM lanes of its own quarter, 32 * (warp index in the CTA mod 4); the two
+    // warps of a quarter split the columns
+    const int quarter = (DX_WARP_MMA + 1 + ewarp) & 3, half = ewarp >> 2;
+    bool ok = true;
+    for (long long b0 = row_lo; b0 < row_hi && ok; b0 += RPC) {
+        const int rows = (int)(row_hi - b0 < RPC ? row_hi - b0 : RPC);
+        const int t = (int)(acc_it % DX_NACC);
+        const long long use = acc_it / DX_NACC;
+        ok = mbar_wait(bars.acc_full + t, (unsigned)(use & 1), p.status, ERR_DX_ACC_FULL);
+        ok = dx_epilogue_all(ok);          // the warps must agree before anyone touches the staging buffer
+        if (!ok) break;
+        tc_fence_after();
+        // accumulator row m = 32 * quarter + lane holds (row m / D3, component m % D3) for all u
+        const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(t * DX_ACC_COLS);
+#pragma unroll
+        for (int c0 = 0; c0 < MUP; c0 += 32) {
+            const int c = c0 + 16 * half;
+            if (c < MUP) {
+                unsigned v[16], v2[16];
+                tc_load16(taddr + (unsigned)c, v);
+                tc_load16(taddr + (unsigned)(MUP + c), v2);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int q = 0; q < 16; ++q)
+                    stg[(quarter * 32 + lane) * DX_STG_PITCH + c + q] = __uint_as_float(v[q]) + __uint_as_float(v2[q]);
+            }
+        }
+        tc_fence_before();
+        asm volatile("bar.sync 1, %0;" ::"n"(DX_EPILOGUE_WARPS * 32) : "memory");
+        if (ewarp == 0 && lane == 0) mbar_arrive(bars.acc_empty + t);   // the accumulator tile may be overwritten
+        // one warp per batch row, lanes over the channels: dX by the owning lane, dY reduced over the warp
+        for (int r = ewarp; r < rows; r += DX_EPILOGUE_WARPS) {
+            const float* xrow = p.X + (b0 + r) * (long long)X_DIM + IN1_OFF[a];
+            const float* yrow = p.Y + (b0 + r) * (long long)Y_DIM + IN2_OFF[b];
+            float* dxrow = p.dX + (b0 + r) * (long long)X_DIM + IN1_OFF[a];
+            float y[D2], dy[D2];
+#pragma unroll
+            for (int j = 0; j < D2; ++j) {
+                y[j] = __ldg(yrow + j);
+                dy[j] = 0.f;
+            }
+            for (int u = lane; u < MU; u += 32) {
+                float x[D1], dx[D1], g[D3];
+#pragma unroll
+                for (int i = 0; i < D1; ++i) {
+                    x[i] = __ldg(xrow + u * D1 + i);
+                    dx[i] = 0.f;
+                }
+#pragma unroll
+                for (int k = 0; k < D3; ++k) g[k] = stg[(r * D3 + k) * DX_STG_PITCH + u];
+                sfor<CG_BEGIN[P], CG_BEGIN[P + 1]>([&](auto n_) {
+                    constexpr int N = n_;
+                    const float cg = (float)CG_V[N] * g[CG_K[N]];
+                    dx[CG_I[N]] = fmaf(cg, y[CG_J[N]], dx[CG_I[N]]);
+                    dy[CG_J[N]] = fmaf(cg, x[CG_I[N]], dy[CG_J[N]]);
+                });
+#pragma unroll
+                for (int i = 0; i < D1; ++i) dxrow[u * D1 + i] += dx[i];
+            }
+#pragma unroll
+            for (int j = 0; j < D2; ++j) {
+                float sum = dy[j];
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+                if (lane == 0) p.dY[(b0 + r) * (long long)Y_DIM + IN2_OFF[b] + j] += sum;
+            }
+        }
+        // the staging buffer is rewritten by the next tile, and the next path adds to the same dX / dY rows
+        __threadfence_block();
+        asm volatile("bar.sync 1, %0;" ::"n"(DX_EPILOGUE_WARPS * 32) : "memory");
+        ++acc_it;
+    }
+    return ok;
+}
+
+__device__ void uvw_tc_dxy(const UvwTcBwdParams& p) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    const DxBars bars(smem);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    long long row_lo, row_hi;
+    tb_row_range(p.batch, row_lo, row_hi);
+    if (tid == 0) {
+        for (int i = 0; i < DX_NA; ++i) {
+            mbar_init(bars.full + i, DX_PRODUCER_WARPS);
+            mbar_init(bars.empty + i, 1);
+        }
+        for (int i = 0; i < DX_NACC; ++i) {
+            mbar_init(bars.acc_full + i, 1);
+            mbar_init(bars.acc_empty + i, 1);
+        }
+        mbar_init(bars.w_full, 1);
+        mbar_init(bars.w_free, 1);
+        fence_mbar_init();
+    }
+    if (warp == DX_WARP_MMA) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(bars.tmem_slot)),
+                     "n"(512)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem_base = *reinterpret_cast<volatile unsigned*>(bars.tmem_slot);
+
+    if (warp < DX_PRODUCER_WARPS) {
+        long long stage_it = 0;
+        bool ok = true;
+        sfor<0, N_INSTR>([&](auto p_) {
+            constexpr int P = p_;
+            if (ok) ok = dx_produce<I_OUT[P]>(p, smem, bars, row_lo, row_hi, stage_it, tid);
+        });
+    } else if (warp == DX_WARP_MMA) {
+        if (lane == 0) {
+            long long stage_it = 0, acc_it = 0;
+            int w_use = 0;
+            bool ok = true;
+            sfor<0, N_INSTR>([&](auto p_) {
+                constexpr int P = p_;
+                if (ok) ok = dx_mma<P>(p, smem, bars, row_lo, row_hi, stage_it, acc_it, w_use, tmem_base);
+            });
+        }
+        __syncwarp();
+    } else {
+        long long acc_it = 0;
+        bool ok = true;
+        sfor<0, N_INSTR>([&](auto p_) {
+            constexpr int P = p_;
+            if (ok) ok = dx_epilogue<P>(p, smem, bars, row_lo, row_hi, acc_it, tmem_base, warp - DX_WARP_MMA - 1, lane);
+        });
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == DX_WARP_MMA) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "n"(512) : "memory");
+    }
+}
+
 }  // namespace oeq
 
 #define OEQ_K_UVW_TC_DW 21
+#define OEQ_K_UVW_TC_DXY 22
 
 #if OEQ_KERNEL == OEQ_K_UVW_TC_DW
 extern "C" __global__ void __launch_bounds__(oeq::TB_THREADS, 1) oeq_uvw_tc_dw_kernel(const oeq::UvwTcBwdParams p) {
     oeq::uvw_tc_dw(p);
+}
+#elif OEQ_KERNEL == OEQ_K_UVW_TC_DXY
+extern "C" __global__ void __launch_bounds__(oeq::DX_THREADS, 1) oeq_uvw_tc_dxy_kernel(const oeq::UvwTcBwdParams p) {
+    oeq::uvw_tc_dxy(p);
+}
+
+// Splits the shared weights into TF32 hi / lo parts, transposed for the dX/dY kernel: per path and per
+// 32-wide slice of w a [u rows x 32] K-major tile with the 128-byte swizzle for hi, followed by one for lo.
+// Rows of u beyond the multiplicity (up to a multiple of 16) and columns of w beyond the output multiplicity are zero.
+extern "C" __global__ void oeq_uvw_pack_weights_t(const float* __restrict__ W, float* __restrict__ packed) {
+    using namespace oeqd;
+    const int tid = blockIdx.x * blockDim.x + threadIdx.x, nthreads = gridDim.x * blockDim.x;
+    oeq::sfor<0, N_INSTR>([&](auto p_) {
+        constexpr int P = p_;
+        constexpr int O = I_OUT[P], MU = IN1_MUL[I_IN1[P]], MW = OUT_MUL[O];
+        constexpr int KB = oeq::dx_kblocks(O), MUP = oeq::dx_mup(P);
+        unsigned char* base = reinterpret_cast<unsigned char*>(packed) + oeq::dx_wt_offset(P);
+        for (int e = tid; e < KB * MUP * 32; e += nthreads) {
+            const int col = e & 31, u = (e >> 5) % MUP, kb = e / (32 * MUP);
+            const int w = kb * 32 + col;
+            const float v = (u < MU && w < MW) ? W[oeq::tb_weight_offset<P>(u, w)] : 0.f;
+            const float hi = oeq::tf32_round(v), lo = oeq::tf32_round(v - hi);
+            unsigned char* blk = base + kb * 2 * MUP * 128;
+            *reinterpret_cast<float*>(blk + oeq::tc_swizzle(u, col)) = hi;
+            *reinterpret_cast<float*>(blk + MUP * 128 + oeq::tc_swizzle(u, col)) = lo;
+        }
+    });
 }
 #endif
 
