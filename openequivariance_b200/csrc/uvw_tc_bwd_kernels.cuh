@@ -132,41 +132,67 @@ __device__ __forceinline__ bool dw_produce(const UvwTcBwdParams& p, unsigned cha
         unsigned char* a_lo = a_hi + TB_TILE;
         unsigned char* b_hi = a_lo + TB_TILE;
         unsigned char* b_lo = b_hi + MW * 128;          // the lo tile follows the hi tile: one descriptor spans both
-        // ---- A: T^T.  item = (row of the stage, slot row); a warp's 32 items share the path
-        for (int item = ptid; item < RB * 128; item += NPT) {
-            const int rr = item / 128, srow = item % 128;
-            const int which = srow / SLOT, u = srow % SLOT;
-            float t[D3];
-#pragma unroll
-            for (int k = 0; k < D3; ++k) t[k] = 0.f;
+        // ---- A: T^T.  A thread keeps its slot row (path, u) and walks the stage's batch rows rr0, rr0 + 4, ...;
+        // the global loads of a batch of rows go out together, so that their latency is paid once per batch
+        {
+            static_assert(NPT % 128 == 0, "a thread must keep its slot row");
+            constexpr int STEP = NPT / 128, NI = (RB + STEP - 1) / STEP, NBATCH = NI < 4 ? NI : 4;
+            const int srow = ptid % 128, which = srow / SLOT, u = srow % SLOT, rr0 = ptid / 128;
+            bool done = false;
             sfor<0, PER>([&](auto j_) {
                 constexpr int P = tb_nth_path(O, GRP * PER + j_);
                 if constexpr (P >= 0) {
                     constexpr int a = I_IN1[P], b = I_IN2[P], D1 = IN1_D[a], D2 = IN2_D[b], MU = IN1_MUL[a];
-                    if (which == j_ && u < MU && rr < rows) {
-                        const float* xrow = p.X + (b0 + rr) * (long long)X_DIM + IN1_OFF[a] + u * D1;
-                        const float* yrow = p.Y + (b0 + rr) * (long long)Y_DIM + IN2_OFF[b];
-                        float x[D1], y[D2];
+                    if (which == j_ && u < MU) {
+                        done = true;
+                        for (int q0 = 0; q0 < NI; q0 += NBATCH) {
+                            float x[NBATCH][D1], y[NBATCH][D2];
 #pragma unroll
-                        for (int i = 0; i < D1; ++i) x[i] = __ldg(xrow + i);
+                            for (int q = 0; q < NBATCH; ++q) {
+                                const int rr = rr0 + (q0 + q) * STEP;
+                                const bool live = rr < rows;
+                                const float* xrow = p.X + (b0 + (live ? rr : 0)) * (long long)X_DIM + IN1_OFF[a] + u * D1;
+                                const float* yrow = p.Y + (b0 + (live ? rr : 0)) * (long long)Y_DIM + IN2_OFF[b];
 #pragma unroll
-                        for (int j = 0; j < D2; ++j) y[j] = __ldg(yrow + j);
-                        float xy = 0.f;
-                        sfor<CG_BEGIN[P], CG_BEGIN[P + 1]>([&](auto n_) {
-                            constexpr int N = n_;
-                            if constexpr (N == CG_BEGIN[P] || CG_I[N] != CG_I[N - 1] || CG_J[N] != CG_J[N - 1])
-                                xy = x[CG_I[N]] * y[CG_J[N]];
-                            t[CG_K[N]] = fmaf(xy, (float)CG_V[N], t[CG_K[N]]);
-                        });
+                                for (int i = 0; i < D1; ++i) x[q][i] = live ? __ldg(xrow + i) : 0.f;
+#pragma unroll
+                                for (int j = 0; j < D2; ++j) y[q][j] = live ? __ldg(yrow + j) : 0.f;
+                            }
+#pragma unroll
+                            for (int q = 0; q < NBATCH; ++q) {
+                                const int rr = rr0 + (q0 + q) * STEP;
+                                if (rr < RB) {
+                                    float t[D3];
+#pragma unroll
+                                    for (int k = 0; k < D3; ++k) t[k] = 0.f;
+                                    float xy = 0.f;
+                                    sfor<CG_BEGIN[P], CG_BEGIN[P + 1]>([&](auto n_) {
+                                        constexpr int N = n_;
+                                        if constexpr (N == CG_BEGIN[P] || CG_I[N] != CG_I[N - 1] || CG_J[N] != CG_J[N - 1])
+                                            xy = x[q][CG_I[N]] * y[q][CG_J[N]];
+                                        t[CG_K[N]] = fmaf(xy, (float)CG_V[N], t[CG_K[N]]);
+                                    });
+#pragma unroll
+                                    for (int k = 0; k < D3; ++k) {
+                                        const int off = tc_swizzle(srow, rr * D3 + k);
+                                        const float th = tf32_hi(t[k]);
+                                        *reinterpret_cast<float*>(a_hi + off) = th;
+                                        *reinterpret_cast<float*>(a_lo + off) = t[k] - th;
+                                    }
+                                }
+                            }
+                        }
                     }
                 }
             });
+            if (!done) {      // no path in this slot, or a channel beyond its multiplicity: zero rows
+                for (int rr = rr0; rr < RB; rr += STEP)
 #pragma unroll
-            for (int k = 0; k < D3; ++k) {
-                const int off = tc_swizzle(srow, rr * D3 + k);
-                const float th = tf32_hi(t[k]);
-                *reinterpret_cast<float*>(a_hi + off) = th;
-                *reinterpret_cast<float*>(a_lo + off) = t[k] - th;
+                    for (int k = 0; k < D3; ++k) {
+                        const int off = tc_swizzle(srow, rr * D3 + k);
+                        *reinterpret_cast<float*>(a_hi + off) = 0.f;
+                        *reinterpret_cast<float*>(a_lo + off) = 0.f;
+                    }
             }
         }
         // columns beyond RB * D3 are padding
@@ -178,24 +204,39 @@ __device__ __forceinline__ bool dw_produce(const UvwTcBwdParams& p, unsigned cha
                 *reinterpret_cast<float*>(a_lo + off) = 0.f;
             }
         }
-        // ---- B: dZ^T.  consecutive threads read consecutive (w, k) of a batch row
-        for (int item = ptid; item < 32 * MW; item += NPT) {
-            int w, col;
-            float g = 0.f;
-            if (item < RB * MW * D3) {
-                const int rr = item / (MW * D3), wk = item % (MW * D3);
-                w = wk / D3;
-                col = rr * D3 + wk % D3;
-                if (rr < rows) g = __ldg(p.dZ + (b0 + rr) * (long long)Z_DIM + OUT_OFF[O] + wk);
-            } else {                                    // padding columns
-                const int e = item - RB * MW * D3;
-                w = e % MW;
-                col = RB * D3 + e / MW;
+        // ---- B: dZ^T.  consecutive threads read consecutive (w, k) of a batch row; loads first, then stores
+        {
+            constexpr int NBI = (32 * MW + NPT - 1) / NPT;
+            float g[NBI];
+#pragma unroll
+            for (int q = 0; q < NBI; ++q) {
+                const int item = ptid + q * NPT;
+                g[q] = 0.f;
+                if (item < RB * MW * D3) {
+                    const int rr = item / (MW * D3), wk = item % (MW * D3);
+                    if (rr < rows) g[q] = __ldg(p.dZ + (b0 + rr) * (long long)Z_DIM + OUT_OFF[O] + wk);
+                }
             }
-            const int off = tc_swizzle(w, col);
-            const float gh = tf32_hi(g);
-            *reinterpret_cast<float*>(b_hi + off) = gh;
-            *reinterpret_cast<float*>(b_lo + off) = g - gh;
+#pragma unroll
+            for (int q = 0; q < NBI; ++q) {
+                const int item = ptid + q * NPT;
+                if (item < 32 * MW) {
+                    int w, col;
+                    if (item < RB * MW * D3) {
+                        const int rr = item / (MW * D3), wk = item % (MW * D3);
+                        w = wk / D3;
+                        col = rr * D3 + wk % D3;
+                    } else {                                    // padding columns
+                        const int e = item - RB * MW * D3;
+                        w = e % MW;
+                        col = RB * D3 + e / MW;
+                    }
+                    const int off = tc_swizzle(w, col);
+                    const float gh = tf32_hi(g[q]);
+                    *reinterpret_cast<float*>(b_hi + off) = gh;
+                    *reinterpret_cast<float*>(b_lo + off) = g[q] - gh;
+                }
+            }
         }
         fence_async_smem();
         __syncwarp();
@@ -424,16 +465,29 @@ __device__ __forceinline__ bool dx_produce(const UvwTcBwdParams& p, unsigned cha
         if (use > 0) ok = mbar_wait(bars.empty + s, (unsigned)((use - 1) & 1), p.status, ERR_DX_EMPTY);
         if (!ok) break;
         unsigned char* st = smem + DX_OFF_A + s * DX_STAGE_BYTES;
-        // values: consecutive threads read consecutive (w, k) of a batch row
-        for (int item = ptid; item < RPC * MW * D3; item += NPT) {
-            const int r = item / (MW * D3), wk = item % (MW * D3);
-            const int w = wk / D3, k = wk % D3;
-            const float g = r < rows ? __ldg(p.dZ + (b0 + r) * (long long)Z_DIM + OUT_OFF[O] + wk) : 0.f;
-            unsigned char* hi = st + (w >> 5) * 2 * TB_TILE;
-            const int off = tc_swizzle(r * D3 + k, w & 31);
-            const float gh = tf32_hi(g);
-            *reinterpret_cast<float*>(hi + off) = gh;
-            *reinterpret_cast<float*>(hi + TB_TILE + off) = g - gh;
+        // values: consecutive threads read consecutive (w, k) of a batch row; 16 loads in flight per thread
+        constexpr int TOTAL = RPC * MW * D3, NBATCH = 16;
+        for (int base = 0; base < TOTAL; base += NBATCH * NPT) {
+            float g[NBATCH];
+#pragma unroll
+            for (int q = 0; q < NBATCH; ++q) {
+                const int item = base + q * NPT + ptid;
+                const int r = item / (MW * D3);
+                g[q] = (item < TOTAL && r < rows) ? __ldg(p.dZ + (b0 + r) * (long long)Z_DIM + OUT_OFF[O] + item % (MW * D3)) : 0.f;
+            }
+#pragma unroll
+            for (int q = 0; q < NBATCH; ++q) {
+                const int item = base + q * NPT + ptid;
+                if (item < TOTAL) {
+                    const int r = item / (MW * D3), wk = item % (MW * D3);
+                    const int w = wk / D3, k = wk % D3;
+                    unsigned char* hi = st + (w >> 5) * 2 * TB_TILE;
+                    const int off = tc_swizzle(r * D3 + k, w & 31);
+                    const float gh = tf32_hi(g[q]);
+                    *reinterpret_cast<float*>(hi + off) = gh;
+                    *reinterpret_cast<float*>(hi + TB_TILE + off) = g[q] - gh;
+                }
+            }
         }
         // padding: rows beyond RPC * D3 and columns beyond MW
         constexpr int PAD_ROWS = 128 - RPC * D3, PAD_COLS = KB * 32 - MW;
@@ -577,23 +631,36 @@ __device__ __forceinline__ bool dx_epilogue(const UvwTcBwdParams& p, unsigned ch
                 y[j] = __ldg(yrow + j);
                 dy[j] = 0.f;
             }
-            for (int u = lane; u < MU; u += 32) {
-                float x[D1], dx[D1], g[D3];
+            // two channel slices (u = lane + 32 v) per pass: their X values and old dX values are fetched together
+            constexpr int NU = (MU + 31) / 32;
+            for (int v0 = 0; v0 < NU; v0 += 2) {
+                float x[2][D1], old[2][D1], g[2][D3];
 #pragma unroll
-                for (int i = 0; i < D1; ++i) {
-                    x[i] = __ldg(xrow + u * D1 + i);
-                    dx[i] = 0.f;
+                for (int v = 0; v < 2; ++v) {
+                    const int u = lane + 32 * (v0 + v);
+                    const bool live = u < MU;
+#pragma unroll
+                    for (int i = 0; i < D1; ++i) {
+                        x[v][i] = live ? __ldg(xrow + u * D1 + i) : 0.f;
+                        old[v][i] = live ? dxrow[u * D1 + i] : 0.f;
+                    }
+#pragma unroll
+                    for (int k = 0; k < D3; ++k) g[v][k] = live ? stg[(r * D3 + k) * DX_STG_PITCH + u] : 0.f;
                 }
 #pragma unroll
-                for (int k = 0; k < D3; ++k) g[k] = stg[(r * D3 + k) * DX_STG_PITCH + u];
-                sfor<CG_BEGIN[P], CG_BEGIN[P + 1]>([&](auto n_) {
-                    constexpr int N = n_;
-                    const float cg = (float)CG_V[N] * g[CG_K[N]];
-                    dx[CG_I[N]] = fmaf(cg, y[CG_J[N]], dx[CG_I[N]]);
-                    dy[CG_J[N]] = fmaf(cg, x[CG_I[N]], dy[CG_J[N]]);
-                });
+                for (int v = 0; v < 2; ++v) {
+                    const int u = lane + 32 * (v0 + v);
+                    sfor<CG_BEGIN[P], CG_BEGIN[P + 1]>([&](auto n_) {
+                        constexpr int N = n_;
+                        const float cg = (float)CG_V[N] * g[v][CG_K[N]];
+                        old[v][CG_I[N]] = fmaf(cg, y[CG_J[N]], old[v][CG_I[N]]);
+                        dy[CG_J[N]] = fmaf(cg, x[v][CG_I[N]], dy[CG_J[N]]);
+                    });
+                    if (u < MU) {
 #pragma unroll
-                for (int i = 0; i < D1; ++i) dxrow[u * D1 + i] += dx[i];
+                        for (int i = 0; i < D1; ++i) dxrow[u * D1 + i] = old[v][i];
+                    }
+                }
             }
 #pragma unroll
             for (int j = 0; j < D2; ++j) {
