@@ -1297,7 +1297,7 @@ int oeq_tp_backward(oeq_tp* h, int64_t batch, const void* X, const void* Y, cons
             if ((size_t)dw_ctas * p.w_numel * p.elem() > workspace_bytes)
                 return fail(OEQ_ERR_INVALID, "workspace too small for the shared-weight gradient (see oeq_tp_workspace_bytes)");
             struct { const void* X; const void* Y; const void* Wt; const void* dZ; void* dX; void* dY; void* ws; long long batch;
-                     int* status; } tp{X, Y, nullptr, dZ, dX, dY, workspace, batch, h->d_status};
+                     int* status; unsigned long long* prof; } tp{X, Y, nullptr, dZ, dX, dY, workspace, batch, h->d_status, nullptr};
             void* targs[] = {&tp};
             OEQ_CUDA(cudaLaunchKernel((const void*)k.fn, dim3((unsigned)dw_ctas), dim3(21 * 32), targs, (size_t)k.smem, st));
             int n = p.w_numel;
@@ -1326,6 +1326,20 @@ int oeq_tp_backward(oeq_tp* h, int64_t batch, const void* X, const void* Y, cons
                 OEQ_CUDA(cudaMemsetAsync(dY, 0, (size_t)batch * p.y_dim * p.elem(), st));
                 tp.Wt = h->d_packed_t;
                 const long long ctas_x = std::max<long long>(1, std::min<long long>(kx.sm_count, (batch + 23) / 24));
+                if (env_int("OEQ_B200_TC_PROFILE", 0)) {
+                    // cycle accounting of the roles of CTA 0 (development aid): synchronous, prints to stderr
+                    OEQ_CUDA(cudaMalloc(&tp.prof, 32 * 8));
+                    OEQ_CUDA(cudaMemsetAsync(tp.prof, 0, 32 * 8, st));
+                    OEQ_CUDA(cudaLaunchKernel((const void*)kx.fn, dim3((unsigned)ctas_x), dim3(17 * 32), targs, (size_t)kx.smem, st));
+                    unsigned long long hb[32];
+                    OEQ_CUDA(cudaMemcpyAsync(hb, tp.prof, sizeof hb, cudaMemcpyDeviceToHost, st));
+                    OEQ_CUDA(cudaStreamSynchronize(st));
+                    cudaFree(tp.prof);
+                    fprintf(stderr, "[oeq_b200 uvw dxy profile] producer: stages %llu wait %llu fill %llu | mma: wait-acc %llu wait-full %llu "
+                                    "issue %llu | epilogue: wait %llu drain %llu rows %llu sync %llu\n", hb[2], hb[0], hb[1], hb[8], hb[9],
+                            hb[10], hb[16], hb[17], hb[18], hb[19]);
+                    return OEQ_OK;
+                }
                 OEQ_CUDA(cudaLaunchKernel((const void*)kx.fn, dim3((unsigned)ctas_x), dim3(17 * 32), targs, (size_t)kx.smem, st));
                 return OEQ_OK;
             }

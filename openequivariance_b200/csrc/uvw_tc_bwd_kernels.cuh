@@ -32,6 +32,7 @@ struct UvwTcBwdParams {
     float* ws;              // [gridDim.x][W_NUMEL] partial weight gradients (dW kernel)
     long long batch;
     int* status;
+    unsigned long long* prof;   // optional cycle accounting of CTA 0 (development aid), else null
 };
 
 constexpr int TB_PRODUCER_WARPS = 16;
@@ -462,30 +463,52 @@ __device__ __forceinline__ bool dx_produce(const UvwTcBwdParams& p, unsigned cha
         const int rows = (int)(row_hi - b0 < RPC ? row_hi - b0 : RPC);
         const int s = (int)(stage_it % DX_NA);
         const long long use = stage_it / DX_NA;
+        const bool prof = p.prof && blockIdx.x == 0 && ptid == 0;
+        const long long t0 = prof ? clock64() : 0;
         if (use > 0) ok = mbar_wait(bars.empty + s, (unsigned)((use - 1) & 1), p.status, ERR_DX_EMPTY);
+        const long long t1 = prof ? clock64() : 0;
         if (!ok) break;
         unsigned char* st = smem + DX_OFF_A + s * DX_STAGE_BYTES;
-        // values: consecutive threads read consecutive (w, k) of a batch row; 16 loads in flight per thread
-        constexpr int TOTAL = RPC * MW * D3, NBATCH = 16;
-        for (int base = 0; base < TOTAL; base += NBATCH * NPT) {
-            float g[NBATCH];
+        // values: a thread keeps its (w, k) positions of a batch row and walks the rows, eight rows of loads
+        // in flight at a time (consecutive threads read consecutive addresses)
+        {
+            constexpr int ROWLEN = MW * D3, NJ = (ROWLEN + NPT - 1) / NPT, RBATCH = 8;
+            int kk_[NJ], tile_[NJ], chunk_[NJ], within_[NJ];
 #pragma unroll
-            for (int q = 0; q < NBATCH; ++q) {
-                const int item = base + q * NPT + ptid;
-                const int r = item / (MW * D3);
-                g[q] = (item < TOTAL && r < rows) ? __ldg(p.dZ + (b0 + r) * (long long)Z_DIM + OUT_OFF[O] + item % (MW * D3)) : 0.f;
+            for (int j = 0; j < NJ; ++j) {
+                const int wk = ptid + j * NPT, w = wk / D3;
+                kk_[j] = wk % D3;
+                tile_[j] = (w >> 5) * 2 * TB_TILE;
+                chunk_[j] = (w & 31) >> 2;
+                within_[j] = (w & 3) << 2;
             }
+            for (int r0 = 0; r0 < RPC; r0 += RBATCH) {
+                float g[RBATCH][NJ];
 #pragma unroll
-            for (int q = 0; q < NBATCH; ++q) {
-                const int item = base + q * NPT + ptid;
-                if (item < TOTAL) {
-                    const int r = item / (MW * D3), wk = item % (MW * D3);
-                    const int w = wk / D3, k = wk % D3;
-                    unsigned char* hi = st + (w >> 5) * 2 * TB_TILE;
-                    const int off = tc_swizzle(r * D3 + k, w & 31);
-                    const float gh = tf32_hi(g[q]);
-                    *reinterpret_cast<float*>(hi + off) = gh;
-                    *reinterpret_cast<float*>(hi + TB_TILE + off) = g[q] - gh;
+                for (int rr = 0; rr < RBATCH; ++rr) {
+                    const int r = r0 + rr;
+                    const float* src = p.dZ + (b0 + r) * (long long)Z_DIM + OUT_OFF[O];
+#pragma unroll
+                    for (int j = 0; j < NJ; ++j) {
+                        const int wk = ptid + j * NPT;
+                        g[rr][j] = (r < rows && wk < ROWLEN) ? __ldg(src + wk) : 0.f;
+                    }
+                }
+#pragma unroll
+                for (int rr = 0; rr < RBATCH; ++rr) {
+                    const int r = r0 + rr;
+#pragma unroll
+                    for (int j = 0; j < NJ; ++j) {
+                        const int wk = ptid + j * NPT;
+                        if (r < RPC && wk < ROWLEN) {
+                            const int row = r * D3 + kk_[j];
+                            const int off = (row >> 3) * 1024 + (row & 7) * 128 + (((chunk_[j] ^ (row & 7)) & 7) << 4) + within_[j];
+                            unsigned char* hi = st + tile_[j];
+                            const float gh = tf32_hi(g[rr][j]);
+                            *reinterpret_cast<float*>(hi + off) = gh;
+                            *reinterpret_cast<float*>(hi + TB_TILE + off) = g[rr][j] - gh;
+                        }
+                    }
                 }
             }
         }
@@ -512,6 +535,11 @@ __device__ __forceinline__ bool dx_produce(const UvwTcBwdParams& p, unsigned cha
         fence_async_smem();
         __syncwarp();
         if ((ptid & 31) == 0) mbar_arrive(bars.full + s);
+        if (prof) {
+            atomicAdd(p.prof + 0, (unsigned long long)(t1 - t0));
+            atomicAdd(p.prof + 1, (unsigned long long)(clock64() - t1));
+            atomicAdd(p.prof + 2, 1ull);
+        }
         ++stage_it;
     }
     return ok;
@@ -544,10 +572,14 @@ __device__ __forceinline__ bool dx_mma(const UvwTcBwdParams& p, unsigned char* s
     for (long long b0 = row_lo; b0 < row_hi; b0 += RPC) {
         const int t = (int)(acc_it % DX_NACC);
         const long long acc_use = acc_it / DX_NACC;
+        const bool prof = p.prof && blockIdx.x == 0;
+        const long long t0 = prof ? clock64() : 0;
         if (acc_use > 0 && !mbar_wait(bars.acc_empty + t, (unsigned)((acc_use - 1) & 1), p.status, ERR_DX_ACC_EMPTY)) return false;
+        const long long t1 = prof ? clock64() : 0;
         const int s = (int)(stage_it % DX_NA);
         const long long use = stage_it / DX_NA;
         if (!mbar_wait(bars.full + s, (unsigned)(use & 1), p.status, ERR_DX_FULL)) return false;
+        const long long t2 = prof ? clock64() : 0;
         tc_fence_after();
         const unsigned tmem_d = tmem_base + (unsigned)(t * DX_ACC_COLS);
         unsigned accumulate = 0;
@@ -565,6 +597,11 @@ __device__ __forceinline__ bool dx_mma(const UvwTcBwdParams& p, unsigned char* s
         }
         tc_commit(bars.empty + s);
         tc_commit(bars.acc_full + t);
+        if (prof) {
+            atomicAdd(p.prof + 8, (unsigned long long)(t1 - t0));
+            atomicAdd(p.prof + 9, (unsigned long long)(t2 - t1));
+            atomicAdd(p.prof + 10, (unsigned long long)(clock64() - t2));
+        }
         ++stage_it;
         ++acc_it;
     }
@@ -598,8 +635,11 @@ __device__ __forceinline__ bool dx_epilogue(const UvwTcBwdParams& p, unsigned ch
         const int rows = (int)(row_hi - b0 < RPC ? row_hi - b0 : RPC);
         const int t = (int)(acc_it % DX_NACC);
         const long long use = acc_it / DX_NACC;
+        const bool prof = p.prof && blockIdx.x == 0 && ewarp == 0 && lane == 0;
+        const long long t0 = prof ? clock64() : 0;
         ok = mbar_wait(bars.acc_full + t, (unsigned)(use & 1), p.status, ERR_DX_ACC_FULL);
         ok = dx_epilogue_all(ok);          // the warps must agree before anyone touches the staging buffer
+        const long long t1 = prof ? clock64() : 0;
         if (!ok) break;
         tc_fence_after();
         // accumulator row m = 32 * quarter + lane holds (row m / D3, component m % D3) for all u
@@ -620,59 +660,87 @@ __device__ __forceinline__ bool dx_epilogue(const UvwTcBwdParams& p, unsigned ch
         tc_fence_before();
         asm volatile("bar.sync 1, %0;" ::"n"(DX_EPILOGUE_WARPS * 32) : "memory");
         if (ewarp == 0 && lane == 0) mbar_arrive(bars.acc_empty + t);   // the accumulator tile may be overwritten
-        // one warp per batch row, lanes over the channels: dX by the owning lane, dY reduced over the warp
-        for (int r = ewarp; r < rows; r += DX_EPILOGUE_WARPS) {
-            const float* xrow = p.X + (b0 + r) * (long long)X_DIM + IN1_OFF[a];
-            const float* yrow = p.Y + (b0 + r) * (long long)Y_DIM + IN2_OFF[b];
-            float* dxrow = p.dX + (b0 + r) * (long long)X_DIM + IN1_OFF[a];
-            float y[D2], dy[D2];
-#pragma unroll
-            for (int j = 0; j < D2; ++j) {
-                y[j] = __ldg(yrow + j);
-                dy[j] = 0.f;
-            }
-            // two channel slices (u = lane + 32 v) per pass: their X values and old dX values are fetched together
+        const long long t2 = prof ? clock64() : 0;
+        // one warp per batch row, lanes over the channels: dX by the owning lane, dY reduced over the warp.
+        // The global values of the warp's next row (X, Y and the running dX, dY) are fetched before the current
+        // row is computed and stored, so that their latency overlaps the arithmetic.
+        {
             constexpr int NU = (MU + 31) / 32;
-            for (int v0 = 0; v0 < NU; v0 += 2) {
-                float x[2][D1], old[2][D1], g[2][D3];
+            static_assert(NU <= 4, "first-input multiplicity above 128");
+            float yA[D2], oyA[D2], xA[NU][D1], oldA[NU][D1];
+            auto load_row = [&](int r, float (&y)[D2], float (&oy)[D2], float (&x)[NU][D1], float (&old)[NU][D1]) {
+                const float* xrow = p.X + (b0 + r) * (long long)X_DIM + IN1_OFF[a];
+                const float* yrow = p.Y + (b0 + r) * (long long)Y_DIM + IN2_OFF[b];
+                const float* dxrow = p.dX + (b0 + r) * (long long)X_DIM + IN1_OFF[a];
+                const float* dyrow = p.dY + (b0 + r) * (long long)Y_DIM + IN2_OFF[b];
 #pragma unroll
-                for (int v = 0; v < 2; ++v) {
-                    const int u = lane + 32 * (v0 + v);
-                    const bool live = u < MU;
-#pragma unroll
-                    for (int i = 0; i < D1; ++i) {
-                        x[v][i] = live ? __ldg(xrow + u * D1 + i) : 0.f;
-                        old[v][i] = live ? dxrow[u * D1 + i] : 0.f;
-                    }
-#pragma unroll
-                    for (int k = 0; k < D3; ++k) g[v][k] = live ? stg[(r * D3 + k) * DX_STG_PITCH + u] : 0.f;
+                for (int j = 0; j < D2; ++j) {
+                    y[j] = __ldg(yrow + j);
+                    oy[j] = lane == 0 ? dyrow[j] : 0.f;
                 }
 #pragma unroll
-                for (int v = 0; v < 2; ++v) {
-                    const int u = lane + 32 * (v0 + v);
+                for (int v = 0; v < NU; ++v) {
+                    const int u = lane + 32 * v;
+#pragma unroll
+                    for (int i = 0; i < D1; ++i) {
+                        x[v][i] = u < MU ? __ldg(xrow + u * D1 + i) : 0.f;
+                        old[v][i] = u < MU ? dxrow[u * D1 + i] : 0.f;
+                    }
+                }
+            };
+            if (ewarp < rows) load_row(ewarp, yA, oyA, xA, oldA);
+            for (int r = ewarp; r < rows; r += DX_EPILOGUE_WARPS) {
+                float yB[D2], oyB[D2], xB[NU][D1], oldB[NU][D1];
+                const int rn = r + DX_EPILOGUE_WARPS;
+                if (rn < rows) load_row(rn, yB, oyB, xB, oldB);
+                float dy[D2];
+#pragma unroll
+                for (int j = 0; j < D2; ++j) dy[j] = 0.f;
+                float* dxrow = p.dX + (b0 + r) * (long long)X_DIM + IN1_OFF[a];
+#pragma unroll
+                for (int v = 0; v < NU; ++v) {
+                    const int u = lane + 32 * v;
+                    float g[D3];
+#pragma unroll
+                    for (int k = 0; k < D3; ++k) g[k] = u < MU ? stg[(r * D3 + k) * DX_STG_PITCH + u] : 0.f;
                     sfor<CG_BEGIN[P], CG_BEGIN[P + 1]>([&](auto n_) {
                         constexpr int N = n_;
-                        const float cg = (float)CG_V[N] * g[v][CG_K[N]];
-                        old[v][CG_I[N]] = fmaf(cg, y[CG_J[N]], old[v][CG_I[N]]);
-                        dy[CG_J[N]] = fmaf(cg, x[v][CG_I[N]], dy[CG_J[N]]);
+                        const float cg = (float)CG_V[N] * g[CG_K[N]];
+                        oldA[v][CG_I[N]] = fmaf(cg, yA[CG_J[N]], oldA[v][CG_I[N]]);
+                        dy[CG_J[N]] = fmaf(cg, xA[v][CG_I[N]], dy[CG_J[N]]);
                     });
                     if (u < MU) {
 #pragma unroll
-                        for (int i = 0; i < D1; ++i) dxrow[u * D1 + i] = old[v][i];
+                        for (int i = 0; i < D1; ++i) dxrow[u * D1 + i] = oldA[v][i];
                     }
                 }
-            }
 #pragma unroll
-            for (int j = 0; j < D2; ++j) {
-                float sum = dy[j];
+                for (int j = 0; j < D2; ++j) {
+                    float sum = dy[j];
 #pragma unroll
-                for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
-                if (lane == 0) p.dY[(b0 + r) * (long long)Y_DIM + IN2_OFF[b] + j] += sum;
+                    for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+                    if (lane == 0) p.dY[(b0 + r) * (long long)Y_DIM + IN2_OFF[b] + j] = oyA[j] + sum;
+                }
+                if (rn < rows) {
+#pragma unroll
+                    for (int j = 0; j < D2; ++j) { yA[j] = yB[j]; oyA[j] = oyB[j]; }
+#pragma unroll
+                    for (int v = 0; v < NU; ++v)
+#pragma unroll
+                        for (int i = 0; i < D1; ++i) { xA[v][i] = xB[v][i]; oldA[v][i] = oldB[v][i]; }
+                }
             }
         }
         // the staging buffer is rewritten by the next tile, and the next path adds to the same dX / dY rows
+        const long long t3 = prof ? clock64() : 0;
         __threadfence_block();
         asm volatile("bar.sync 1, %0;" ::"n"(DX_EPILOGUE_WARPS * 32) : "memory");
+        if (prof) {
+            atomicAdd(p.prof + 16, (unsigned long long)(t1 - t0));
+            atomicAdd(p.prof + 17, (unsigned long long)(t2 - t1));
+            atomicAdd(p.prof + 18, (unsigned long long)(t3 - t2));
+            atomicAdd(p.prof + 19, (unsigned long long)(clock64() - t3));
+        }
         ++acc_it;
     }
     return ok;
