@@ -878,22 +878,27 @@ bool uvw_tc_bwd_geometry(const Problem& p, TcBwdGeometry& g) {
     if (stages < 2) return false;
     g.dw_smem = stages * stage + (2 * stages + 4) * 8 + 16 + 1024;
     if (g.dw_smem > SMEM_LIMIT) return false;
-    // dX/dY kernel: two A stages, one path's transposed weights, the epilogue staging buffer
+    // dX/dY kernel: one set of A tiles, the transposed weights of all paths into one output irrep, the
+    // epilogue staging buffer
     int kb_max = 1, mup_max = 16, wt_max = 0;
     size_t wt_total = 0;
     for (const Irrep& r : p.out) kb_max = std::max(kb_max, (r.mul + 31) / 32);
-    for (const Instr& t : p.instr) {
-        const int mup = (p.in1[t.i1].mul + 15) / 16 * 16;
-        const int bytes = ((p.out[t.io].mul + 31) / 32) * 2 * mup * 128;
-        mup_max = std::max(mup_max, mup);
-        wt_max = std::max(wt_max, bytes);
-        wt_total += bytes;
+    for (size_t o = 0; o < p.out.size(); ++o) {
+        int out_bytes = 0;
+        for (const Instr& t : p.instr)
+            if (t.io == (int)o) {
+                const int mup = (p.in1[t.i1].mul + 15) / 16 * 16;
+                mup_max = std::max(mup_max, mup);
+                out_bytes += ((p.out[o].mul + 31) / 32) * 2 * mup * 128;
+            }
+        wt_max = std::max(wt_max, out_bytes);
+        wt_total += out_bytes;
     }
     const int nacc = std::min(4, 512 / (2 * mup_max));
-    const int off_w = 2 * kb_max * 2 * 128 * 128;
+    const int off_w = kb_max * 2 * 128 * 128;
     const int off_stg = off_w + (wt_max + 1023) / 1024 * 1024;
     const int off_bar = off_stg + (128 * (mup_max + 1) * 4 + 15) / 16 * 16;
-    const int dxy = off_bar + (2 * 2 + 2 * nacc + 2) * 8 + 16 + 1024;
+    const int dxy = off_bar + (2 * 1 + 2 * nacc + 2) * 8 + 16 + 1024;
     if (nacc >= 1 && dxy <= SMEM_LIMIT) {
         g.dxy_smem = dxy;
         g.wt_bytes = wt_total;
@@ -1330,17 +1335,17 @@ int oeq_tp_backward(oeq_tp* h, int64_t batch, const void* X, const void* Y, cons
                     // cycle accounting of the roles of CTA 0 (development aid): synchronous, prints to stderr
                     OEQ_CUDA(cudaMalloc(&tp.prof, 32 * 8));
                     OEQ_CUDA(cudaMemsetAsync(tp.prof, 0, 32 * 8, st));
-                    OEQ_CUDA(cudaLaunchKernel((const void*)kx.fn, dim3((unsigned)ctas_x), dim3(17 * 32), targs, (size_t)kx.smem, st));
+                    OEQ_CUDA(cudaLaunchKernel((const void*)kx.fn, dim3((unsigned)ctas_x), dim3(16 * 32), targs, (size_t)kx.smem, st));
                     unsigned long long hb[32];
                     OEQ_CUDA(cudaMemcpyAsync(hb, tp.prof, sizeof hb, cudaMemcpyDeviceToHost, st));
                     OEQ_CUDA(cudaStreamSynchronize(st));
                     cudaFree(tp.prof);
                     fprintf(stderr, "[oeq_b200 uvw dxy profile] producer: stages %llu wait %llu fill %llu | mma: wait-acc %llu wait-full %llu "
-                                    "issue %llu | epilogue: wait %llu drain %llu rows %llu sync %llu\n", hb[2], hb[0], hb[1], hb[8], hb[9],
-                            hb[10], hb[16], hb[17], hb[18], hb[19]);
+                                    "issue %llu | epilogue: wait %llu drain %llu rows %llu sync %llu | per row: n %llu compute %llu dy %llu\n", hb[2], hb[0], hb[1], hb[8], hb[9],
+                            hb[10], hb[16], hb[17], hb[18], hb[19], hb[26], hb[24], hb[25]);
                     return OEQ_OK;
                 }
-                OEQ_CUDA(cudaLaunchKernel((const void*)kx.fn, dim3((unsigned)ctas_x), dim3(17 * 32), targs, (size_t)kx.smem, st));
+                OEQ_CUDA(cudaLaunchKernel((const void*)kx.fn, dim3((unsigned)ctas_x), dim3(16 * 32), targs, (size_t)kx.smem, st));
                 return OEQ_OK;
             }
         }

@@ -400,15 +400,17 @@ __device__ void uvw_tc_dw(const UvwTcBwdParams& p) {
 }
 
 // =====================================================================================================
-// dX / dY kernel.  Per output irrep o, path p into o (its weights W_p^T resident in shared memory as the
-// B operand, [u rows x w], hi tile followed by lo tile per 32-wide slice of w) and chunk of
-// RPC = floor(128 / (2l+1)) batch rows: D[(row,k), u] = sum_w dZ[row,o,w,k] W_p[u,w] on the tensor cores,
-// A = dZ gathered as [(row,k) x w] tiles.  The epilogue warps turn D (= dT) into dX and dY with the
+// dX / dY kernel.  Per output irrep o (the weights W_p^T of all paths into o resident in shared memory as B
+// operands, [u rows x w], hi tile followed by lo tile per 32-wide slice of w), chunk of
+// RPC = floor(128 / (2l+1)) batch rows (A = dZ gathered once as [(row,k) x w] tiles) and path p into o:
+// D[(row,k), u] = sum_w dZ[row,o,w,k] W_p[u,w] on the tensor cores.  The epilogue warps turn D (= dT) into dX and dY with the
 // Clebsch-Gordan coefficients unrolled; dX and dY are cleared by the host and accumulated path by path by
 // the CTA that owns the rows, in a fixed order.
 // =====================================================================================================
-constexpr int DX_PRODUCER_WARPS = 8;
-constexpr int DX_EPILOGUE_WARPS = 8;
+constexpr int DX_PRODUCER_WARPS = 3;        // one fill per chunk serves all paths into the output irrep; 16 warps in
+                                            // all leave 128 registers per thread for the epilogue's prefetch
+constexpr int DX_EPILOGUE_WARPS = 12;       // the per-row arithmetic is what bounds the kernel
+constexpr int DX_SUB = DX_EPILOGUE_WARPS / 4;   // epilogue warps per TMEM lane quarter
 constexpr int DX_WARP_MMA = DX_PRODUCER_WARPS;
 constexpr int DX_THREADS = (DX_PRODUCER_WARPS + 1 + DX_EPILOGUE_WARPS) * 32;
 constexpr int ERR_DX_EMPTY = 41, ERR_DX_FULL = 42, ERR_DX_ACC_EMPTY = 43, ERR_DX_ACC_FULL = 44, ERR_DX_W = 45;
@@ -416,11 +418,24 @@ constexpr int ERR_DX_EMPTY = 41, ERR_DX_FULL = 42, ERR_DX_ACC_EMPTY = 43, ERR_DX
 constexpr int dx_mup(int p) { return (IN1_MUL[I_IN1[p]] + 15) / 16 * 16; }          // rows of the weight tile
 constexpr int dx_kblocks(int o) { return (OUT_MUL[o] + 31) / 32; }                   // 32-wide slices of w
 constexpr int dx_wt_bytes(int p) { return dx_kblocks(I_OUT[p]) * 2 * dx_mup(p) * 128; }
-constexpr int dx_wt_offset(int p_end) {        // byte offset of path p_end inside the packed transposed weights
+constexpr int dx_wt_out_bytes(int o) {         // all paths into o
     int b = 0;
-    for (int p = 0; p < p_end; ++p) b += dx_wt_bytes(p);
+    for (int p = 0; p < N_INSTR; ++p)
+        if (I_OUT[p] == o) b += dx_wt_bytes(p);
     return b;
 }
+constexpr int dx_wt_out_offset(int o) {        // byte offset of output o's block inside the packed transposed weights
+    int b = 0;
+    for (int q = 0; q < o; ++q) b += dx_wt_out_bytes(q);
+    return b;
+}
+constexpr int dx_wt_local(int p_end) {         // byte offset of path p_end inside its output's block
+    int b = 0;
+    for (int p = 0; p < p_end; ++p)
+        if (I_OUT[p] == I_OUT[p_end]) b += dx_wt_bytes(p);
+    return b;
+}
+constexpr int dx_wt_offset(int p) { return dx_wt_out_offset(I_OUT[p]) + dx_wt_local(p); }
 constexpr int dx_max(int (*f)(int), int n) {
     int m = 0;
     for (int i = 0; i < n; ++i) m = f(i) > m ? f(i) : m;
@@ -428,9 +443,19 @@ constexpr int dx_max(int (*f)(int), int n) {
 }
 constexpr int DX_KB_MAX = dx_max(dx_kblocks, N_OUT);
 constexpr int DX_MUP_MAX = dx_max(dx_mup, N_INSTR);
-constexpr int DX_WT_MAX = dx_max(dx_wt_bytes, N_INSTR);
+constexpr int DX_WT_MAX = dx_max(dx_wt_out_bytes, N_OUT);
+// Rows are walked in blocks of DX_BLOCK rows, each taken through all output irreps and paths before the next,
+// so that a row's X, dX, dY and dZ values are still in cache when the next path needs them (every row is
+// visited once per path).  The block is a whole number of chunks of the widest output irrep.
+constexpr int dx_d3_max() {
+    int m = 1;
+    for (int o = 0; o < N_OUT; ++o)
+        if (tb_paths_into(o) > 0 && OUT_D[o] > m) m = OUT_D[o];
+    return m;
+}
+constexpr int DX_BLOCK = (128 / dx_d3_max()) * (128 / (128 / dx_d3_max()));
 constexpr int DX_STAGE_BYTES = DX_KB_MAX * 2 * TB_TILE;         // per 32-wide slice of w: hi tile, lo tile
-constexpr int DX_NA = 2;
+constexpr int DX_NA = 1;        // one set of A tiles: it serves all paths into the output irrep
 constexpr int DX_ACC_COLS = 2 * DX_MUP_MAX;                      // [hi.hi + lo.hi | hi.lo]
 constexpr int DX_NACC = 512 / DX_ACC_COLS < 4 ? 512 / DX_ACC_COLS : 4;
 constexpr int DX_STG_PITCH = DX_MUP_MAX + 1;
@@ -545,21 +570,20 @@ __device__ __forceinline__ bool dx_produce(const UvwTcBwdParams& p, unsigned cha
     return ok;
 }
 
-template <int P>
+template <int O>
 __device__ __forceinline__ bool dx_mma(const UvwTcBwdParams& p, unsigned char* smem, const DxBars& bars, long long row_lo,
                                        long long row_hi, long long& stage_it, long long& acc_it, int& w_use, unsigned tmem_base) {
-    constexpr int O = I_OUT[P], D3 = OUT_D[O], RPC = 128 / D3, KB = dx_kblocks(O), MUP = dx_mup(P);
-    constexpr unsigned IDESC = tc_instr_desc(MUP), IDESC_WIDE = tc_instr_desc(2 * MUP);
+    constexpr int D3 = OUT_D[O], RPC = 128 / D3, KB = dx_kblocks(O);
     if (row_lo >= row_hi) return true;
-    // the weights of the previous path must not be overwritten while tensor cores still read them
+    // the weights of the previous output irrep must not be overwritten while tensor cores still read them
     if (w_use > 0) {
         tc_commit(bars.w_free);
         if (!mbar_wait(bars.w_free, (unsigned)((w_use - 1) & 1), p.status, ERR_DX_W)) return false;
     }
-    mbar_arrive_expect_tx(bars.w_full, (unsigned)dx_wt_bytes(P));
+    mbar_arrive_expect_tx(bars.w_full, (unsigned)dx_wt_out_bytes(O));
     {
-        const unsigned char* src = reinterpret_cast<const unsigned char*>(p.Wt) + dx_wt_offset(P);
-        constexpr int TOTAL = dx_wt_bytes(P);
+        const unsigned char* src = reinterpret_cast<const unsigned char*>(p.Wt) + dx_wt_out_offset(O);
+        constexpr int TOTAL = dx_wt_out_bytes(O);
         for (int off = 0; off < TOTAL; off += 32768) {
             const int n = TOTAL - off < 32768 ? TOTAL - off : 32768;
             bulk_g2s(smem + DX_OFF_W + off, src + off, (unsigned)n, bars.w_full);
@@ -569,43 +593,58 @@ __device__ __forceinline__ bool dx_mma(const UvwTcBwdParams& p, unsigned char* s
     ++w_use;
     const unsigned long long a_desc0 = tc_smem_desc(smem_u32(smem + DX_OFF_A));
     const unsigned long long w_desc0 = tc_smem_desc(smem_u32(smem + DX_OFF_W));
-    for (long long b0 = row_lo; b0 < row_hi; b0 += RPC) {
-        const int t = (int)(acc_it % DX_NACC);
-        const long long acc_use = acc_it / DX_NACC;
-        const bool prof = p.prof && blockIdx.x == 0;
-        const long long t0 = prof ? clock64() : 0;
-        if (acc_use > 0 && !mbar_wait(bars.acc_empty + t, (unsigned)((acc_use - 1) & 1), p.status, ERR_DX_ACC_EMPTY)) return false;
-        const long long t1 = prof ? clock64() : 0;
+    bool ok = true;
+    for (long long b0 = row_lo; b0 < row_hi && ok; b0 += RPC) {
         const int s = (int)(stage_it % DX_NA);
         const long long use = stage_it / DX_NA;
+        const bool prof = p.prof && blockIdx.x == 0;
+        const long long t1 = prof ? clock64() : 0;
         if (!mbar_wait(bars.full + s, (unsigned)(use & 1), p.status, ERR_DX_FULL)) return false;
         const long long t2 = prof ? clock64() : 0;
         tc_fence_after();
-        const unsigned tmem_d = tmem_base + (unsigned)(t * DX_ACC_COLS);
-        unsigned accumulate = 0;
+        sfor<0, N_INSTR>([&](auto p_) {
+            constexpr int P = p_;
+            if constexpr (I_OUT[P] == O) {
+                constexpr int MUP = dx_mup(P);
+                constexpr unsigned IDESC = tc_instr_desc(MUP), IDESC_WIDE = tc_instr_desc(2 * MUP);
+                if (ok) {
+                    const int t = (int)(acc_it % DX_NACC);
+                    const long long acc_use = acc_it / DX_NACC;
+                    const long long t0 = prof ? clock64() : 0;
+                    if (acc_use > 0) ok = mbar_wait(bars.acc_empty + t, (unsigned)((acc_use - 1) & 1), p.status, ERR_DX_ACC_EMPTY);
+                    if (prof) atomicAdd(p.prof + 8, (unsigned long long)(clock64() - t0));
+                    if (ok) {
+                        tc_fence_after();
+                        const unsigned tmem_d = tmem_base + (unsigned)(t * DX_ACC_COLS);
+                        unsigned accumulate = 0;
 #pragma unroll
-        for (int kb = 0; kb < KB; ++kb) {
-            const unsigned long long da_hi = a_desc0 + (unsigned long long)((s * DX_STAGE_BYTES + kb * 2 * TB_TILE) >> 4);
-            const unsigned long long da_lo = da_hi + (TB_TILE >> 4);
-            const unsigned long long db = w_desc0 + (unsigned long long)((kb * 2 * MUP * 128) >> 4);   // hi rows, then lo rows
+                        for (int kb = 0; kb < KB; ++kb) {
+                            const unsigned long long da_hi = a_desc0 + (unsigned long long)((s * DX_STAGE_BYTES + kb * 2 * TB_TILE) >> 4);
+                            const unsigned long long da_lo = da_hi + (TB_TILE >> 4);
+                            // this path's tiles of the slice: hi rows, then lo rows
+                            const unsigned long long db = w_desc0 + (unsigned long long)((dx_wt_local(P) + kb * 2 * MUP * 128) >> 4);
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk) {
-                tc_mma(tmem_d, da_hi + 2 * kk, db + 2 * kk, IDESC_WIDE, accumulate);   // [hi.hi | hi.lo]
-                accumulate = 1;
-                tc_mma(tmem_d, da_lo + 2 * kk, db + 2 * kk, IDESC, 1);                 // lo.hi into the first half
+                            for (int kk = 0; kk < 4; ++kk) {
+                                tc_mma(tmem_d, da_hi + 2 * kk, db + 2 * kk, IDESC_WIDE, accumulate);   // [hi.hi | hi.lo]
+                                accumulate = 1;
+                                tc_mma(tmem_d, da_lo + 2 * kk, db + 2 * kk, IDESC, 1);                 // lo.hi into the first half
+                            }
+                        }
+                        tc_commit(bars.acc_full + t);
+                        ++acc_it;
+                    }
+                }
             }
-        }
-        tc_commit(bars.empty + s);
-        tc_commit(bars.acc_full + t);
+        });
+        if (!ok) return false;
+        tc_commit(bars.empty + s);        // the A tiles may be refilled once the MMAs of all paths have read them
         if (prof) {
-            atomicAdd(p.prof + 8, (unsigned long long)(t1 - t0));
             atomicAdd(p.prof + 9, (unsigned long long)(t2 - t1));
             atomicAdd(p.prof + 10, (unsigned long long)(clock64() - t2));
         }
         ++stage_it;
-        ++acc_it;
     }
-    return true;
+    return ok;
 }
 
 // AND-reduction of a flag over the epilogue warps (hardware barrier 1).
@@ -620,19 +659,19 @@ __device__ __forceinline__ bool dx_epilogue_all(bool ok) {
     return r != 0;
 }
 
+// One (chunk, path) unit: accumulator -> staging buffer -> dX, dY of the chunk's rows.
 template <int P>
-__device__ __forceinline__ bool dx_epilogue(const UvwTcBwdParams& p, unsigned char* smem, const DxBars& bars,
-                                            long long row_lo, long long row_hi, long long& acc_it, unsigned tmem_base,
-                                            int ewarp, int lane) {
+__device__ __forceinline__ bool dx_epilogue_unit(const UvwTcBwdParams& p, unsigned char* smem, const DxBars& bars,
+                                                 long long b0, int rows, long long& acc_it, unsigned tmem_base,
+                                                 int ewarp, int lane) {
     constexpr int O = I_OUT[P], a = I_IN1[P], b = I_IN2[P];
     constexpr int D1 = IN1_D[a], D2 = IN2_D[b], D3 = OUT_D[O], RPC = 128 / D3, MU = IN1_MUL[a], MUP = dx_mup(P);
     float* stg = reinterpret_cast<float*>(smem + DX_OFF_STG);
-    // a warp may only read the TMEM lanes of its own quarter, 32 * (warp index in the CTA mod 4); the two
-    // warps of a quarter split the columns
-    const int quarter = (DX_WARP_MMA + 1 + ewarp) & 3, half = ewarp >> 2;
+    // a warp may only read the TMEM lanes of its own quarter, 32 * (warp index in the CTA mod 4); the
+    // warps of a quarter split the columns in slices of 16
+    const int quarter = (DX_WARP_MMA + 1 + ewarp) & 3, sub = ewarp >> 2;
     bool ok = true;
-    for (long long b0 = row_lo; b0 < row_hi && ok; b0 += RPC) {
-        const int rows = (int)(row_hi - b0 < RPC ? row_hi - b0 : RPC);
+    {
         const int t = (int)(acc_it % DX_NACC);
         const long long use = acc_it / DX_NACC;
         const bool prof = p.prof && blockIdx.x == 0 && ewarp == 0 && lane == 0;
@@ -640,14 +679,14 @@ __device__ __forceinline__ bool dx_epilogue(const UvwTcBwdParams& p, unsigned ch
         ok = mbar_wait(bars.acc_full + t, (unsigned)(use & 1), p.status, ERR_DX_ACC_FULL);
         ok = dx_epilogue_all(ok);          // the warps must agree before anyone touches the staging buffer
         const long long t1 = prof ? clock64() : 0;
-        if (!ok) break;
+        if (!ok) return false;
         tc_fence_after();
         // accumulator row m = 32 * quarter + lane holds (row m / D3, component m % D3) for all u
         const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(t * DX_ACC_COLS);
 #pragma unroll
-        for (int c0 = 0; c0 < MUP; c0 += 32) {
-            const int c = c0 + 16 * half;
-            if (c < MUP) {
+        for (int c16 = 0; c16 < MUP / 16; ++c16) {
+            if (c16 % DX_SUB == sub) {
+                const int c = 16 * c16;
                 unsigned v[16], v2[16];
                 tc_load16(taddr + (unsigned)c, v);
                 tc_load16(taddr + (unsigned)(MUP + c), v2);
@@ -693,6 +732,7 @@ __device__ __forceinline__ bool dx_epilogue(const UvwTcBwdParams& p, unsigned ch
                 float yB[D2], oyB[D2], xB[NU][D1], oldB[NU][D1];
                 const int rn = r + DX_EPILOGUE_WARPS;
                 if (rn < rows) load_row(rn, yB, oyB, xB, oldB);
+                const long long tr0 = prof ? clock64() : 0;
                 float dy[D2];
 #pragma unroll
                 for (int j = 0; j < D2; ++j) dy[j] = 0.f;
@@ -714,12 +754,18 @@ __device__ __forceinline__ bool dx_epilogue(const UvwTcBwdParams& p, unsigned ch
                         for (int i = 0; i < D1; ++i) dxrow[u * D1 + i] = oldA[v][i];
                     }
                 }
+                const long long tr1 = prof ? clock64() : 0;
 #pragma unroll
                 for (int j = 0; j < D2; ++j) {
                     float sum = dy[j];
 #pragma unroll
                     for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
                     if (lane == 0) p.dY[(b0 + r) * (long long)Y_DIM + IN2_OFF[b] + j] = oyA[j] + sum;
+                }
+                if (prof) {
+                    atomicAdd(p.prof + 24, (unsigned long long)(tr1 - tr0));          // compute + dX stores
+                    atomicAdd(p.prof + 25, (unsigned long long)(clock64() - tr1));    // dY reduction + stores
+                    atomicAdd(p.prof + 26, 1ull);
                 }
                 if (rn < rows) {
 #pragma unroll
@@ -742,6 +788,24 @@ __device__ __forceinline__ bool dx_epilogue(const UvwTcBwdParams& p, unsigned ch
             atomicAdd(p.prof + 19, (unsigned long long)(clock64() - t3));
         }
         ++acc_it;
+    }
+    return ok;
+}
+
+template <int O>
+__device__ __forceinline__ bool dx_epilogue(const UvwTcBwdParams& p, unsigned char* smem, const DxBars& bars,
+                                            long long row_lo, long long row_hi, long long& acc_it, unsigned tmem_base,
+                                            int ewarp, int lane) {
+    constexpr int RPC = 128 / OUT_D[O];
+    bool ok = true;
+    for (long long b0 = row_lo; b0 < row_hi && ok; b0 += RPC) {
+        const int rows = (int)(row_hi - b0 < RPC ? row_hi - b0 : RPC);
+        sfor<0, N_INSTR>([&](auto p_) {
+            constexpr int P = p_;
+            if constexpr (I_OUT[P] == O) {
+                if (ok) ok = dx_epilogue_unit<P>(p, smem, bars, b0, rows, acc_it, tmem_base, ewarp, lane);
+            }
+        });
     }
     return ok;
 }
@@ -780,28 +844,43 @@ __device__ void uvw_tc_dxy(const UvwTcBwdParams& p) {
     if (warp < DX_PRODUCER_WARPS) {
         long long stage_it = 0;
         bool ok = true;
-        sfor<0, N_INSTR>([&](auto p_) {
-            constexpr int P = p_;
-            if (ok) ok = dx_produce<I_OUT[P]>(p, smem, bars, row_lo, row_hi, stage_it, tid);
-        });
+        for (long long blk = row_lo; blk < row_hi && ok; blk += DX_BLOCK) {
+            const long long blk_hi = blk + DX_BLOCK < row_hi ? blk + DX_BLOCK : row_hi;
+            sfor<0, N_OUT>([&](auto o_) {
+                constexpr int O = o_;
+                if constexpr (tb_paths_into(O) > 0) {
+                    if (ok) ok = dx_produce<O>(p, smem, bars, blk, blk_hi, stage_it, tid);
+                }
+            });
+        }
     } else if (warp == DX_WARP_MMA) {
         if (lane == 0) {
             long long stage_it = 0, acc_it = 0;
             int w_use = 0;
             bool ok = true;
-            sfor<0, N_INSTR>([&](auto p_) {
-                constexpr int P = p_;
-                if (ok) ok = dx_mma<P>(p, smem, bars, row_lo, row_hi, stage_it, acc_it, w_use, tmem_base);
-            });
+            for (long long blk = row_lo; blk < row_hi && ok; blk += DX_BLOCK) {
+                const long long blk_hi = blk + DX_BLOCK < row_hi ? blk + DX_BLOCK : row_hi;
+                sfor<0, N_OUT>([&](auto o_) {
+                    constexpr int O = o_;
+                    if constexpr (tb_paths_into(O) > 0) {
+                        if (ok) ok = dx_mma<O>(p, smem, bars, blk, blk_hi, stage_it, acc_it, w_use, tmem_base);
+                    }
+                });
+            }
         }
         __syncwarp();
     } else {
         long long acc_it = 0;
         bool ok = true;
-        sfor<0, N_INSTR>([&](auto p_) {
-            constexpr int P = p_;
-            if (ok) ok = dx_epilogue<P>(p, smem, bars, row_lo, row_hi, acc_it, tmem_base, warp - DX_WARP_MMA - 1, lane);
-        });
+        for (long long blk = row_lo; blk < row_hi && ok; blk += DX_BLOCK) {
+            const long long blk_hi = blk + DX_BLOCK < row_hi ? blk + DX_BLOCK : row_hi;
+            sfor<0, N_OUT>([&](auto o_) {
+                constexpr int O = o_;
+                if constexpr (tb_paths_into(O) > 0) {
+                    if (ok) ok = dx_epilogue<O>(p, smem, bars, blk, blk_hi, acc_it, tmem_base, warp - DX_WARP_MMA - 1, lane);
+                }
+            });
+        }
     }
     tc_fence_before();
     __syncthreads();
