@@ -17,6 +17,9 @@ sender nodes of a rank's edges that another rank owns.
   travel back to their owners (the mirrored all-to-all) and are added to the
   owners' rows peer by peer in rank order, so the result is reproducible.
 
+The batch tensor product shards by rows with no exchange at all; only a shared weight
+tensor's gradient is summed over the ranks (``ShardedTensorProduct``).
+
 With spatially ordered node ids the halo is a thin shell, so the exchanged
 volume is a small fraction of an all-gather of ``X``.  Collectives go through
 ``torch.distributed`` (NCCL on GPUs; gloo works for the host-side logic on CPU
@@ -194,3 +197,60 @@ class ShardedTensorProductConv:
         z = self.local_forward(x_local, y, w)
         dx_local, dy, dw = self.local_backward(x_local, y, w, dz)
         return z, self.scatter_sender_grads(dx_local), dy, dw
+
+
+# ---------------------------------------------------------------------------------------------------
+# batch tensor product: rows are independent
+
+
+def row_range(batch: int, rank: int, world: int):
+    """Rows ``[lo, hi)`` of a batch of ``batch`` rows that rank ``rank`` of ``world`` owns."""
+    if not (0 <= rank < world):
+        raise ValueError("rank out of range")
+    chunk = -(-batch // world) if batch else 0
+    return min(rank * chunk, batch), min((rank + 1) * chunk, batch)
+
+
+class _ShardedTPFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, module, x, y, w):
+        ctx.module = module
+        ctx.save_for_backward(x, y, w)
+        return module.tp._forward_impl(x, y, w)
+
+    @staticmethod
+    def backward(ctx, dz):
+        x, y, w = ctx.saved_tensors
+        dx, dy, dw = ctx.module.local_backward(x, y, w, dz.contiguous())
+        return None, dx, dy, dw
+
+
+class ShardedTensorProduct:
+    """Batch tensor product on this rank's rows of a batch that is split by rows over the ranks.
+
+    Forward and the input gradients need no communication.  With ``shared_weights`` every rank holds the
+    whole weight tensor and the weight gradient is the sum over all rows, so the local gradients are added
+    with one all-reduce (``weight_numel`` values).  ``local_tp`` may replace the CUDA tensor product by an
+    object with the same ``_forward_impl`` / ``_backward_impl`` (tests of the host logic).
+    """
+
+    def __init__(self, problem, group=None, local_tp=None):
+        self.problem = problem
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        if local_tp is None:
+            from .tensor_product import TensorProduct
+            local_tp = TensorProduct(problem, torch_op=True)
+        self.tp = local_tp
+
+    def local_backward(self, x, y, w, dz):
+        dx, dy, dw = self.tp._backward_impl(x, y, w, dz)
+        if self.problem.shared_weights and self.world > 1:
+            dist.all_reduce(dw, op=dist.ReduceOp.SUM, group=self.group)
+        return dx, dy, dw
+
+    def forward(self, x, y, w):
+        return _ShardedTPFn.apply(self, x, y, w)
+
+    __call__ = forward
+

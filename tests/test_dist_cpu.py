@@ -108,3 +108,80 @@ def test_two_rank_conv_matches_the_single_process_oracle(nodes):
         pr.join(timeout=240)
         assert pr.exitcode == 0
     assert len(result) == world and max(result.values()) < 1e-12
+
+
+# ---------------------------------------------------------------------------------------------------
+# batch tensor product sharded by rows
+
+
+class OracleLocalTP:
+    """Stand-in with the two methods the row-sharded layer calls on its local tensor product."""
+
+    def __init__(self, problem):
+        self.problem = problem
+
+    def _forward_impl(self, x, y, w):
+        return orc.tp_torch(self.problem, x, y, w)
+
+    def _backward_impl(self, x, y, w, dz):
+        with torch.enable_grad():
+            x, y, w = (t.detach().clone().requires_grad_(True) for t in (x, y, w))
+            self._forward_impl(x, y, w).backward(dz)
+        return x.grad, y.grad, w.grad
+
+
+def test_row_ranges_partition_the_batch():
+    from openequivariance_b200.dist import row_range
+    for batch in (0, 1, 7, 64, 1000):
+        for world in (1, 2, 3, 8):
+            ranges = [row_range(batch, r, world) for r in range(world)]
+            assert ranges[0][0] == 0 and ranges[-1][1] == batch
+            assert all(a[1] == b[0] for a, b in zip(ranges, ranges[1:]))
+            assert all(lo <= hi for lo, hi in ranges)
+    with pytest.raises(ValueError):
+        row_range(10, 2, 2)
+
+
+def _tp_worker(rank, world, port, batch, result):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from helpers import tp_inputs
+        from openequivariance_b200.dist import ShardedTensorProduct, row_range
+        out = {}
+        for name in ("uvw_small", "cw_mixed"):       # shared weights (all-reduce of dW) and per-row weights
+            p = problem_by_name(name, irrep_dtype=np.float64, weight_dtype=np.float64)
+            x, y, w, dz = (torch.from_numpy(a) for a in tp_inputs(p, batch, 5))
+            lo, hi = row_range(batch, rank, world)
+            tp = ShardedTensorProduct(p, local_tp=OracleLocalTP(p))
+            xs, ys = x[lo:hi].clone().requires_grad_(True), y[lo:hi].clone().requires_grad_(True)
+            ws = (w if p.shared_weights else w[lo:hi]).clone().requires_grad_(True)
+            z = tp(xs, ys, ws)
+            z.backward(dz[lo:hi])
+            out[name] = (lo, hi, z.detach(), xs.grad, ys.grad, ws.grad)
+        result[rank] = out
+    finally:
+        dist.destroy_process_group()
+
+
+def test_row_sharded_tensor_product_two_ranks():
+    from helpers import tp_inputs
+    batch, world = 37, 2
+    with mp.Manager() as manager:
+        result = manager.dict()
+        mp.spawn(_tp_worker, args=(world, 29533, batch, result), nprocs=world, join=True)
+        got = dict(result)
+    for name in ("uvw_small", "cw_mixed"):
+        p = problem_by_name(name, irrep_dtype=np.float64, weight_dtype=np.float64)
+        x, y, w, dz = (torch.from_numpy(a) for a in tp_inputs(p, batch, 5))
+        ref = OracleLocalTP(p)
+        z_ref = ref._forward_impl(x, y, w)
+        dx_ref, dy_ref, dw_ref = ref._backward_impl(x, y, w, dz)
+        for rank in range(world):
+            lo, hi, z, dx, dy, dw = got[rank][name]
+            assert rel_err(z.numpy(), z_ref[lo:hi].numpy()) < 1e-12
+            assert rel_err(dx.numpy(), dx_ref[lo:hi].numpy()) < 1e-12
+            assert rel_err(dy.numpy(), dy_ref[lo:hi].numpy()) < 1e-12
+            want = dw_ref if p.shared_weights else dw_ref[lo:hi]
+            assert rel_err(dw.numpy(), want.numpy()) < 1e-12       # every rank holds the full sum of a shared gradient
+
