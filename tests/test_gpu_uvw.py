@@ -111,6 +111,34 @@ def test_tensor_core_forward_matches_oracle_and_fma_path(in1, in2, out, batch, m
         assert torch.equal(z, tp(xt, yt, wt))
 
 
+@pytest.mark.parametrize("in1,in2,out,batch", TC_SHAPES + [s[:3] + (9_000,) for s in TC_SHAPES[1:3]],
+                         ids=[f"{s[2]}-{s[3]}" for s in TC_SHAPES] + [f"{s[2]}-9000" for s in TC_SHAPES[1:3]])
+def test_tensor_core_backward_matches_oracle_and_fma_path(in1, in2, out, batch, monkeypatch):
+    """Shared-weight FP32 problems run their backward pass on tcgen05 too (weight gradient; dX and dY):
+    same tolerance as the FMA kernel, padded multiplicities, ragged chunks, many chunks per CTA, and a
+    bit-reproducible weight gradient."""
+    p = oeq.FullyConnectedTPProblem(in1, in2, out)
+    tp = oeq.TensorProduct(p, torch_op=True)
+    x, y, w, dz = tp_inputs(p, batch, 29)
+    w = (w / np.sqrt(max(1, p.weight_numel / len(p.instructions)))).astype(np.float32)
+    xt, yt, wt, dzt = (torch.from_numpy(a).cuda() for a in (x, y, to_oeq(p, w), dz))
+    dx, dy, dw = tp.backward_helper(xt, yt, wt, dzt)
+    torch.cuda.synchronize()
+    tp.check_device_status()
+    rx, ry, rw = orc.tp_backward(p, x, y, w, dz)
+    assert rel_err(dx.cpu().numpy(), rx) < 1e-5
+    assert rel_err(dy.cpu().numpy(), ry) < 1e-5
+    assert rel_err(to_e3nn(p, dw.cpu().numpy()), rw) < 1e-5
+    for _ in range(2):
+        dx2, dy2, dw2 = tp.backward_helper(xt, yt, wt, dzt)
+        assert torch.equal(dw, dw2) and torch.equal(dx, dx2) and torch.equal(dy, dy2)
+    monkeypatch.setenv("OEQ_B200_UVW_TC_BWD", "0")
+    fma = oeq.TensorProduct(p, torch_op=True)
+    fx, fy, fw = fma.backward_helper(xt, yt, wt, dzt)
+    assert rel_err(fx.cpu().numpy(), rx) < 1e-5 and rel_err(fy.cpu().numpy(), ry) < 1e-5
+    assert rel_err(to_e3nn(p, fw.cpu().numpy()), rw) < 1e-5
+
+
 @pytest.mark.parametrize("in1,in2,out,batch", [s[:3] + (40_000,) for s in TC_SHAPES[1:3]], ids=[s[2] for s in TC_SHAPES[1:3]])
 def test_tensor_core_forward_many_tiles_mixed_multiplicities(in1, in2, out, batch, monkeypatch):
     """Every CTA walks many row chunks of every output irrep, so the accumulator ring wraps within and
