@@ -878,27 +878,25 @@ bool uvw_tc_bwd_geometry(const Problem& p, TcBwdGeometry& g) {
     if (stages < 2) return false;
     g.dw_smem = stages * stage + (2 * stages + 4) * 8 + 16 + 1024;
     if (g.dw_smem > SMEM_LIMIT) return false;
-    // dX/dY kernel: one set of A tiles, the transposed weights of all paths into one output irrep, the
-    // epilogue staging buffer
-    int kb_max = 1, mup_max = 16, wt_max = 0;
+    // dX/dY kernel: one set of A tiles, two buffers of one path's transposed weights, the epilogue staging
+    // buffer, one [channel][component] row per epilogue warp
+    int kb_max = 1, mup_max = 16, wt_max = 0, row_max = 0;
     size_t wt_total = 0;
     for (const Irrep& r : p.out) kb_max = std::max(kb_max, (r.mul + 31) / 32);
-    for (size_t o = 0; o < p.out.size(); ++o) {
-        int out_bytes = 0;
-        for (const Instr& t : p.instr)
-            if (t.io == (int)o) {
-                const int mup = (p.in1[t.i1].mul + 15) / 16 * 16;
-                mup_max = std::max(mup_max, mup);
-                out_bytes += ((p.out[o].mul + 31) / 32) * 2 * mup * 128;
-            }
-        wt_max = std::max(wt_max, out_bytes);
-        wt_total += out_bytes;
+    for (const Instr& t : p.instr) {
+        const int mup = (p.in1[t.i1].mul + 15) / 16 * 16;
+        const int bytes = ((p.out[t.io].mul + 31) / 32) * 2 * mup * 128;
+        mup_max = std::max(mup_max, mup);
+        wt_max = std::max(wt_max, bytes);
+        wt_total += bytes;
+        row_max = std::max(row_max, p.in1[t.i1].mul * p.in1[t.i1].dim);
     }
     const int nacc = std::min(4, 512 / (2 * mup_max));
     const int off_w = kb_max * 2 * 128 * 128;
-    const int off_stg = off_w + (wt_max + 1023) / 1024 * 1024;
-    const int off_bar = off_stg + (128 * (mup_max + 1) * 4 + 15) / 16 * 16;
-    const int dxy = off_bar + (2 * 1 + 2 * nacc + 2) * 8 + 16 + 1024;
+    const int off_stg = off_w + 2 * ((wt_max + 1023) / 1024 * 1024);
+    const int off_row = off_stg + (128 * (mup_max + 1) * 4 + 15) / 16 * 16;
+    const int off_bar = off_row + 12 * ((row_max * 4 + 15) / 16 * 16);
+    const int dxy = off_bar + (2 * 1 + 2 * nacc + 4) * 8 + 16 + 1024;
     if (nacc >= 1 && dxy <= SMEM_LIMIT) {
         g.dxy_smem = dxy;
         g.wt_bytes = wt_total;

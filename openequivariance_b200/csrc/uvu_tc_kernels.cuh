@@ -40,7 +40,7 @@ constexpr int UTC_CONSUMERS = 128 * UTC_PARTS;
 constexpr int UTC_CONSUMER_WARPS = UTC_CONSUMERS / 32;
 constexpr int UTC_WARP_STAGE = UTC_CONSUMER_WARPS, UTC_WARP_MMA = UTC_CONSUMER_WARPS + 1;
 constexpr int UTC_THREADS = UTC_CONSUMERS + 2 * 32;
-constexpr int ERR_UTC_A = 21, ERR_UTC_M = 22, ERR_UTC_DFREE = 23, ERR_UTC_D = 24, ERR_UTC_B = 25;
+constexpr int ERR_UTC_A = 21, ERR_UTC_DFREE = 23, ERR_UTC_D = 24;
 
 // ---- columns of the product: path p owns columns [TC_COL_BEGIN[p], TC_COL_BEGIN[p] + 2 l_out + 1); the paths
 // of consumer partition q are contiguous and start at TC_PART_COL[q], a multiple of 16 (tables from the host)
@@ -81,7 +81,6 @@ struct UtcCtrl {
     unsigned long long* full;      // [UTC_MAX_STAGES]  X and W rows of the stage have landed
     unsigned long long* empty;     // [UTC_MAX_STAGES]  consumers are done with the stage
     unsigned long long* a_ready;   // [2] A and B tiles written by the consumers
-    unsigned long long* m_ready;   // [2] (unused)
     unsigned long long* d_ready;   // [2] accumulator complete (and A, B tiles read)
     unsigned long long* d_free;    // [2] accumulator read by the consumers
     long long* hdr;                // [UTC_MAX_STAGES][4] edge, receiver, chunk node range markers
@@ -90,7 +89,7 @@ struct UtcCtrl {
     __device__ explicit UtcCtrl(unsigned char* smem) {
         unsigned long long* b = reinterpret_cast<unsigned long long*>(smem + UTC_OFF_CTRL);
         full = b; empty = b + UTC_MAX_STAGES;
-        a_ready = b + 2 * UTC_MAX_STAGES; m_ready = a_ready + 2; d_ready = m_ready + 2; d_free = d_ready + 2;
+        a_ready = b + 2 * UTC_MAX_STAGES; d_ready = a_ready + 2; d_free = d_ready + 2;
         hdr = reinterpret_cast<long long*>(d_free + 2);
         total = hdr + 4 * UTC_MAX_STAGES;
         tmem_slot = reinterpret_cast<unsigned*>(const_cast<long long*>(total) + 1);
@@ -436,7 +435,6 @@ __device__ void uvu_tc_forward(const UvuParams& p) {
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(c.a_ready + b, UTC_CONSUMER_WARPS);
-            mbar_init(c.m_ready + b, 1);
             mbar_init(c.d_ready + b, 1);
             mbar_init(c.d_free + b, UTC_CONSUMER_WARPS);
         }

@@ -400,9 +400,9 @@ __device__ void uvw_tc_dw(const UvwTcBwdParams& p) {
 }
 
 // =====================================================================================================
-// dX / dY kernel.  Per output irrep o (the weights W_p^T of all paths into o resident in shared memory as B
-// operands, [u rows x w], hi tile followed by lo tile per 32-wide slice of w), chunk of
-// RPC = floor(128 / (2l+1)) batch rows (A = dZ gathered once as [(row,k) x w] tiles) and path p into o:
+// dX / dY kernel.  Per output irrep o, chunk of RPC = floor(128 / (2l+1)) batch rows (A = dZ gathered once as
+// [(row,k) x w] tiles) and path p into o (its weights W_p^T as the B operand, [u rows x w], hi tile followed
+// by lo tile per 32-wide slice of w, double buffered in shared memory and fetched one path ahead):
 // D[(row,k), u] = sum_w dZ[row,o,w,k] W_p[u,w] on the tensor cores.  The epilogue warps turn D (= dT) into dX and dY with the
 // Clebsch-Gordan coefficients unrolled; dX and dY are cleared by the host and accumulated path by path by
 // the CTA that owns the rows, in a fixed order.
@@ -443,7 +443,9 @@ constexpr int dx_max(int (*f)(int), int n) {
 }
 constexpr int DX_KB_MAX = dx_max(dx_kblocks, N_OUT);
 constexpr int DX_MUP_MAX = dx_max(dx_mup, N_INSTR);
-constexpr int DX_WT_MAX = dx_max(dx_wt_out_bytes, N_OUT);
+constexpr int DX_WT_MAX = (dx_max(dx_wt_bytes, N_INSTR) + 1023) / 1024 * 1024;    // one path's tiles
+constexpr int dx_row_floats(int p) { return IN1_MUL[I_IN1[p]] * IN1_D[I_IN1[p]]; }
+constexpr int DX_ROWBUF = (dx_max(dx_row_floats, N_INSTR) * 4 + 15) / 16 * 16;       // one [channel][component] row
 // Rows are walked in blocks of DX_BLOCK rows, each taken through all output irreps and paths before the next,
 // so that a row's X, dX, dY and dZ values are still in cache when the next path needs them (every row is
 // visited once per path).  The block is a whole number of chunks of the widest output irrep.
@@ -461,9 +463,10 @@ constexpr int DX_NACC = 512 / DX_ACC_COLS < 4 ? 512 / DX_ACC_COLS : 4;
 constexpr int DX_STG_PITCH = DX_MUP_MAX + 1;
 constexpr int DX_OFF_A = 0;
 constexpr int DX_OFF_W = DX_OFF_A + DX_NA * DX_STAGE_BYTES;
-constexpr int DX_OFF_STG = DX_OFF_W + (DX_WT_MAX + 1023) / 1024 * 1024;
-constexpr int DX_OFF_BAR = DX_OFF_STG + (128 * DX_STG_PITCH * 4 + 15) / 16 * 16;
-constexpr int DX_SMEM_BYTES = DX_OFF_BAR + (2 * DX_NA + 2 * DX_NACC + 2) * 8 + 16 + 1024;
+constexpr int DX_OFF_STG = DX_OFF_W + 2 * DX_WT_MAX;
+constexpr int DX_OFF_ROW = DX_OFF_STG + (128 * DX_STG_PITCH * 4 + 15) / 16 * 16;
+constexpr int DX_OFF_BAR = DX_OFF_ROW + DX_EPILOGUE_WARPS * DX_ROWBUF;
+constexpr int DX_SMEM_BYTES = DX_OFF_BAR + (2 * DX_NA + 2 * DX_NACC + 4) * 8 + 16 + 1024;
 static_assert(DX_ACC_COLS <= 256, "first-input multiplicity above 128");
 
 struct DxBars {
@@ -472,8 +475,8 @@ struct DxBars {
     __device__ explicit DxBars(unsigned char* smem) {
         unsigned long long* b = reinterpret_cast<unsigned long long*>(smem + DX_OFF_BAR);
         full = b; empty = b + DX_NA; acc_full = b + 2 * DX_NA; acc_empty = acc_full + DX_NACC;
-        w_full = acc_empty + DX_NACC; w_free = w_full + 1;
-        tmem_slot = reinterpret_cast<unsigned*>(w_free + 1);
+        w_full = acc_empty + DX_NACC; w_free = w_full + 2;       // one pair per weight buffer
+        tmem_slot = reinterpret_cast<unsigned*>(w_free + 2);
     }
 };
 
@@ -570,30 +573,48 @@ __device__ __forceinline__ bool dx_produce(const UvwTcBwdParams& p, unsigned cha
     return ok;
 }
 
+constexpr int dx_next_path(int p) {            // next path into the same output irrep, cyclically
+    for (int q = p + 1; q < N_INSTR; ++q)
+        if (I_OUT[q] == I_OUT[p]) return q;
+    for (int q = 0; q < p; ++q)
+        if (I_OUT[q] == I_OUT[p]) return q;
+    return p;
+}
+constexpr int dx_last_path(int o) {
+    int last = -1;
+    for (int p = 0; p < N_INSTR; ++p)
+        if (I_OUT[p] == o) last = p;
+    return last;
+}
+
+// Start the copy of path P's weight tiles into weight buffer `buf` (after the MMAs that read its previous
+// contents are done).  w_cnt[buf] counts the copies into that buffer.
+template <int P>
+__device__ __forceinline__ bool dx_load_w(const UvwTcBwdParams& p, unsigned char* smem, const DxBars& bars, int buf,
+                                          long long (&w_cnt)[2]) {
+    const long long k = w_cnt[buf];
+    if (k > 0 && !mbar_wait(bars.w_free + buf, (unsigned)((k - 1) & 1), p.status, ERR_DX_W)) return false;
+    constexpr int TOTAL = dx_wt_bytes(P);
+    mbar_arrive_expect_tx(bars.w_full + buf, (unsigned)TOTAL);
+    const unsigned char* src = reinterpret_cast<const unsigned char*>(p.Wt) + dx_wt_offset(P);
+    for (int off = 0; off < TOTAL; off += 32768) {
+        const int n = TOTAL - off < 32768 ? TOTAL - off : 32768;
+        bulk_g2s(smem + DX_OFF_W + buf * DX_WT_MAX + off, src + off, (unsigned)n, bars.w_full + buf);
+    }
+    ++w_cnt[buf];
+    return true;
+}
+
 template <int O>
 __device__ __forceinline__ bool dx_mma(const UvwTcBwdParams& p, unsigned char* smem, const DxBars& bars, long long row_lo,
-                                       long long row_hi, long long& stage_it, long long& acc_it, int& w_use, unsigned tmem_base) {
+                                       long long row_hi, long long& stage_it, long long& acc_it, long long (&w_cnt)[2],
+                                       unsigned tmem_base) {
     constexpr int D3 = OUT_D[O], RPC = 128 / D3, KB = dx_kblocks(O);
     if (row_lo >= row_hi) return true;
-    // the weights of the previous output irrep must not be overwritten while tensor cores still read them
-    if (w_use > 0) {
-        tc_commit(bars.w_free);
-        if (!mbar_wait(bars.w_free, (unsigned)((w_use - 1) & 1), p.status, ERR_DX_W)) return false;
-    }
-    mbar_arrive_expect_tx(bars.w_full, (unsigned)dx_wt_out_bytes(O));
-    {
-        const unsigned char* src = reinterpret_cast<const unsigned char*>(p.Wt) + dx_wt_out_offset(O);
-        constexpr int TOTAL = dx_wt_out_bytes(O);
-        for (int off = 0; off < TOTAL; off += 32768) {
-            const int n = TOTAL - off < 32768 ? TOTAL - off : 32768;
-            bulk_g2s(smem + DX_OFF_W + off, src + off, (unsigned)n, bars.w_full);
-        }
-    }
-    if (!mbar_wait(bars.w_full, (unsigned)(w_use & 1), p.status, ERR_DX_W)) return false;
-    ++w_use;
     const unsigned long long a_desc0 = tc_smem_desc(smem_u32(smem + DX_OFF_A));
     const unsigned long long w_desc0 = tc_smem_desc(smem_u32(smem + DX_OFF_W));
     bool ok = true;
+    bool fetched = false;      // the weights of the coming unit are already on their way
     for (long long b0 = row_lo; b0 < row_hi && ok; b0 += RPC) {
         const int s = (int)(stage_it % DX_NA);
         const long long use = stage_it / DX_NA;
@@ -602,16 +623,23 @@ __device__ __forceinline__ bool dx_mma(const UvwTcBwdParams& p, unsigned char* s
         if (!mbar_wait(bars.full + s, (unsigned)(use & 1), p.status, ERR_DX_FULL)) return false;
         const long long t2 = prof ? clock64() : 0;
         tc_fence_after();
+        const bool last_chunk = b0 + RPC >= row_hi;
         sfor<0, N_INSTR>([&](auto p_) {
             constexpr int P = p_;
             if constexpr (I_OUT[P] == O) {
                 constexpr int MUP = dx_mup(P);
                 constexpr unsigned IDESC = tc_instr_desc(MUP), IDESC_WIDE = tc_instr_desc(2 * MUP);
                 if (ok) {
+                    const int wb = (int)(acc_it & 1);          // weight buffer of this unit
+                    if (!fetched) ok = dx_load_w<P>(p, smem, bars, wb, w_cnt);
+                    // the next unit's weights travel while this unit's MMAs run
+                    fetched = !(last_chunk && P == dx_last_path(O));
+                    if (ok && fetched) ok = dx_load_w<dx_next_path(P)>(p, smem, bars, wb ^ 1, w_cnt);
                     const int t = (int)(acc_it % DX_NACC);
                     const long long acc_use = acc_it / DX_NACC;
                     const long long t0 = prof ? clock64() : 0;
-                    if (acc_use > 0) ok = mbar_wait(bars.acc_empty + t, (unsigned)((acc_use - 1) & 1), p.status, ERR_DX_ACC_EMPTY);
+                    if (ok && acc_use > 0) ok = mbar_wait(bars.acc_empty + t, (unsigned)((acc_use - 1) & 1), p.status, ERR_DX_ACC_EMPTY);
+                    if (ok) ok = mbar_wait(bars.w_full + wb, (unsigned)((w_cnt[wb] - 1) & 1), p.status, ERR_DX_W);
                     if (prof) atomicAdd(p.prof + 8, (unsigned long long)(clock64() - t0));
                     if (ok) {
                         tc_fence_after();
@@ -622,7 +650,7 @@ __device__ __forceinline__ bool dx_mma(const UvwTcBwdParams& p, unsigned char* s
                             const unsigned long long da_hi = a_desc0 + (unsigned long long)((s * DX_STAGE_BYTES + kb * 2 * TB_TILE) >> 4);
                             const unsigned long long da_lo = da_hi + (TB_TILE >> 4);
                             // this path's tiles of the slice: hi rows, then lo rows
-                            const unsigned long long db = w_desc0 + (unsigned long long)((dx_wt_local(P) + kb * 2 * MUP * 128) >> 4);
+                            const unsigned long long db = w_desc0 + (unsigned long long)((wb * DX_WT_MAX + kb * 2 * MUP * 128) >> 4);
 #pragma unroll
                             for (int kk = 0; kk < 4; ++kk) {
                                 tc_mma(tmem_d, da_hi + 2 * kk, db + 2 * kk, IDESC_WIDE, accumulate);   // [hi.hi | hi.lo]
@@ -630,6 +658,7 @@ __device__ __forceinline__ bool dx_mma(const UvwTcBwdParams& p, unsigned char* s
                                 tc_mma(tmem_d, da_lo + 2 * kk, db + 2 * kk, IDESC, 1);                 // lo.hi into the first half
                             }
                         }
+                        tc_commit(bars.w_free + wb);
                         tc_commit(bars.acc_full + t);
                         ++acc_it;
                     }
@@ -700,14 +729,17 @@ __device__ __forceinline__ bool dx_epilogue_unit(const UvwTcBwdParams& p, unsign
         asm volatile("bar.sync 1, %0;" ::"n"(DX_EPILOGUE_WARPS * 32) : "memory");
         if (ewarp == 0 && lane == 0) mbar_arrive(bars.acc_empty + t);   // the accumulator tile may be overwritten
         const long long t2 = prof ? clock64() : 0;
-        // one warp per batch row, lanes over the channels: dX by the owning lane, dY reduced over the warp.
-        // The global values of the warp's next row (X, Y and the running dX, dY) are fetched before the current
-        // row is computed and stored, so that their latency overlaps the arithmetic.
+        // One warp per batch row, lanes over the channels: dX by the owning lane, dY reduced over the warp.
+        // X and dX rows are [channel][component]: read and written as contiguous floats (lane = flat index) and
+        // turned into per-channel values through the warp's own shared-memory row buffer, because a lane-per-
+        // channel access would touch 2l+1 times the sectors it uses.  The global values of the warp's next row
+        // are fetched before the current row is computed and stored, so that their latency overlaps the arithmetic.
         {
-            constexpr int NU = (MU + 31) / 32;
+            constexpr int NU = (MU + 31) / 32, ROW = MU * D1, NF = (ROW + 31) / 32;
             static_assert(NU <= 4, "first-input multiplicity above 128");
-            float yA[D2], oyA[D2], xA[NU][D1], oldA[NU][D1];
-            auto load_row = [&](int r, float (&y)[D2], float (&oy)[D2], float (&x)[NU][D1], float (&old)[NU][D1]) {
+            float* rowbuf = reinterpret_cast<float*>(smem + DX_OFF_ROW + ewarp * DX_ROWBUF);
+            float yA[D2], oyA[D2], xfA[NF], ofA[NF];
+            auto load_row = [&](int r, float (&y)[D2], float (&oy)[D2], float (&xf)[NF], float (&of)[NF]) {
                 const float* xrow = p.X + (b0 + r) * (long long)X_DIM + IN1_OFF[a];
                 const float* yrow = p.Y + (b0 + r) * (long long)Y_DIM + IN2_OFF[b];
                 const float* dxrow = p.dX + (b0 + r) * (long long)X_DIM + IN1_OFF[a];
@@ -718,25 +750,37 @@ __device__ __forceinline__ bool dx_epilogue_unit(const UvwTcBwdParams& p, unsign
                     oy[j] = lane == 0 ? dyrow[j] : 0.f;
                 }
 #pragma unroll
-                for (int v = 0; v < NU; ++v) {
-                    const int u = lane + 32 * v;
-#pragma unroll
-                    for (int i = 0; i < D1; ++i) {
-                        x[v][i] = u < MU ? __ldg(xrow + u * D1 + i) : 0.f;
-                        old[v][i] = u < MU ? dxrow[u * D1 + i] : 0.f;
-                    }
+                for (int q = 0; q < NF; ++q) {
+                    const int idx = lane + 32 * q;
+                    xf[q] = idx < ROW ? __ldg(xrow + idx) : 0.f;
+                    of[q] = idx < ROW ? dxrow[idx] : 0.f;
                 }
             };
-            if (ewarp < rows) load_row(ewarp, yA, oyA, xA, oldA);
             for (int r = ewarp; r < rows; r += DX_EPILOGUE_WARPS) {
-                float yB[D2], oyB[D2], xB[NU][D1], oldB[NU][D1];
-                const int rn = r + DX_EPILOGUE_WARPS;
-                if (rn < rows) load_row(rn, yB, oyB, xB, oldB);
+                load_row(r, yA, oyA, xfA, ofA);
                 const long long tr0 = prof ? clock64() : 0;
+                float x[NU][D1], old[NU][D1];
+#pragma unroll
+                for (int q = 0; q < NF; ++q)
+                    if (lane + 32 * q < ROW) rowbuf[lane + 32 * q] = xfA[q];
+                __syncwarp();
+#pragma unroll
+                for (int v = 0; v < NU; ++v)
+#pragma unroll
+                    for (int i = 0; i < D1; ++i) x[v][i] = lane + 32 * v < MU ? rowbuf[(lane + 32 * v) * D1 + i] : 0.f;
+                __syncwarp();
+#pragma unroll
+                for (int q = 0; q < NF; ++q)
+                    if (lane + 32 * q < ROW) rowbuf[lane + 32 * q] = ofA[q];
+                __syncwarp();
+#pragma unroll
+                for (int v = 0; v < NU; ++v)
+#pragma unroll
+                    for (int i = 0; i < D1; ++i) old[v][i] = lane + 32 * v < MU ? rowbuf[(lane + 32 * v) * D1 + i] : 0.f;
+                __syncwarp();
                 float dy[D2];
 #pragma unroll
                 for (int j = 0; j < D2; ++j) dy[j] = 0.f;
-                float* dxrow = p.dX + (b0 + r) * (long long)X_DIM + IN1_OFF[a];
 #pragma unroll
                 for (int v = 0; v < NU; ++v) {
                     const int u = lane + 32 * v;
@@ -746,14 +790,20 @@ __device__ __forceinline__ bool dx_epilogue_unit(const UvwTcBwdParams& p, unsign
                     sfor<CG_BEGIN[P], CG_BEGIN[P + 1]>([&](auto n_) {
                         constexpr int N = n_;
                         const float cg = (float)CG_V[N] * g[CG_K[N]];
-                        oldA[v][CG_I[N]] = fmaf(cg, yA[CG_J[N]], oldA[v][CG_I[N]]);
-                        dy[CG_J[N]] = fmaf(cg, xA[v][CG_I[N]], dy[CG_J[N]]);
+                        old[v][CG_I[N]] = fmaf(cg, yA[CG_J[N]], old[v][CG_I[N]]);
+                        dy[CG_J[N]] = fmaf(cg, x[v][CG_I[N]], dy[CG_J[N]]);
                     });
                     if (u < MU) {
 #pragma unroll
-                        for (int i = 0; i < D1; ++i) dxrow[u * D1 + i] = oldA[v][i];
+                        for (int i = 0; i < D1; ++i) rowbuf[u * D1 + i] = old[v][i];
                     }
                 }
+                __syncwarp();
+                float* dxrow = p.dX + (b0 + r) * (long long)X_DIM + IN1_OFF[a];
+#pragma unroll
+                for (int q = 0; q < NF; ++q)
+                    if (lane + 32 * q < ROW) dxrow[lane + 32 * q] = rowbuf[lane + 32 * q];
+                __syncwarp();
                 const long long tr1 = prof ? clock64() : 0;
 #pragma unroll
                 for (int j = 0; j < D2; ++j) {
@@ -766,14 +816,6 @@ __device__ __forceinline__ bool dx_epilogue_unit(const UvwTcBwdParams& p, unsign
                     atomicAdd(p.prof + 24, (unsigned long long)(tr1 - tr0));          // compute + dX stores
                     atomicAdd(p.prof + 25, (unsigned long long)(clock64() - tr1));    // dY reduction + stores
                     atomicAdd(p.prof + 26, 1ull);
-                }
-                if (rn < rows) {
-#pragma unroll
-                    for (int j = 0; j < D2; ++j) { yA[j] = yB[j]; oyA[j] = oyB[j]; }
-#pragma unroll
-                    for (int v = 0; v < NU; ++v)
-#pragma unroll
-                        for (int i = 0; i < D1; ++i) { xA[v][i] = xB[v][i]; oldA[v][i] = oldB[v][i]; }
                 }
             }
         }
@@ -826,8 +868,10 @@ __device__ void uvw_tc_dxy(const UvwTcBwdParams& p) {
             mbar_init(bars.acc_full + i, 1);
             mbar_init(bars.acc_empty + i, 1);
         }
-        mbar_init(bars.w_full, 1);
-        mbar_init(bars.w_free, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bars.w_full + i, 1);
+            mbar_init(bars.w_free + i, 1);
+        }
         fence_mbar_init();
     }
     if (warp == DX_WARP_MMA) {
@@ -856,14 +900,14 @@ __device__ void uvw_tc_dxy(const UvwTcBwdParams& p) {
     } else if (warp == DX_WARP_MMA) {
         if (lane == 0) {
             long long stage_it = 0, acc_it = 0;
-            int w_use = 0;
+            long long w_cnt[2] = {0, 0};
             bool ok = true;
             for (long long blk = row_lo; blk < row_hi && ok; blk += DX_BLOCK) {
                 const long long blk_hi = blk + DX_BLOCK < row_hi ? blk + DX_BLOCK : row_hi;
                 sfor<0, N_OUT>([&](auto o_) {
                     constexpr int O = o_;
                     if constexpr (tb_paths_into(O) > 0) {
-                        if (ok) ok = dx_mma<O>(p, smem, bars, blk, blk_hi, stage_it, acc_it, w_use, tmem_base);
+                        if (ok) ok = dx_mma<O>(p, smem, bars, blk, blk_hi, stage_it, acc_it, w_cnt, tmem_base);
                     }
                 });
             }
