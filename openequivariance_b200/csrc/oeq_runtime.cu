@@ -879,7 +879,7 @@ bool uvw_tc_bwd_geometry(const Problem& p, TcBwdGeometry& g) {
     g.dw_smem = stages * stage + (2 * stages + 4) * 8 + 16 + 1024;
     if (g.dw_smem > SMEM_LIMIT) return false;
     // dX/dY kernel: one set of A tiles, two buffers of one path's transposed weights, the epilogue staging
-    // buffer, one [channel][component] row per epilogue warp
+    // buffer, two sets of an X row and a dX row per epilogue warp
     int kb_max = 1, mup_max = 16, wt_max = 0, row_max = 0;
     size_t wt_total = 0;
     for (const Irrep& r : p.out) kb_max = std::max(kb_max, (r.mul + 31) / 32);
@@ -895,7 +895,7 @@ bool uvw_tc_bwd_geometry(const Problem& p, TcBwdGeometry& g) {
     const int off_w = kb_max * 2 * 128 * 128;
     const int off_stg = off_w + 2 * ((wt_max + 1023) / 1024 * 1024);
     const int off_row = off_stg + (128 * (mup_max + 1) * 4 + 15) / 16 * 16;
-    const int off_bar = off_row + 12 * ((row_max * 4 + 15) / 16 * 16);
+    const int off_bar = off_row + 12 * 4 * ((row_max * 4 + 15) / 16 * 16);
     const int dxy = off_bar + (2 * 1 + 2 * nacc + 4) * 8 + 16 + 1024;
     if (nacc >= 1 && dxy <= SMEM_LIMIT) {
         g.dxy_smem = dxy;

@@ -465,7 +465,7 @@ constexpr int DX_OFF_A = 0;
 constexpr int DX_OFF_W = DX_OFF_A + DX_NA * DX_STAGE_BYTES;
 constexpr int DX_OFF_STG = DX_OFF_W + 2 * DX_WT_MAX;
 constexpr int DX_OFF_ROW = DX_OFF_STG + (128 * DX_STG_PITCH * 4 + 15) / 16 * 16;
-constexpr int DX_OFF_BAR = DX_OFF_ROW + DX_EPILOGUE_WARPS * DX_ROWBUF;
+constexpr int DX_OFF_BAR = DX_OFF_ROW + DX_EPILOGUE_WARPS * 4 * DX_ROWBUF;   // per warp: two sets of an X row and a dX row
 constexpr int DX_SMEM_BYTES = DX_OFF_BAR + (2 * DX_NA + 2 * DX_NACC + 4) * 8 + 16 + 1024;
 static_assert(DX_ACC_COLS <= 256, "first-input multiplicity above 128");
 
@@ -730,80 +730,89 @@ __device__ __forceinline__ bool dx_epilogue_unit(const UvwTcBwdParams& p, unsign
         if (ewarp == 0 && lane == 0) mbar_arrive(bars.acc_empty + t);   // the accumulator tile may be overwritten
         const long long t2 = prof ? clock64() : 0;
         // One warp per batch row, lanes over the channels: dX by the owning lane, dY reduced over the warp.
-        // X and dX rows are [channel][component]: read and written as contiguous floats (lane = flat index) and
-        // turned into per-channel values through the warp's own shared-memory row buffer, because a lane-per-
-        // channel access would touch 2l+1 times the sectors it uses.  The global values of the warp's next row
-        // are fetched before the current row is computed and stored, so that their latency overlaps the arithmetic.
+        // X and dX rows are [channel][component]: they travel as contiguous floats (lane = flat index) between
+        // global memory and the warp's own shared-memory row buffers, because a lane-per-channel access would
+        // touch 2l+1 times the sectors it uses.  The rows of the warp's next batch row are copied asynchronously
+        // (cp.async into the other buffer set) while the current row is computed.
         {
             constexpr int NU = (MU + 31) / 32, ROW = MU * D1, NF = (ROW + 31) / 32;
             static_assert(NU <= 4, "first-input multiplicity above 128");
-            float* rowbuf = reinterpret_cast<float*>(smem + DX_OFF_ROW + ewarp * DX_ROWBUF);
-            float yA[D2], oyA[D2], xfA[NF], ofA[NF];
-            auto load_row = [&](int r, float (&y)[D2], float (&oy)[D2], float (&xf)[NF], float (&of)[NF]) {
+            unsigned char* rowbase = smem + DX_OFF_ROW + ewarp * 4 * DX_ROWBUF;
+            auto xbuf = [&](int set) { return reinterpret_cast<float*>(rowbase + set * 2 * DX_ROWBUF); };
+            auto dbuf = [&](int set) { return reinterpret_cast<float*>(rowbase + set * 2 * DX_ROWBUF + DX_ROWBUF); };
+            auto prefetch = [&](int r, int set) {
                 const float* xrow = p.X + (b0 + r) * (long long)X_DIM + IN1_OFF[a];
-                const float* yrow = p.Y + (b0 + r) * (long long)Y_DIM + IN2_OFF[b];
                 const float* dxrow = p.dX + (b0 + r) * (long long)X_DIM + IN1_OFF[a];
+#pragma unroll
+                for (int q = 0; q < NF; ++q) {
+                    const int idx = lane + 32 * q;
+                    if (idx < ROW) {
+                        cp_async_elem<4>(xbuf(set) + idx, xrow + idx);
+                        cp_async_elem<4>(dbuf(set) + idx, dxrow + idx);
+                    }
+                }
+                asm volatile("cp.async.commit_group;" ::: "memory");
+            };
+            auto load_y = [&](int r, float (&y)[D2], float (&oy)[D2]) {
+                const float* yrow = p.Y + (b0 + r) * (long long)Y_DIM + IN2_OFF[b];
                 const float* dyrow = p.dY + (b0 + r) * (long long)Y_DIM + IN2_OFF[b];
 #pragma unroll
                 for (int j = 0; j < D2; ++j) {
                     y[j] = __ldg(yrow + j);
                     oy[j] = lane == 0 ? dyrow[j] : 0.f;
                 }
-#pragma unroll
-                for (int q = 0; q < NF; ++q) {
-                    const int idx = lane + 32 * q;
-                    xf[q] = idx < ROW ? __ldg(xrow + idx) : 0.f;
-                    of[q] = idx < ROW ? dxrow[idx] : 0.f;
-                }
             };
+            float yA[D2], oyA[D2];
+            int set = 0;
+            if (ewarp < rows) {
+                prefetch(ewarp, 0);
+                load_y(ewarp, yA, oyA);
+            }
             for (int r = ewarp; r < rows; r += DX_EPILOGUE_WARPS) {
-                load_row(r, yA, oyA, xfA, ofA);
+                float yB[D2], oyB[D2];
+                const int rn = r + DX_EPILOGUE_WARPS;
+                if (rn < rows) {
+                    prefetch(rn, set ^ 1);
+                    load_y(rn, yB, oyB);
+                    asm volatile("cp.async.wait_group 1;" ::: "memory");
+                } else {
+                    asm volatile("cp.async.wait_group 0;" ::: "memory");
+                }
+                __syncwarp();
                 const long long tr0 = prof ? clock64() : 0;
-                float x[NU][D1], old[NU][D1];
-#pragma unroll
-                for (int q = 0; q < NF; ++q)
-                    if (lane + 32 * q < ROW) rowbuf[lane + 32 * q] = xfA[q];
-                __syncwarp();
-#pragma unroll
-                for (int v = 0; v < NU; ++v)
-#pragma unroll
-                    for (int i = 0; i < D1; ++i) x[v][i] = lane + 32 * v < MU ? rowbuf[(lane + 32 * v) * D1 + i] : 0.f;
-                __syncwarp();
-#pragma unroll
-                for (int q = 0; q < NF; ++q)
-                    if (lane + 32 * q < ROW) rowbuf[lane + 32 * q] = ofA[q];
-                __syncwarp();
-#pragma unroll
-                for (int v = 0; v < NU; ++v)
-#pragma unroll
-                    for (int i = 0; i < D1; ++i) old[v][i] = lane + 32 * v < MU ? rowbuf[(lane + 32 * v) * D1 + i] : 0.f;
-                __syncwarp();
+                float* xs = xbuf(set);
+                float* ds = dbuf(set);
                 float dy[D2];
 #pragma unroll
                 for (int j = 0; j < D2; ++j) dy[j] = 0.f;
 #pragma unroll
                 for (int v = 0; v < NU; ++v) {
                     const int u = lane + 32 * v;
-                    float g[D3];
-#pragma unroll
-                    for (int k = 0; k < D3; ++k) g[k] = u < MU ? stg[(r * D3 + k) * DX_STG_PITCH + u] : 0.f;
-                    sfor<CG_BEGIN[P], CG_BEGIN[P + 1]>([&](auto n_) {
-                        constexpr int N = n_;
-                        const float cg = (float)CG_V[N] * g[CG_K[N]];
-                        old[v][CG_I[N]] = fmaf(cg, yA[CG_J[N]], old[v][CG_I[N]]);
-                        dy[CG_J[N]] = fmaf(cg, x[v][CG_I[N]], dy[CG_J[N]]);
-                    });
                     if (u < MU) {
+                        float x[D1], old[D1], g[D3];
 #pragma unroll
-                        for (int i = 0; i < D1; ++i) rowbuf[u * D1 + i] = old[v][i];
+                        for (int i = 0; i < D1; ++i) {
+                            x[i] = xs[u * D1 + i];
+                            old[i] = ds[u * D1 + i];
+                        }
+#pragma unroll
+                        for (int k = 0; k < D3; ++k) g[k] = stg[(r * D3 + k) * DX_STG_PITCH + u];
+                        sfor<CG_BEGIN[P], CG_BEGIN[P + 1]>([&](auto n_) {
+                            constexpr int N = n_;
+                            const float cg = (float)CG_V[N] * g[CG_K[N]];
+                            old[CG_I[N]] = fmaf(cg, yA[CG_J[N]], old[CG_I[N]]);
+                            dy[CG_J[N]] = fmaf(cg, x[CG_I[N]], dy[CG_J[N]]);
+                        });
+#pragma unroll
+                        for (int i = 0; i < D1; ++i) ds[u * D1 + i] = old[i];    // a lane rewrites only what it read
                     }
                 }
                 __syncwarp();
                 float* dxrow = p.dX + (b0 + r) * (long long)X_DIM + IN1_OFF[a];
 #pragma unroll
                 for (int q = 0; q < NF; ++q)
-                    if (lane + 32 * q < ROW) dxrow[lane + 32 * q] = rowbuf[lane + 32 * q];
-                __syncwarp();
+                    if (lane + 32 * q < ROW) dxrow[lane + 32 * q] = ds[lane + 32 * q];
+                __syncwarp();          // the buffer set is refilled two rows later
                 const long long tr1 = prof ? clock64() : 0;
 #pragma unroll
                 for (int j = 0; j < D2; ++j) {
@@ -817,6 +826,11 @@ __device__ __forceinline__ bool dx_epilogue_unit(const UvwTcBwdParams& p, unsign
                     atomicAdd(p.prof + 25, (unsigned long long)(clock64() - tr1));    // dY reduction + stores
                     atomicAdd(p.prof + 26, 1ull);
                 }
+                if (rn < rows) {
+#pragma unroll
+                    for (int j = 0; j < D2; ++j) { yA[j] = yB[j]; oyA[j] = oyB[j]; }
+                }
+                set ^= 1;
             }
         }
         // the staging buffer is rewritten by the next tile, and the next path adds to the same dX / dY rows
