@@ -6,9 +6,14 @@
  * entry point takes plain pointers and sizes, returns an int status (0 = OK) and
  * never exits or throws across the boundary; oeq_last_error() gives the text of
  * the calling thread's last failure.  The library allocates no user-visible
- * memory: inputs, outputs and scratch are the caller's device buffers.  Launches
- * are asynchronous on the stream that is passed in (a cudaStream_t as void*),
- * on the CUDA device that is current in the calling thread.
+ * memory: inputs, outputs and scratch are the caller's device buffers.  A handle
+ * loads its kernels on first use and, for shared-weight 'uvw' problems, owns a
+ * device copy of the weights in the tensor cores' operand layout (a few hundred
+ * KB, allocated on first use, rewritten by every call): calls on one handle must
+ * not run concurrently from several host threads or on several streams at once;
+ * different handles are independent.  Launches are asynchronous on the stream that
+ * is passed in (a cudaStream_t as void*), on the CUDA device that is current in
+ * the calling thread.
  *
  * Data layout: row-major [rows][dim]; within a row the irreps are concatenated,
  * each as a [mul][2l+1] block.  Weights are in the kernel ("oeq") order defined
