@@ -1003,7 +1003,7 @@ struct UvuParams {
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
-int launch_uvu(Kernel& k, const Problem& p, UvuParams& prm, cudaStream_t stream) {
+int launch_uvu(Kernel& k, const Problem& p, UvuParams& prm, cudaStream_t stream, int extra_flags = 0) {
     const int e = p.elem();
     int flags = 0;
     if ((p.x_dim * e) % 16 == 0 && aligned16(prm.X)) flags |= 1;
@@ -1012,7 +1012,7 @@ int launch_uvu(Kernel& k, const Problem& p, UvuParams& prm, cudaStream_t stream)
     const void* zlike = prm.dZ ? prm.dZ : prm.Z;
     if ((p.z_dim * e) % 16 == 0 && aligned16(zlike)) flags |= 8;
     if (env_int("OEQ_B200_NO_BULK", 0)) flags = 0;
-    prm.flags = flags;
+    prm.flags = flags | extra_flags;
     prm.stages = k.stages;
     prm.chunk = std::max(1, env_int("OEQ_B200_CHUNK", 128));
     long long want = (prm.n_items + k.map.ng - 1) / k.map.ng;
@@ -1607,6 +1607,21 @@ int oeq_conv_backward(oeq_conv* h, int64_t nodes, int64_t edges, const void* X, 
     prm.rows = (const long long*)rows; prm.cols = (const long long*)cols; prm.perm = (const long long*)perm;
     prm.n_items = edges; prm.n_nodes = nodes; prm.status = h->d_status;
     h->last_stream = st;
+    if (env_int("OEQ_B200_UVU_PROFILE", 0)) {
+        // cycle accounting of CTA 0's first group (development aid): synchronous, prints to stderr
+        unsigned long long* d = nullptr;
+        OEQ_CUDA(cudaMalloc(&d, 8 * 8));
+        OEQ_CUDA(cudaMemsetAsync(d, 0, 8 * 8, st));
+        prm.ws = d;
+        rc = launch_uvu(h->bwd, p, prm, st, 16);
+        unsigned long long hb[8];
+        OEQ_CUDA(cudaMemcpyAsync(hb, d, sizeof hb, cudaMemcpyDeviceToHost, st));
+        OEQ_CUDA(cudaStreamSynchronize(st));
+        cudaFree(d);
+        fprintf(stderr, "[oeq_b200 conv backward profile] consumer: cycles %llu waiting for rows %llu items %llu | producer: cycles %llu "
+                        "waiting for a stage %llu walking %llu issuing %llu\n", hb[0], hb[1], hb[2], hb[4], hb[5], hb[6], hb[7]);
+        return rc;
+    }
     return launch_uvu(h->bwd, p, prm, st);
 }
 

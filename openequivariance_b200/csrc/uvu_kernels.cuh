@@ -458,14 +458,34 @@ __device__ void run_producer(const UvuParams& p, const Smem<BWD, MODE>& sm, int 
     volatile long long* total = sm.total(g);
     long long it = 0;
     bool ok = true;
+    // optional cycle accounting (flags bit 4: p.ws is a counter buffer): producer of CTA 0's first group
+    const bool prof = BWD && !SHARED_W && (p.flags & 16) && blockIdx.x == 0 && g == 0 && lane == 0;
+    unsigned long long prof_wait = 0, prof_walk = 0, prof_issue = 0;
+    const long long prof_begin = prof ? clock64() : 0;
     while (ok) {
         long long e, s, r, lo, hi;
-        if (!walker.next(e, s, r, lo, hi)) break;
+        const long long tw = prof ? clock64() : 0;
+        const bool got = walker.next(e, s, r, lo, hi);
+        if (prof) prof_walk += (unsigned long long)(clock64() - tw);
+        if (!got) break;
         for (int ph = 0; ph < PHASES && ok; ++ph, ++it) {
             const int stage = (int)(it % S);
+            const long long t0 = prof ? clock64() : 0;
             if (it >= S) ok = mbar_wait(sm.empty(g, stage), (unsigned)(((it / S) - 1) & 1), p.status, ERR_WAIT_EMPTY);
+            const long long t1 = prof ? clock64() : 0;
             if (ok) issue_item<MODE, BWD>(p, sm, g, stage, lane, e, s, r, lo, hi, ph);
+            if (prof) {
+                prof_wait += (unsigned long long)(t1 - t0);
+                prof_issue += (unsigned long long)(clock64() - t1);
+            }
         }
+    }
+    if (prof) {
+        unsigned long long* out = reinterpret_cast<unsigned long long*>(p.ws);
+        out[4] = (unsigned long long)(clock64() - prof_begin);   // producer: total cycles
+        out[5] = prof_wait;                                      // ... of which waiting for a free stage,
+        out[6] = prof_walk;                                      // walking the edge list,
+        out[7] = prof_issue;                                     // issuing the copies
     }
     if (lane == 0) *total = it - (ok ? 0 : 1);
     asm volatile("cp.async.wait_all;" ::: "memory");
@@ -967,6 +987,10 @@ __device__ void run_backward(const UvuParams& p, const Smem<true, MODE>& sm, int
 
     long long prev = -1;
     long long next_unwritten = 0;
+    // optional cycle accounting (flags bit 4: p.ws is a counter buffer): first thread of CTA 0's first group
+    const bool prof = (p.flags & 16) && blockIdx.x == 0 && g == 0 && tg == 0;
+    unsigned long long prof_wait = 0, prof_items = 0;
+    const long long prof_begin = prof ? clock64() : 0;
     for (long long it = 0;; ++it) {
         const int stage = (int)(it % S);
         const int ph = (int)(it % NPH);
@@ -974,7 +998,13 @@ __device__ void run_backward(const UvuParams& p, const Smem<true, MODE>& sm, int
         if constexpr (!PRODUCER) {
             if (issuer) issue_next();
         }
-        if (acquire_item<MODE, true>(p, sm, g, it) != 0) break;
+        const long long prof_t0 = prof ? clock64() : 0;
+        const int got = acquire_item<MODE, true>(p, sm, g, it);
+        if (prof) {
+            prof_wait += (unsigned long long)(clock64() - prof_t0);
+            ++prof_items;
+        }
+        if (got != 0) break;
         const long long* h = sm.hdr(g, stage);
         const unsigned char* st = sm.stage(g, stage);
         const long long item = h[0];
@@ -1093,6 +1123,11 @@ __device__ void run_backward(const UvuParams& p, const Smem<true, MODE>& sm, int
         group_sync(bar_id, G);
         T* out = p.ws + gid * (long long)W_NUMEL;
         for (int i = tg; i < W_NUMEL; i += G) out[i] = dwacc[i];
+    } else if (prof) {
+        unsigned long long* out = reinterpret_cast<unsigned long long*>(p.ws);
+        out[0] = (unsigned long long)(clock64() - prof_begin);   // consumer: total cycles
+        out[1] = prof_wait;                                      // ... of which waiting for staged rows
+        out[2] = prof_items;                                     // staged items (edges x phases)
     }
 }
 
