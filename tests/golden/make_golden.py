@@ -1,9 +1,9 @@
 """Regenerate the golden fixtures in this directory from the reference project.
 
-Run in a container that has the reference checkout (default
-``/root/reference``; override with ``OEQ_REFERENCE``):
+Run where a checkout of the reference project is available and point
+``OEQ_REFERENCE`` at it:
 
-    python tests/golden/make_golden.py
+    OEQ_REFERENCE=/path/to/OpenEquivariance python tests/golden/make_golden.py
 
 Only the reference's CPU-runnable pieces are executed: its problem
 description and Clebsch-Gordan generator (e3nn_lite.py), its numpy "uvu"
@@ -29,7 +29,9 @@ import types
 
 import numpy as np
 
-REF = os.environ.get("OEQ_REFERENCE", "/root/reference")
+REF = os.environ.get("OEQ_REFERENCE")
+if not REF:
+    raise SystemExit("set OEQ_REFERENCE to the root of a checkout of the reference project")
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
