@@ -204,3 +204,26 @@ def test_tensor_core_forward(name, deterministic, monkeypatch):
         first = conv.forward(*args)
         for _ in range(3):
             assert torch.equal(conv.forward(*args), first)
+
+
+@pytest.mark.parametrize("chunk", [16, 128])
+def test_widest_rows_many_chunks_per_group(chunk, monkeypatch):
+    """MACE-large rows on a graph large enough that every group walks several work chunks (small chunks make
+    that happen at a size the oracle can follow): chunk boundaries moved to node boundaries, the phased
+    backward stages and the ring of dY partials all wrap many times."""
+    monkeypatch.setenv("OEQ_B200_CHUNK", str(chunk))
+    p = problem_by_name("mace_large_128")
+    nodes = 700
+    rows, cols = random_graph(nodes, 20000, seed=31)
+    conv, (xt, yt, wt, dzt, index), (z, dx, dy, dw) = check_conv(p, nodes, rows, cols, 32, True)
+    z2 = conv.forward(xt, yt, wt, *index)
+    dx2, dy2, dw2 = conv.backward_helper(xt, yt, wt, dzt, *index)
+    assert torch.equal(z, z2) and torch.equal(dx, dx2) and torch.equal(dy, dy2) and torch.equal(dw, dw2)
+    atomic = oeq.TensorProductConv(p, torch_op=True, deterministic=False)
+    za = atomic.forward(xt, yt, wt, index[0], index[1])
+    dxa, dya, dwa = atomic.backward_helper(xt, yt, wt, dzt, index[0], index[1])
+    atomic.check_device_status()
+    assert rel_err(za.cpu().numpy(), z.cpu().numpy()) < 1e-5
+    assert rel_err(dxa.cpu().numpy(), dx.cpu().numpy()) < 1e-5
+    assert rel_err(dya.cpu().numpy(), dy.cpu().numpy()) < 1e-5
+    assert rel_err(dwa.cpu().numpy(), dw.cpu().numpy()) < 1e-5
