@@ -626,6 +626,8 @@ std::string descriptor_text(const Problem& p, const Mapping& m, const UvwConfig*
         s << "};\n";
     }
     s << "constexpr int ZPC_MAX = " << m.zpc_max << ", XPC = " << m.xpc << ";\n";
+    // cycle accounting inside the convolution backward kernel is a separate specialisation: it costs registers
+    s << "constexpr bool UVU_PROFILE = " << (env_int("OEQ_B200_UVU_PROFILE", 0) ? "true" : "false") << ";\n";
     if (m.tc_tables) {
         const UvuTcColumns cols = uvu_tc_columns(p, m.part_of_out, m.ps);
         const UvuTcTables t = build_uvu_tc_tables(p, cols);

@@ -459,7 +459,7 @@ __device__ void run_producer(const UvuParams& p, const Smem<BWD, MODE>& sm, int 
     long long it = 0;
     bool ok = true;
     // optional cycle accounting (flags bit 4: p.ws is a counter buffer): producer of CTA 0's first group
-    const bool prof = BWD && !SHARED_W && (p.flags & 16) && blockIdx.x == 0 && g == 0 && lane == 0;
+    const bool prof = UVU_PROFILE && BWD && !SHARED_W && (p.flags & 16) && blockIdx.x == 0 && g == 0 && lane == 0;
     unsigned long long prof_wait = 0, prof_walk = 0, prof_issue = 0;
     const long long prof_begin = prof ? clock64() : 0;
     while (ok) {
@@ -987,8 +987,9 @@ __device__ void run_backward(const UvuParams& p, const Smem<true, MODE>& sm, int
 
     long long prev = -1;
     long long next_unwritten = 0;
-    // optional cycle accounting (flags bit 4: p.ws is a counter buffer): first thread of CTA 0's first group
-    const bool prof = (p.flags & 16) && blockIdx.x == 0 && g == 0 && tg == 0;
+    // optional cycle accounting, compiled in only when the descriptor says so (flags bit 4: p.ws is a counter
+    // buffer): first thread of CTA 0's first group
+    const bool prof = UVU_PROFILE && (p.flags & 16) && blockIdx.x == 0 && g == 0 && tg == 0;
     unsigned long long prof_wait = 0, prof_items = 0;
     const long long prof_begin = prof ? clock64() : 0;
     for (long long it = 0;; ++it) {
