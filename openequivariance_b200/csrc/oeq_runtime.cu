@@ -1161,9 +1161,9 @@ int oeq_tp_destroy(oeq_tp* h) {
     if (!h) return OEQ_OK;
     if (h->d_status) cudaFree(h->d_status);
     if (h->d_packed) cudaFree(h->d_packed);
-    if (h->fwd.lib) cudaLibraryUnload(h->fwd.lib);
-    if (h->bwd.lib) cudaLibraryUnload(h->bwd.lib);
-    if (h->fwd_tc.lib) cudaLibraryUnload(h->fwd_tc.lib);
+    if (h->d_packed_t) cudaFree(h->d_packed_t);
+    for (Kernel* k : {&h->fwd, &h->bwd, &h->fwd_tc, &h->bwd_dw_tc, &h->bwd_dxy_tc})
+        if (k->lib) cudaLibraryUnload(k->lib);
     delete h;
     return OEQ_OK;
 }
