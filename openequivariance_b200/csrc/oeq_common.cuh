@@ -85,7 +85,7 @@ __device__ __forceinline__ void fence_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
-// global -> shared bulk copy (1-D TMA, no tensor map, no multicast); both
+// global -> shared bulk copy (1-D TMA, no tensor map, one destination CTA); both
 // addresses 16-byte aligned, bytes a multiple of 16; completion on `bar`.
 __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, unsigned bytes,
                                          unsigned long long* bar) {
