@@ -133,6 +133,18 @@ __device__ __forceinline__ bool dw_produce(const UvwTcBwdParams& p, unsigned cha
         unsigned char* a_lo = a_hi + TB_TILE;
         unsigned char* b_hi = a_lo + TB_TILE;
         unsigned char* b_lo = b_hi + MW * 128;          // the lo tile follows the hi tile: one descriptor spans both
+        // the loads of dZ (the B operand, formed last) go out first: their latency overlaps the work on A
+        constexpr int NBI = (32 * MW + NPT - 1) / NPT;
+        float g[NBI];
+#pragma unroll
+        for (int q = 0; q < NBI; ++q) {
+            const int item = ptid + q * NPT;
+            g[q] = 0.f;
+            if (item < RB * MW * D3) {
+                const int rr = item / (MW * D3), wk = item % (MW * D3);
+                if (rr < rows) g[q] = __ldg(p.dZ + (b0 + rr) * (long long)Z_DIM + OUT_OFF[O] + wk);
+            }
+        }
         // ---- A: T^T.  A thread keeps its slot row (path, u) and walks the stage's batch rows rr0, rr0 + 4, ...;
         // the global loads of a batch of rows go out together, so that their latency is paid once per batch
         {
@@ -205,19 +217,8 @@ __device__ __forceinline__ bool dw_produce(const UvwTcBwdParams& p, unsigned cha
                 *reinterpret_cast<float*>(a_lo + off) = 0.f;
             }
         }
-        // ---- B: dZ^T.  consecutive threads read consecutive (w, k) of a batch row; loads first, then stores
+        // ---- B: dZ^T.  consecutive threads hold consecutive (w, k) of a batch row (loaded above)
         {
-            constexpr int NBI = (32 * MW + NPT - 1) / NPT;
-            float g[NBI];
-#pragma unroll
-            for (int q = 0; q < NBI; ++q) {
-                const int item = ptid + q * NPT;
-                g[q] = 0.f;
-                if (item < RB * MW * D3) {
-                    const int rr = item / (MW * D3), wk = item % (MW * D3);
-                    if (rr < rows) g[q] = __ldg(p.dZ + (b0 + rr) * (long long)Z_DIM + OUT_OFF[O] + wk);
-                }
-            }
 #pragma unroll
             for (int q = 0; q < NBI; ++q) {
                 const int item = ptid + q * NPT;
