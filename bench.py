@@ -374,9 +374,10 @@ def run_e2e(args, torch, dist, world, device, conv, det, x, y, w, dz, edges, loc
     gradient move through one pinned tile that is re-used for every slice of the device array (the
     bytes that cross PCIe are the full arrays).
 
-    One GPU, deterministic variant: the public host-tensor entry point
-    (``StreamedTensorProductConv.forward_backward_host``), which pipelines edge slabs so that the
-    copies in both directions overlap the kernels.  Otherwise: copy in, run, copy out."""
+    Deterministic variant, any number of GPUs: the public host-tensor entry point
+    (``ShardedTensorProductConv.forward_backward_host``), which exchanges the halo once and pipelines
+    the rank's edge slabs so that the copies in both directions overlap the kernels.  Atomic variant
+    (one GPU): copy in, run, copy out."""
     pin = lambda t: torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t)
     pinned_like = lambda t: torch.empty(t.shape, dtype=t.dtype, pin_memory=True)   # empty_like would not pin
 
@@ -399,34 +400,37 @@ def run_e2e(args, torch, dist, world, device, conv, det, x, y, w, dz, edges, loc
                 "d2h_bytes_per_step": int(d2h), "ms_per_step": dt.item() * 1e3, "steps": args.e2e_steps,
                 "note": note}
 
-    if world == 1 and det and graph is not None:
-        from openequivariance_b200.stream import StreamedTensorProductConv
-        rows_h, cols_h = conv.rows.cpu().numpy(), conv.cols.cpu().numpy()
-        streamed = StreamedTensorProductConv(conv.problem, rows_h, cols_h, x.shape[0], slab_edges=args.slab_edges,
-                                             device=device, local_conv=conv.conv)
-        tile = streamed.max_edges
-        x_h, dz_h = pin(x), pin(dz)
-        y_h, w_h = pin(y[:tile]), pin(w[:tile])
-        z_h = torch.empty((x.shape[0], dz.shape[1]), dtype=x.dtype, pin_memory=True)
-        dx_h, dy_h, dw_h = pinned_like(x_h), pinned_like(y_h), pinned_like(w_h)
-        tile_of = lambda t: (lambda i, lo, hi: t[:hi - lo])      # every slab crosses through the same pinned tile
+    if det:
+        # host-tensor entry point of the sharded convolution: X of the rank's nodes goes in, the halo is
+        # exchanged, the per-edge arrays stream through the GPU in slabs (copies overlap the kernels)
         elem = x.element_size()
+        streamed = conv.slab_plan(args.slab_edges)
+        x_h, dz_h = pin(x), pin(dz)
+        z_h = torch.empty((x.shape[0], dz.shape[1]), dtype=x.dtype, pin_memory=True)
+        dx_h = pinned_like(x_h)
+        tile = streamed.max_edges
+        y_h, w_h = pin(y[:tile]), pin(w[:tile])
+        dy_h, dw_h = pinned_like(y_h), pinned_like(w_h)
+        tile_of = lambda t: (lambda i, lo, hi: t[:hi - lo])      # every slab crosses through the same pinned tile
 
         def one():
-            streamed.forward_backward_host(x_h, tile_of(y_h), tile_of(w_h), dz_h, z_h, dx_h, tile_of(dy_h), tile_of(dw_h))
+            conv.forward_backward_host(x_h, tile_of(y_h), tile_of(w_h), dz_h, z_h, dx_h, tile_of(dy_h), tile_of(dw_h),
+                                       slab_edges=args.slab_edges)
             torch.cuda.synchronize()
 
-        return timed(one, streamed.h2d_bytes(elem), streamed.d2h_bytes(elem),
-                     f"{len(streamed.slabs)} edge slabs pipelined (copy in / kernels / copy out overlap); per-edge "
-                     "arrays cross PCIe through one re-used pinned tile per array")
+        h2d, d2h = conv.host_bytes(elem)
+        if world > 1:
+            tot = torch.tensor([h2d, d2h], device=device, dtype=torch.float64)
+            dist.all_reduce(tot)
+            h2d, d2h = tot[0].item(), tot[1].item()
+        return timed(one, h2d, d2h,
+                     f"{len(streamed.slabs)} edge slabs per rank pipelined (copy in / kernels / copy out overlap); "
+                     "per-edge arrays cross PCIe through one re-used pinned tile per array; bytes summed over ranks")
 
     tile = min(local_edges, 1 << 19)
     x_h, y_h, dz_h = pin(x), pin(y), pin(dz)
     w_h = pin(w[:tile])
-    if det:
-        idx_dev = [conv.rows, conv.cols, conv.perm]
-    else:
-        idx_dev = list(index)
+    idx_dev = list(index)
     idx_h = [pin(t) for t in idx_dev]
     z_h = torch.empty((x.shape[0], dz.shape[1]), dtype=x.dtype, pin_memory=True)
     dx_h, dy_h, dw_h = pinned_like(x_h), pinned_like(y_h), pinned_like(w_h)
@@ -443,11 +447,8 @@ def run_e2e(args, torch, dist, world, device, conv, det, x, y, w, dz, edges, loc
         for lo in range(0, local_edges, tile):
             n = min(tile, local_edges - lo)
             w_d[lo:lo + n].copy_(w_h[:n], non_blocking=True)
-        if det:
-            z, dx, dy, dw = conv.forward_backward(x_d, y_d, w_d, dz_d)
-        else:
-            z = conv.forward(x_d, y_d, w_d, *idx_dev)
-            dx, dy, dw = conv.backward_helper(x_d, y_d, w_d, dz_d, *idx_dev)
+        z = conv.forward(x_d, y_d, w_d, *idx_dev)
+        dx, dy, dw = conv.backward_helper(x_d, y_d, w_d, dz_d, *idx_dev)
         z_h.copy_(z, non_blocking=True)
         dx_h.copy_(dx, non_blocking=True)
         dy_h.copy_(dy, non_blocking=True)
@@ -456,7 +457,7 @@ def run_e2e(args, torch, dist, world, device, conv, det, x, y, w, dz, edges, loc
             dw_h[:n].copy_(dw[lo:lo + n], non_blocking=True)
         torch.cuda.synchronize()
 
-    return timed(one, h2d, d2h, "per-rank bytes; W and dW cross PCIe through one re-used pinned tile")
+    return timed(one, h2d, d2h, "copy in, run, copy out; W and dW cross PCIe through one re-used pinned tile")
 
 
 def main():

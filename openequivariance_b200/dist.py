@@ -138,6 +138,9 @@ class ShardedTensorProductConv:
         self.send_index = as_dev(np.concatenate(plan.send_rows)) if self.world > 1 else None
         self.send_index_per_peer = [as_dev(s) for s in plan.send_rows] if self.world > 1 else []
         self._x_local = None
+        self._x_owned = None
+        self._streamed = None
+        self._streamed_slab_edges = None
 
     # ---- exchange steps -------------------------------------------------------------
 
@@ -197,6 +200,52 @@ class ShardedTensorProductConv:
         z = self.local_forward(x_local, y, w)
         dx_local, dy, dw = self.local_backward(x_local, y, w, dz)
         return z, self.scatter_sender_grads(dx_local), dy, dw
+
+
+    def slab_plan(self, slab_edges: int = 1 << 18):
+        """The slab pipeline over this rank's edges (``StreamedTensorProductConv``; ``.slabs``, ``.max_edges``
+        and ``.max_receivers`` size the caller's pinned tiles), built once per slab size."""
+        if self._streamed is None or self._streamed_slab_edges != slab_edges:
+            from .stream import StreamedTensorProductConv
+            plan = self.plan
+            self._streamed = StreamedTensorProductConv(self.problem, plan.local_rows, plan.local_cols, plan.owned,
+                                                       slab_edges=slab_edges, device=self.device, local_conv=self.conv)
+            self._streamed_slab_edges = slab_edges
+        return self._streamed
+
+    def forward_backward_host(self, x_h, y_h, w_h, dz_h, z_h, dx_h, dy_h, dw_h, slab_edges: int = 1 << 18):
+        """The same step on host tensors of this rank's shard (owned rows of ``X`` and ``dZ``, the rank's
+        edge slice of ``Y`` and ``W``; outputs into ``z_h``, ``dx_h``, ``dy_h``, ``dw_h``).
+
+        The owned rows of ``X`` go to the device and the halo is exchanged once; the per-edge arrays then
+        stream through the GPU in edge slabs whose copies overlap the kernels
+        (``StreamedTensorProductConv.stream_slabs``); ``dX`` stays on the device until its halo rows have
+        gone back to their owners.  Edge arrays may be callables ``f(slab_index, e0, e1)`` as in the
+        single-GPU entry point (edge positions relative to the rank's slice).  Results are complete once
+        the current stream is."""
+        plan = self.plan
+        streamed = self.slab_plan(slab_edges)
+        if x_h.shape[0] != plan.owned:
+            raise ValueError(f"rank {self.rank} owns {plan.owned} nodes, got {x_h.shape[0]} rows")
+        if self.device.type == "cuda":
+            buf = self._x_owned
+            if buf is None or buf.dtype != x_h.dtype:
+                buf = self._x_owned = torch.empty((plan.owned, x_h.shape[1]), dtype=x_h.dtype, device=self.device)
+            buf.copy_(x_h, non_blocking=True)
+            x_owned = buf
+        else:
+            x_owned = x_h
+        x_local = self.gather_senders(x_owned)
+        dx_local = streamed.stream_slabs(x_local, y_h, w_h, dz_h, z_h, dy_h, dw_h)
+        dx_h.copy_(self.scatter_sender_grads(dx_local), non_blocking=True)
+
+    def host_bytes(self, elem: int):
+        """(host-to-device, device-to-host) bytes of one ``forward_backward_host`` step on this rank."""
+        p, plan = self.problem, self.plan
+        edges = plan.edge_hi - plan.edge_lo
+        node = plan.owned * (p.irreps_in1.dim + p.irreps_out.dim) * elem
+        edge = edges * (p.irreps_in2.dim + p.weight_numel) * elem
+        return node + edge + edges * 24, node + edge
 
 
 # ---------------------------------------------------------------------------------------------------

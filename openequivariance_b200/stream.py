@@ -130,7 +130,7 @@ class StreamedTensorProductConv:
         mk = lambda *shape, dt=dtype: torch.empty(shape, dtype=dt, device=dev)
         self._buffers = {
             "dtype": dtype,
-            "x": mk(self.nodes, p.irreps_in1.dim),
+            "x": None,                       # first-input rows, allocated when they come from the host
             "y": [mk(self.max_edges, p.irreps_in2.dim) for _ in range(2)],
             "w": [mk(self.max_edges, p.weight_numel) for _ in range(2)],
             "dz": [mk(self.max_receivers, p.irreps_out.dim) for _ in range(2)],
@@ -145,17 +145,33 @@ class StreamedTensorProductConv:
         tensor of that edge range.  Pinned host memory makes the copies asynchronous.  Returns
         after everything is enqueued; the results are complete once the current stream is."""
         if not self.on_gpu:
-            return self._run_serial(x_h, y_h, w_h, dz_h, z_h, dx_h, dy_h, dw_h)
+            dx_h.copy_(self.stream_slabs(x_h, y_h, w_h, dz_h, z_h, dy_h, dw_h))
+            return
         b = self._buffers
         if b is None or b["dtype"] != x_h.dtype:
             self._alloc(x_h.dtype)
+            b = self._buffers
+        if b.get("x") is None:
+            b["x"] = torch.empty((self.nodes, self.problem.irreps_in1.dim), dtype=x_h.dtype, device=self.device)
+        b["x"].copy_(x_h, non_blocking=True)
+        dx_acc = self.stream_slabs(b["x"], y_h, w_h, dz_h, z_h, dy_h, dw_h)
+        dx_h.copy_(dx_acc, non_blocking=True)
+
+    def stream_slabs(self, x_dev, y_h, w_h, dz_h, z_h, dy_h, dw_h):
+        """The slab pipeline for first-input rows that are already on the device: ``x_dev`` holds a row for
+        every sender id in ``cols`` (it may have more rows than there are receivers, e.g. a shard's halo
+        rows).  Writes ``Z``, ``dY`` and ``dW`` to the host arrays and returns ``dX`` (all rows of ``x_dev``)
+        as a device tensor, valid on the current stream."""
+        if not self.on_gpu:
+            return self._run_serial(x_dev, y_h, w_h, dz_h, z_h, dy_h, dw_h)
+        b = self._buffers
+        if b is None or b["dtype"] != x_dev.dtype:
+            self._alloc(x_dev.dtype)
             b = self._buffers
         cur = torch.cuda.current_stream(self.device)
         s_in, s_out = self._s_in, self._s_out
         s_in.wait_stream(cur)                      # earlier work may still read the buffers
         s_out.wait_stream(cur)
-        with torch.cuda.stream(s_in):
-            b["x"].copy_(x_h, non_blocking=True)
         done = [None, None]
         dx_acc = None
         for i, slab in enumerate(self.slabs):
@@ -173,8 +189,8 @@ class StreamedTensorProductConv:
                     dst.copy_(src, non_blocking=True)
                 arrived = s_in.record_event()
             cur.wait_event(arrived)
-            z = self.conv._forward_impl(b["x"], y_d, w_d, idx_d[0], idx_d[1], idx_d[2], n_out=m)
-            dx, dy, dw = self.conv._backward_impl(b["x"], y_d, w_d, dz_d, idx_d[0], idx_d[1], idx_d[2])
+            z = self.conv._forward_impl(x_dev, y_d, w_d, idx_d[0], idx_d[1], idx_d[2], n_out=m)
+            dx, dy, dw = self.conv._backward_impl(x_dev, y_d, w_d, dz_d, idx_d[0], idx_d[1], idx_d[2])
             if dx_acc is None:
                 dx_acc = dx
             else:
@@ -187,14 +203,11 @@ class StreamedTensorProductConv:
                 _host_slice(dw_h, i, slab.e0, slab.e1).copy_(dw, non_blocking=True)
                 for t in (z, dy, dw):
                     t.record_stream(s_out)
-        with torch.cuda.stream(s_out):
-            s_out.wait_stream(cur)
-            dx_h.copy_(dx_acc, non_blocking=True)
-            dx_acc.record_stream(s_out)
         cur.wait_stream(s_out)
         cur.wait_stream(s_in)
+        return dx_acc
 
-    def _run_serial(self, x_h, y_h, w_h, dz_h, z_h, dx_h, dy_h, dw_h):
+    def _run_serial(self, x, y_h, w_h, dz_h, z_h, dy_h, dw_h):
         """The same slab sequence without streams (host-logic tests with a stand-in convolution)."""
         dx_acc = None
         for i, slab in enumerate(self.slabs):
@@ -202,10 +215,10 @@ class StreamedTensorProductConv:
             y = _host_slice(y_h, i, slab.e0, slab.e1)
             w = _host_slice(w_h, i, slab.e0, slab.e1)
             dz = dz_h[slab.r0:slab.r1]
-            z = self.conv._forward_impl(x_h, y, w, rows, cols, perm, n_out=slab.receivers)
-            dx, dy, dw = self.conv._backward_impl(x_h, y, w, dz, rows, cols, perm)
+            z = self.conv._forward_impl(x, y, w, rows, cols, perm, n_out=slab.receivers)
+            dx, dy, dw = self.conv._backward_impl(x, y, w, dz, rows, cols, perm)
             dx_acc = dx if dx_acc is None else dx_acc + dx
             z_h[slab.r0:slab.r1].copy_(z)
             _host_slice(dy_h, i, slab.e0, slab.e1).copy_(dy)
             _host_slice(dw_h, i, slab.e0, slab.e1).copy_(dw)
-        dx_h.copy_(dx_acc)
+        return dx_acc

@@ -110,6 +110,47 @@ def test_two_rank_conv_matches_the_single_process_oracle(nodes):
     assert len(result) == world and max(result.values()) < 1e-12
 
 
+def _host_worker(rank, world, port, nodes, result):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        p = problem_by_name("cw_mixed", irrep_dtype=np.float64, weight_dtype=np.float64)
+        rows, cols = random_graph(nodes, 300, seed=4)
+        rows, cols, order, _ = orc.coord_graph(rows, cols)
+        x, y, w, dz = conv_inputs(p, nodes, len(rows), 5)
+        conv = ShardedTensorProductConv(p, rows, cols, nodes, device="cpu", local_conv=OracleLocalConv(p))
+        plan = conv.plan
+        n_lo, n_hi, e_lo, e_hi = plan.node_lo, plan.node_hi, plan.edge_lo, plan.edge_hi
+        xs, dzs = torch.from_numpy(x[n_lo:n_hi]), torch.from_numpy(dz[n_lo:n_hi])
+        ys, ws = torch.from_numpy(y[e_lo:e_hi]), torch.from_numpy(w[e_lo:e_hi])
+        z_h = torch.zeros(plan.owned, p.irreps_out.dim, dtype=torch.float64)
+        dx_h, dy_h, dw_h = torch.zeros_like(xs), torch.zeros_like(ys), torch.zeros_like(ws)
+        # several slabs per rank; the weights are handed over lazily, slab by slab
+        conv.forward_backward_host(xs, ys, lambda i, lo, hi: ws[lo:hi], dzs, z_h, dx_h, dy_h, dw_h, slab_edges=40)
+        assert len(conv.slab_plan(40).slabs) > 1
+        z_ref = orc.conv_forward(p, x, y, w, rows, cols)
+        rx, ry, rw = orc.conv_backward(p, x, y, w, dz, rows, cols)
+        result[rank] = max(rel_err(z_h.numpy(), z_ref[n_lo:n_hi]), rel_err(dx_h.numpy(), rx[n_lo:n_hi]),
+                           rel_err(dy_h.numpy(), ry[e_lo:e_hi]), rel_err(dw_h.numpy(), rw[e_lo:e_hi]))
+        h2d, d2h = conv.host_bytes(8)
+        assert h2d - d2h == 24 * (e_hi - e_lo)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_host_tensor_step_streams_slabs_and_matches_the_oracle():
+    world, nodes = 2, 41
+    ctx = mp.get_context("spawn")
+    result = ctx.Manager().dict()
+    procs = [ctx.Process(target=_host_worker, args=(r, world, 29671, nodes, result)) for r in range(world)]
+    for pr in procs:
+        pr.start()
+    for pr in procs:
+        pr.join(timeout=240)
+        assert pr.exitcode == 0
+    assert len(result) == world and max(result.values()) < 1e-12
+
+
 # ---------------------------------------------------------------------------------------------------
 # batch tensor product sharded by rows
 

@@ -186,6 +186,29 @@ def test_streamed_host_tensors(name, slab_edges):
         assert len(streamed.slabs) > 2
 
 
+def test_sharded_host_tensor_step_on_one_rank():
+    """The host-tensor entry point of the sharded convolution (one rank: no halo): owned rows in, edge slabs
+    streamed with lazily supplied weight slices, results equal to the resident convolution."""
+    from openequivariance_b200.dist import ShardedTensorProductConv
+    p = problem_by_name("mace_128")
+    nodes = 90
+    rows, cols = random_graph(nodes, 1100, seed=31)
+    conv, (xt, yt, wt, dzt, index), (z, dx, dy, dw) = check_conv(p, nodes, rows, cols, 32, True)
+    sharded = ShardedTensorProductConv(p, index[0].cpu().numpy(), index[1].cpu().numpy(), nodes)
+    pin = lambda t: torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t)
+    x_h, y_h, w_h, dz_h = pin(xt), pin(yt), pin(wt), pin(dzt)
+    out = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True).fill_(float("nan")) for t in (z, dx, dy, dw)]
+    sharded.forward_backward_host(x_h, y_h, lambda i, lo, hi: w_h[lo:hi], dz_h, out[0], out[1], out[2],
+                                  lambda i, lo, hi: out[3][lo:hi], slab_edges=300)
+    torch.cuda.synchronize()
+    sharded.conv.check_device_status()
+    assert len(sharded.slab_plan(300).slabs) > 2
+    assert torch.equal(out[0], z.cpu()) and torch.equal(out[2], dy.cpu()) and torch.equal(out[3], dw.cpu())
+    assert rel_err(out[1].numpy(), dx.cpu().numpy()) < REL_TOL[np.float32]
+    h2d, d2h = sharded.host_bytes(4)
+    assert d2h == sum(t.numel() * 4 for t in out) and h2d == d2h + 24 * len(rows)
+
+
 @pytest.mark.parametrize("deterministic", [False, True], ids=["atomic", "deterministic"])
 @pytest.mark.parametrize("name", ["mace_128", "mace_large_128"])
 def test_tensor_core_forward(name, deterministic, monkeypatch):
