@@ -116,9 +116,12 @@ int oeq_tp_backward(oeq_tp* h, int64_t batch, const void* X, const void* Y, cons
  * inside the library image (held by every GPU that loads the library); the launch is narrowed until
  * its partials fit, and a weight tensor larger than the array is refused with OEQ_ERR_UNSUPPORTED.
  * The call itself makes no cudaMalloc / cudaFree; the first call on a device (and the first call on
- * a handle) does one-time set-up -- the array's address is looked up, the kernels are loaded -- so
- * make that call before any stream capture.  All calls share the array, which keeps whatever the last
- * call left; every call rewrites the part it reads, but two calls that overlap on the GPU race.  A
+ * a handle) does one-time set-up -- the array's address is looked up (under a lock, so host threads
+ * may race to it), the kernels are loaded -- so make that call before any stream capture.  All calls
+ * share the array, which keeps whatever the last call left; every call rewrites the part it reads,
+ * but two calls that overlap on the GPU race.  'uvw' problems always take the FMA kernels here (the
+ * tensor-core kernels of oeq_tp_backward need packed weight copies that the library would have to
+ * allocate), so expect that pass to be several times slower than oeq_tp_backward for them.  A
  * bounded wait that runs out is recorded only if the handle already owns a status word (any earlier
  * oeq_tp_forward / oeq_tp_backward creates it). */
 int oeq_tp_backward_noalloc(oeq_tp* h, int64_t batch, const void* X, const void* Y, const void* W, const void* dZ,

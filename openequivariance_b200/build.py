@@ -33,18 +33,39 @@ def needs_build() -> bool:
 
 
 def build_library(force: bool = False, verbose: bool = False) -> str:
+    """Build the library if it is missing or older than its sources.
+
+    Several processes may get here at once (one rank per GPU under ``torch.distributed.run``): the build
+    runs under an exclusive lock on a sidecar file, writes to a temporary name and is renamed into place,
+    so no process ever loads a half-written library; whoever waited for the lock re-checks and usually
+    finds the work done.
+    """
     if not force and not needs_build():
         return LIB
-    cmd = [_nvcc(), "-O2", "-std=c++17", "-shared", "-Xcompiler", "-fPIC", "-lineinfo",
-           "-gencode", "arch=compute_100a,code=sm_100a", "-cudart", "static",
-           "-o", LIB] + [os.path.join(CSRC, s) for s in SOURCES] + ["-ldl"]
-    if verbose:
-        cmd.insert(1, "-Xptxas=-v")
-    res = subprocess.run(cmd, capture_output=True, text=True)
-    if res.returncode != 0:
-        raise RuntimeError("building liboeq_b200.so failed:\n" + " ".join(cmd) + "\n" + res.stdout + res.stderr)
-    if verbose:
-        print(res.stdout + res.stderr)
+    import fcntl
+    with open(LIB + ".lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and not needs_build():
+                return LIB
+            tmp = f"{LIB}.tmp{os.getpid()}"
+            cmd = [_nvcc(), "-O2", "-std=c++17", "-shared", "-Xcompiler", "-fPIC", "-lineinfo",
+                   "-gencode", "arch=compute_100a,code=sm_100a", "-cudart", "static",
+                   "-o", tmp] + [os.path.join(CSRC, s) for s in SOURCES] + ["-ldl"]
+            if verbose:
+                cmd.insert(1, "-Xptxas=-v")
+            if os.environ.get("OEQ_DEV_PROFILE"):
+                cmd.insert(1, "-DOEQ_DEV_PROFILE")      # development build: cycle accounting inside the kernels
+            res = subprocess.run(cmd, capture_output=True, text=True)
+            if res.returncode != 0:
+                if os.path.exists(tmp):
+                    os.remove(tmp)
+                raise RuntimeError("building liboeq_b200.so failed:\n" + " ".join(cmd) + "\n" + res.stdout + res.stderr)
+            os.replace(tmp, LIB)
+            if verbose:
+                print(res.stdout + res.stderr)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
     return LIB
 
 

@@ -626,8 +626,13 @@ std::string descriptor_text(const Problem& p, const Mapping& m, const UvwConfig*
         s << "};\n";
     }
     s << "constexpr int ZPC_MAX = " << m.zpc_max << ", XPC = " << m.xpc << ";\n";
-    // cycle accounting inside the convolution backward kernel is a separate specialisation: it costs registers
+    // cycle accounting inside the kernels is a development aid: it exists only in a library built with
+    // -DOEQ_DEV_PROFILE (the shipped entry points then contain no allocation, synchronisation or printing)
+#ifdef OEQ_DEV_PROFILE
     s << "constexpr bool UVU_PROFILE = " << (env_int("OEQ_B200_UVU_PROFILE", 0) ? "true" : "false") << ";\n";
+#else
+    s << "constexpr bool UVU_PROFILE = false;\n";
+#endif
     if (m.tc_tables) {
         const UvuTcColumns cols = uvu_tc_columns(p, m.part_of_out, m.ps);
         const UvuTcTables t = build_uvu_tc_tables(p, cols);
@@ -1005,7 +1010,8 @@ struct UvuParams {
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
-int launch_uvu(Kernel& k, const Problem& p, UvuParams& prm, cudaStream_t stream, int extra_flags = 0) {
+int launch_uvu(Kernel& k, const Problem& p, UvuParams& prm, cudaStream_t stream, int extra_flags = 0,
+               long long max_ctas = 0, long long* ctas_out = nullptr) {
     const int e = p.elem();
     int flags = 0;
     if ((p.x_dim * e) % 16 == 0 && aligned16(prm.X)) flags |= 1;
@@ -1019,6 +1025,8 @@ int launch_uvu(Kernel& k, const Problem& p, UvuParams& prm, cudaStream_t stream,
     prm.chunk = std::max(1, env_int("OEQ_B200_CHUNK", 128));
     long long want = (prm.n_items + k.map.ng - 1) / k.map.ng;
     long long grid = std::max<long long>(1, std::min<long long>((long long)k.sm_count * k.ctas_per_sm, want));
+    if (max_ctas > 0) grid = std::min(grid, max_ctas);     // a caller with bounded scratch narrows the launch
+    if (ctas_out) *ctas_out = grid;
     void* args[] = {&prm};
     OEQ_CUDA(cudaLaunchKernel((const void*)k.fn, dim3((unsigned)grid), dim3((unsigned)k.threads()), args,
                               (size_t)k.smem, stream));
@@ -1212,6 +1220,7 @@ int oeq_tp_forward(oeq_tp* h, int64_t batch, const void* X, const void* Y, const
             tp{X, Y, h->d_packed, Z, batch, h->d_status, nullptr};
         void* args[] = {&tp};
         const long long grid = std::max<long long>(1, std::min<long long>(k.sm_count, (batch + 23) / 24));
+#ifdef OEQ_DEV_PROFILE
         if (env_int("OEQ_B200_TC_PROFILE", 0)) {
             // cycle accounting of the roles of CTA 0 (development aid): synchronous, prints to stderr
             OEQ_CUDA(cudaMalloc(&tp.prof, 32 * 8));
@@ -1225,6 +1234,7 @@ int oeq_tp_forward(oeq_tp* h, int64_t batch, const void* X, const void* Y, const
                             "epilogue: tiles %llu wait %llu drain %llu\n", hb[2], hb[0], hb[1], hb[8], hb[9], hb[18], hb[16], hb[17]);
             return OEQ_OK;
         }
+#endif
         OEQ_CUDA(cudaLaunchKernel((const void*)k.fn, dim3((unsigned)grid), dim3(21 * 32), args, (size_t)k.smem, st));
         return OEQ_OK;
     }
@@ -1331,6 +1341,7 @@ int oeq_tp_backward(oeq_tp* h, int64_t batch, const void* X, const void* Y, cons
                 OEQ_CUDA(cudaMemsetAsync(dY, 0, (size_t)batch * p.y_dim * p.elem(), st));
                 tp.Wt = h->d_packed_t;
                 const long long ctas_x = std::max<long long>(1, std::min<long long>(kx.sm_count, (batch + 23) / 24));
+#ifdef OEQ_DEV_PROFILE
                 if (env_int("OEQ_B200_TC_PROFILE", 0)) {
                     // cycle accounting of the roles of CTA 0 (development aid): synchronous, prints to stderr
                     OEQ_CUDA(cudaMalloc(&tp.prof, 32 * 8));
@@ -1345,6 +1356,7 @@ int oeq_tp_backward(oeq_tp* h, int64_t batch, const void* X, const void* Y, cons
                             hb[10], hb[16], hb[17], hb[18], hb[19], hb[26], hb[24], hb[25]);
                     return OEQ_OK;
                 }
+#endif
                 OEQ_CUDA(cudaLaunchKernel((const void*)kx.fn, dim3((unsigned)ctas_x), dim3(16 * 32), targs, (size_t)kx.smem, st));
                 return OEQ_OK;
             }
@@ -1429,11 +1441,13 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH
 // In host code the array's name only stands for the symbol; the device address is looked up
 // once per device (with that device current) and remembered here.
 static void* g_noalloc_scratch_addr[64] = {nullptr};
+static std::mutex g_noalloc_mutex;
 
 static int noalloc_scratch(void** out) {
     int dev = 0;
     OEQ_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return fail(OEQ_ERR_INVALID, "device ordinal out of range");
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);     // two host threads may make a device's first call at once
     if (!g_noalloc_scratch_addr[dev]) {
         void* ptr = nullptr;
         OEQ_CUDA(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
@@ -1460,7 +1474,9 @@ int oeq_tp_backward_noalloc(oeq_tp* h, int64_t batch, const void* X, const void*
     void* scratch = nullptr;
     int rc = noalloc_scratch(&scratch);
     if (rc) return rc;
+    h->last_stream = st;       // oeq_tp_check synchronises the stream of the most recent launch
     if (p.mode == OEQ_MODE_UVW) {
+        // always the FMA kernel: the tensor-core kernels want packed weight copies that only cudaMalloc gives
         if ((rc = load_uvw(h->bwd, p, true))) return rc;
         long long ctas = std::min(uvw_grid(h->bwd, batch), max_slices);
         UvwParams up{};
@@ -1477,22 +1493,14 @@ int oeq_tp_backward_noalloc(oeq_tp* h, int64_t batch, const void* X, const void*
     }
     if ((rc = load_kernel(h->bwd, "oeq_uvu_kernel", true))) return rc;
     Kernel& k = h->bwd;
-    const long long grid = std::min(uvu_grid(k, batch), max_slices / k.map.ng);
-    if (grid < 1)
+    const long long max_ctas = max_slices / k.map.ng;
+    if (max_ctas < 1)
         return fail(OEQ_ERR_UNSUPPORTED, "one CTA's partial gradients exceed the built-in scratch; use oeq_tp_backward");
     UvuParams prm{};
     prm.X = X; prm.Y = Y; prm.W = W; prm.dZ = dZ; prm.dX = dX; prm.dY = dY; prm.dW = dW;
     prm.n_items = batch; prm.n_nodes = batch; prm.status = h->d_status; prm.ws = scratch;
-    const int e = p.elem();
-    int flags = 0;
-    if ((p.x_dim * e) % 16 == 0 && aligned16(X)) flags |= 1;
-    if ((p.y_dim * e) % 16 == 0 && aligned16(Y)) flags |= 2;
-    if ((p.z_dim * e) % 16 == 0 && aligned16(dZ)) flags |= 8;
-    prm.flags = flags;
-    prm.stages = k.stages;
-    prm.chunk = 64;
-    void* args[] = {&prm};
-    OEQ_CUDA(cudaLaunchKernel((const void*)k.fn, dim3((unsigned)grid), dim3((unsigned)k.map.threads()), args, (size_t)k.smem, st));
+    long long grid = 0;
+    if ((rc = launch_uvu(k, p, prm, st, 0, max_ctas, &grid))) return rc;
     long long groups = grid * k.map.ng;
     int n = p.w_numel;
     const void* ws = scratch;
@@ -1564,6 +1572,7 @@ int oeq_conv_forward(oeq_conv* h, int64_t nodes, int64_t edges, const void* X, c
     prm.rows = (const long long*)rows; prm.cols = (const long long*)cols;
     prm.n_items = edges; prm.n_nodes = nodes; prm.status = h->d_status;
     h->last_stream = st;
+#ifdef OEQ_DEV_PROFILE
     if (tc && env_int("OEQ_B200_TC_PROFILE", 0)) {
         // cycle accounting of the roles of CTA 0 (development aid): synchronous, prints to stderr
         unsigned long long* d = nullptr;
@@ -1582,6 +1591,7 @@ int oeq_conv_forward(oeq_conv* h, int64_t nodes, int64_t edges, const void* X, c
                     hbuf[8 * r + 6], hbuf[8 * r + 7]);
         return rc;
     }
+#endif
     return launch_uvu(tc ? h->fwd_tc : h->fwd, p, prm, st);
 }
 
@@ -1609,6 +1619,7 @@ int oeq_conv_backward(oeq_conv* h, int64_t nodes, int64_t edges, const void* X, 
     prm.rows = (const long long*)rows; prm.cols = (const long long*)cols; prm.perm = (const long long*)perm;
     prm.n_items = edges; prm.n_nodes = nodes; prm.status = h->d_status;
     h->last_stream = st;
+#ifdef OEQ_DEV_PROFILE
     if (env_int("OEQ_B200_UVU_PROFILE", 0)) {
         // cycle accounting of CTA 0's first group (development aid): synchronous, prints to stderr
         unsigned long long* d = nullptr;
@@ -1624,6 +1635,7 @@ int oeq_conv_backward(oeq_conv* h, int64_t nodes, int64_t edges, const void* X, 
                         "waiting for a stage %llu walking %llu issuing %llu\n", hb[0], hb[1], hb[2], hb[4], hb[5], hb[6], hb[7]);
         return rc;
     }
+#endif
     return launch_uvu(h->bwd, p, prm, st);
 }
 

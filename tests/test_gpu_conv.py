@@ -250,3 +250,53 @@ def test_widest_rows_many_chunks_per_group(chunk, monkeypatch):
     assert rel_err(dxa.cpu().numpy(), dx.cpu().numpy()) < 1e-5
     assert rel_err(dya.cpu().numpy(), dy.cpu().numpy()) < 1e-5
     assert rel_err(dwa.cpu().numpy(), dw.cpu().numpy()) < 1e-5
+
+
+_periodic_cache = {}
+
+
+def _periodic_case(name, nodes, lmax):
+    """Graph, inputs and oracle results of one periodic-graph case, evaluated once for both variants."""
+    from openequivariance_b200.graph import periodic_radius_graph, spherical_harmonics
+    key = (name, nodes, lmax)
+    if key not in _periodic_cache:
+        p = problem_by_name(name)
+        g = periodic_radius_graph(nodes, 30.0, seed=5, numbering="morton")
+        x, _, w, dz = conv_inputs(p, nodes, g.nnz, 41)
+        y = spherical_harmonics(lmax, g.vectors).astype(np.float32)
+        z_ref = orc.conv_forward(p, x, y, w, g.rows, g.cols)
+        grads = orc.conv_backward(p, x, y, w, dz, g.rows, g.cols)
+        _periodic_cache[key] = (p, g, (x, y, w, dz), z_ref, grads)
+    return _periodic_cache[key]
+
+
+@pytest.mark.parametrize("deterministic", [False, True], ids=["atomic", "deterministic"])
+@pytest.mark.parametrize("name,nodes,lmax", [("nequip_32", 1500, 2), ("mace_large_128", 400, 3)])
+def test_periodic_radius_graph(name, nodes, lmax, deterministic):
+    """The benchmark's own graph class: points uniform in a periodic cube, both directions of every pair within
+    the cutoff for mean degree 30, Morton-ordered node ids, spherical harmonics of the edge vectors as the
+    second input.  (The wide problem runs on fewer nodes so that the float64 oracle's [E, Z.dim] messages fit.)"""
+    p, g, (x, y, w, dz), z_ref, (rx, ry, rw) = _periodic_case(name, nodes, lmax)
+    edges = g.nnz
+    assert abs(edges / nodes - 30.0) < 3.0
+    # structurally symmetric: every (r, s) has its (s, r)
+    fwd = set(zip(g.rows[:2000].tolist(), g.cols[:2000].tolist()))
+    allp = set(zip(g.rows.tolist(), g.cols.tolist()))
+    assert all((s, r) in allp for r, s in fwd)
+    conv = oeq.TensorProductConv(p, torch_op=True, deterministic=deterministic)
+    index = cuda(g.rows, g.cols, g.sender_perm) if deterministic else cuda(g.rows, g.cols)
+    xt, yt, wt, dzt = cuda(x, y, w, dz)
+    z = conv.forward(xt, yt, wt, *index)
+    dx, dy, dw = conv.backward_helper(xt, yt, wt, dzt, *index)
+    torch.cuda.synchronize()
+    conv.check_device_status()
+    tol = REL_TOL[np.float32]
+    assert rel_err(z.cpu().numpy(), z_ref) < tol
+    assert rel_err(dx.cpu().numpy(), rx) < tol
+    assert rel_err(dy.cpu().numpy(), ry) < tol
+    assert rel_err(dw.cpu().numpy(), rw) < tol
+    if deterministic:
+        for _ in range(4):                       # the reference repeats five runs and wants equal bits
+            z2 = conv.forward(xt, yt, wt, *index)
+            dx2, dy2, dw2 = conv.backward_helper(xt, yt, wt, dzt, *index)
+            assert torch.equal(z, z2) and torch.equal(dx, dx2) and torch.equal(dy, dy2) and torch.equal(dw, dw2)
