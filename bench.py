@@ -14,8 +14,13 @@ One JSON line is printed by rank 0.  ``value`` is edges processed per second by 
 for one forward plus one backward pass with inputs resident in HBM; ``e2e`` is the same with
 every input copied from pinned host memory and every output copied back inside the timed
 region.  For N > 1 the graph is split by receiver range (strong scaling): sender features are
-all-gathered before the forward kernel and their gradients reduce-scattered after the backward
-kernel, both inside the timed region (only halo rows -- senders owned by another rank -- move).
+exchanged before the forward kernel and their gradients after the backward kernels, both inside
+the timed region (only halo rows -- senders owned by another rank -- move).
+
+Beside the headline the line carries ``parity`` (rows of Z, dX, dY, dW of the benchmark's own inputs
+checked against the float64 CPU oracle on rank 0, outside every timed region), ``peaks`` (matmul peaks
+measured in this run), ``secondary`` (the other configurations: batch 'uvu', Nequip convolution,
+'uvw' in FP32 and FP64) and ``random_numbering`` (the headline workload with random node ids).
 """
 
 import argparse
@@ -45,10 +50,11 @@ WORKLOADS = {
 }
 
 
-# DRAM read+write bytes per edge of the deterministic backward launch, from a one-pass ncu capture
-# (dram__bytes_read.sum + dram__bytes_write.sum) of the full-size run; proportional to the edge count
-# at fixed degree, so it scales to other --nodes values of the same workload.
-NCU_BWD_DRAM_BYTES_PER_EDGE = {("mace_large", "morton"): 377.4e9 / 6004880}
+# DRAM read+write bytes per edge of the deterministic backward pass (all its launches), from an ncu
+# capture (dram__bytes_read.sum + dram__bytes_write.sum) of a small case of the same workload; the
+# capture's case and date are named in the line ("traffic_from").  Only the per-edge arrays scale with
+# the edge count, so this is an estimate for other sizes, and it is refreshed when the kernels change.
+NCU_BWD_DRAM = {}   # (workload, numbering) -> (bytes per edge, "what was captured")
 
 
 def parse_args():
@@ -64,7 +70,10 @@ def parse_args():
     ap.add_argument("--variant", default="deterministic", choices=["deterministic", "atomic"])
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--e2e-steps", type=int, default=2)
+    ap.add_argument("--no-parity", action="store_true")
+    ap.add_argument("--no-secondary", action="store_true",
+                    help="skip the other configurations, the matmul peaks and the random-numbering run")
+    ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--slab-edges", type=int, default=1 << 18,
                     help="edges per slab of the streamed host-tensor path (end-to-end measurement)")
     ap.add_argument("--seed", type=int, default=11111)
@@ -76,12 +85,14 @@ def make_problem(spec):
     return oeq.ChannelwiseTPP(spec["in1"], spec["in2"], spec["out"])
 
 
-def algorithmic_bytes(problem, nodes, edges, elem=4):
-    """Compulsory HBM traffic of one launch: every edge array once, every node array once,
-    int64 receiver/sender (and the sender-order permutation in the backward pass)."""
+def algorithmic_bytes(problem, nodes, edges, elem=4, x_rows=None):
+    """Compulsory HBM traffic of one pass: every edge array once, every node array once,
+    int64 receiver/sender (and the sender-order permutation in the backward pass).  ``x_rows``:
+    rows of X / dX a shard touches (owned + halo) when that differs from its output rows."""
     x, y, z, w = problem.irreps_in1.dim, problem.irreps_in2.dim, problem.irreps_out.dim, problem.weight_numel
-    fwd = edges * ((w + y) * elem + 16) + nodes * (x + z) * elem
-    bwd = edges * (2 * (w + y) * elem + 24) + nodes * (2 * x + z) * elem
+    xr = nodes if x_rows is None else x_rows
+    fwd = edges * ((w + y) * elem + 16) + (xr * x + nodes * z) * elem
+    bwd = edges * (2 * (w + y) * elem + 24) + (2 * xr * x + nodes * z) * elem
     return fwd, bwd
 
 
@@ -137,10 +148,52 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def build_graph(spec, args):
+def build_graph(spec, args, numbering=None):
     from openequivariance_b200.graph import periodic_radius_graph
     nodes = args.nodes or spec["nodes"]
-    return periodic_radius_graph(nodes, spec["degree"], seed=args.seed, numbering=args.numbering)
+    return periodic_radius_graph(nodes, spec["degree"], seed=args.seed, numbering=numbering or args.numbering)
+
+
+# --------------------------------------------------------------------------- seeded inputs
+#
+# Every array of the workload is a function of (seed, stream, row): rows are drawn in fixed-size slices,
+# each from a generator seeded by the slice index, so any rank -- and the parity check -- can reproduce any
+# row of any array without communication and without trusting the exchange it is checking.
+
+SLICE_ROWS = 1 << 14
+STREAM_X, STREAM_DZ, STREAM_W = 1, 2, 3
+
+
+def _slice_seed(seed, stream, index):
+    return (seed * 1_000_003 + stream * 100_000_007 + index) % (1 << 62)
+
+
+def seeded_rows(torch, seed, stream, row_lo, row_hi, width, device):
+    """Rows [row_lo, row_hi) of the N(0,1) array `stream`, as a device tensor."""
+    out = torch.empty((row_hi - row_lo, width), device=device, dtype=torch.float32)
+    gen = torch.Generator(device=device)
+    pos = row_lo
+    while pos < row_hi:
+        index, off = divmod(pos, SLICE_ROWS)
+        take = min(SLICE_ROWS - off, row_hi - pos)
+        gen.manual_seed(_slice_seed(seed, stream, index))
+        block = torch.randn((SLICE_ROWS, width), device=device, dtype=torch.float32, generator=gen)
+        out[pos - row_lo:pos - row_lo + take] = block[off:off + take]
+        pos += take
+    return out
+
+
+def seeded_rows_at(torch, seed, stream, ids, width, device):
+    """The rows `ids` (any order, repeats allowed) of the same array, regenerated slice by slice."""
+    ids = np.asarray(ids, dtype=np.int64)
+    out = torch.empty((len(ids), width), device=device, dtype=torch.float32)
+    gen = torch.Generator(device=device)
+    for index in np.unique(ids // SLICE_ROWS):
+        sel = np.nonzero(ids // SLICE_ROWS == index)[0]
+        gen.manual_seed(_slice_seed(seed, stream, int(index)))
+        block = torch.randn((SLICE_ROWS, width), device=device, dtype=torch.float32, generator=gen)
+        out[torch.from_numpy(sel).to(device)] = block[torch.from_numpy(ids[sel] - index * SLICE_ROWS).to(device)]
+    return out
 
 
 # --------------------------------------------------------------------------- CPU baseline
@@ -185,8 +238,9 @@ def cpu_baseline(problem, spec, graph, steps, warmup, seed):
     per_step = sum(times) / len(times)
     return {"value": sample / per_step, "unit": "edges/s", "cores": cores, "kind": "port",
             "sample": f"first {sample} receiver-sorted edges of the workload in chunks of {chunk}, "
-                      f"{len(times)} timed passes, torch CPU float32 (gather, per-instruction contraction with the second "
-                      f"input folded into the Clebsch-Gordan tensor, index_add), autograd backward",
+                      f"{warmup} warm-up and {len(times)} timed passes, torch CPU float32 (gather, per-instruction "
+                      f"contraction with the second input folded into the Clebsch-Gordan tensor, index_add), "
+                      f"autograd backward",
             "ms_per_step": per_step * 1e3}
 
 
@@ -197,10 +251,11 @@ def run_reference(args):
     spec = WORKLOADS[args.workload]
     problem = make_problem(spec)
     graph = build_graph(spec, args)
-    base = cpu_baseline(problem, spec, graph, max(1, args.steps), max(0, min(args.warmup, 1)), args.seed)
+    steps, warmup = max(1, args.steps), max(0, args.warmup)
+    base = cpu_baseline(problem, spec, graph, steps, warmup, args.seed)
     line = {
         "impl": "reference", "metric": "conv_fwd_bwd_edges_per_s", "value": base["value"], "unit": "edges/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_step"],
+        "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": base["ms_per_step"],
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(args, spec, graph),
         "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
@@ -210,16 +265,199 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
-def workload_config(args, spec, graph):
+def workload_config(args, spec, graph, numbering=None):
     return {"workload": f"{args.workload}: fused conv uvu {spec['in1']} x {spec['in2']} -> l_out<={spec['lmax']}, "
                         f"{args.variant}, fwd+bwd",
             "nodes": graph.node_count, "edges": graph.nnz, "mean_degree": graph.nnz / max(1, graph.node_count),
-            "numbering": args.numbering, "graph": "uniform points in a periodic unit cube, radius cutoff",
+            "numbering": numbering or args.numbering, "graph": "uniform points in a periodic unit cube, radius cutoff",
             "l2": "inputs larger than L2 (no flush needed)" if graph.nnz > 200_000 else "small case",
             "parallelism": f"receiver-range shards x{args.gpus}" if args.gpus > 1 else "single GPU"}
 
 
+# --------------------------------------------------------------------------- parity on the benchmark's inputs
+
+def parity_check(torch, args, spec, problem, graph, conv, plan, y, w, outputs, device, rows_wanted=64):
+    """Rows of the step's results against the float64 oracle, on rank 0, outside every timed region.
+
+    Receivers: every edge of a receiver is on its owner's rank, so Z, dY and dW rows are checked from the
+    rank's own Y and W and from X rows regenerated from the seed (not taken from the exchange).  Senders:
+    the edges a node sends may live on any rank; their W and dZ rows are regenerated from the seed and Y
+    from the graph's edge vectors, so dX of nodes in other ranks' halos checks the return exchange."""
+    from oracle import tp_oracle as orc
+    from openequivariance_b200.graph import spherical_harmonics
+    z, dx, dy, dw = outputs
+    seed = args.seed
+    xd, zd, wn = problem.irreps_in1.dim, problem.irreps_out.dim, problem.weight_numel
+    rng = np.random.default_rng(seed)
+    node_lo, owned, e_lo = plan.node_lo, plan.owned, plan.edge_lo
+    half = rows_wanted // 2
+
+    def rel(got, want):
+        want = np.asarray(want, dtype=np.float64)
+        return float(np.abs(np.asarray(got, dtype=np.float64) - want).max() / max(np.abs(want).max(), 1e-30))
+
+    # receivers: those with a sender in the halo first, then random ones
+    local_rows, local_cols = plan.local_rows, plan.local_cols
+    with_halo = np.unique(local_rows[local_cols >= owned])
+    pick = list(rng.choice(with_halo, size=min(half, len(with_halo)), replace=False)) if len(with_halo) else []
+    pick += list(rng.choice(owned, size=min(rows_wanted - len(pick), owned), replace=False))
+    recv = np.unique(np.asarray(pick, dtype=np.int64))
+    lo = np.searchsorted(local_rows, recv, side="left")
+    hi = np.searchsorted(local_rows, recv, side="right")
+    eidx = np.concatenate([np.arange(a, b) for a, b in zip(lo, hi)]) if len(recv) else np.zeros(0, np.int64)
+    out = {"rows": int(len(recv)), "edges": int(len(eidx))}
+    if len(eidx):
+        glob_cols = graph.cols[e_lo + eidx]
+        senders, cols_small = np.unique(glob_cols, return_inverse=True)
+        rows_small = np.searchsorted(recv, local_rows[eidx])
+        n = max(len(senders), len(recv))
+        x_s = np.zeros((n, xd), np.float32)
+        x_s[:len(senders)] = seeded_rows_at(torch, seed, STREAM_X, senders, xd, device).cpu().numpy()
+        ei = torch.from_numpy(eidx).to(device)
+        y_s, w_s = y[ei].cpu().numpy(), w[ei].cpu().numpy()
+        dz_s = np.zeros((n, zd), np.float32)
+        dz_s[:len(recv)] = seeded_rows_at(torch, seed, STREAM_DZ, node_lo + recv, zd, device).cpu().numpy()
+        z_ref = orc.conv_forward(problem, x_s, y_s, w_s, rows_small, cols_small)[:len(recv)]
+        _, dy_ref, dw_ref = orc.conv_backward(problem, x_s, y_s, w_s, dz_s, rows_small, cols_small)
+        ri = torch.from_numpy(recv).to(device)
+        out["z_rel"] = rel(z[ri].cpu().numpy(), z_ref)
+        out["dy_rel"] = rel(dy[ei].cpu().numpy(), dy_ref)
+        out["dw_rel"] = rel(dw[ei].cpu().numpy(), dw_ref)
+
+    # senders: nodes that other ranks read (their dX sums contributions that came back), then random ones
+    shared = np.unique(np.concatenate(plan.send_rows)) if plan.send_rows is not None and len(plan.send_rows) else np.zeros(0, np.int64)
+    pick = list(rng.choice(shared, size=min(half, len(shared)), replace=False)) if len(shared) else []
+    pick += list(rng.choice(owned, size=min(rows_wanted - len(pick), owned), replace=False))
+    send = np.unique(np.asarray(pick, dtype=np.int64))
+    by_sender = graph.cols[graph.sender_perm]                     # senders in sender order (non-decreasing)
+    lo = np.searchsorted(by_sender, node_lo + send, side="left")
+    hi = np.searchsorted(by_sender, node_lo + send, side="right")
+    ge = np.concatenate([graph.sender_perm[a:b] for a, b in zip(lo, hi)]) if len(send) else np.zeros(0, np.int64)
+    out["sender_rows"], out["sender_edges"] = int(len(send)), int(len(ge))
+    if len(ge):
+        receivers, rows_small = np.unique(graph.rows[ge], return_inverse=True)
+        cols_small = np.searchsorted(send, graph.cols[ge] - node_lo)
+        n = max(len(send), len(receivers))
+        x_s = np.zeros((n, xd), np.float32)
+        x_s[:len(send)] = seeded_rows_at(torch, seed, STREAM_X, node_lo + send, xd, device).cpu().numpy()
+        dz_s = np.zeros((n, zd), np.float32)
+        dz_s[:len(receivers)] = seeded_rows_at(torch, seed, STREAM_DZ, receivers, zd, device).cpu().numpy()
+        w_s = seeded_rows_at(torch, seed, STREAM_W, ge, wn, device).cpu().numpy()
+        vec = torch.from_numpy(graph.vectors[ge]).to(device=device, dtype=torch.float32)
+        y_s = spherical_harmonics(spec["lmax"], vec).contiguous().cpu().numpy()
+        dx_ref = orc.conv_backward(problem, x_s, y_s, w_s, dz_s, rows_small, cols_small)[0][:len(send)]
+        si = torch.from_numpy(send).to(device)
+        out["dx_rel"] = rel(dx[si].cpu().numpy(), dx_ref)
+    out["tolerance"] = 1e-5
+    out["ok"] = all(out.get(k, 0.0) < 1e-5 for k in ("z_rel", "dx_rel", "dy_rel", "dw_rel"))
+    return out
+
+
 # --------------------------------------------------------------------------- GPU benchmark
+
+def matmul_peaks(torch):
+    """Dense matmul peaks of this GPU (torch.matmul, best of 10, CUDA events): the denominators of the
+    'uvw' tensor-pipe and FP64 fractions.  A peak probe, not a product path."""
+    def one(dtype, n, tf32):
+        old = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = tf32
+        try:
+            a = torch.randn(n, n, device="cuda", dtype=dtype)
+            b = torch.randn(n, n, device="cuda", dtype=dtype)
+            for _ in range(3):
+                a @ b
+            torch.cuda.synchronize()
+            best = float("inf")
+            for _ in range(10):
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s.record()
+                a @ b
+                e.record()
+                torch.cuda.synchronize()
+                best = min(best, s.elapsed_time(e))
+            return 2 * n ** 3 / best / 1e9
+        finally:
+            torch.backends.cuda.matmul.allow_tf32 = old
+    return {"tf32_tflops": one(torch.float32, 8192, True), "fp32_tflops": one(torch.float32, 8192, False),
+            "fp64_tflops": one(torch.float64, 4096, False),
+            "how": "torch.matmul 8192^3 (FP64: 4096^3), best of 10, CUDA events; TF32 with allow_tf32=True"}
+
+
+def conv_case(torch, args, spec, workload, device, variant, numbering, nodes=None, steps=5, warmup=3):
+    """Forward + backward kernel times of one single-GPU convolution workload (inputs resident)."""
+    import openequivariance_b200 as oeq
+    from openequivariance_b200.graph import periodic_radius_graph, spherical_harmonics
+    problem = make_problem(spec)
+    g = periodic_radius_graph(nodes or spec["nodes"], spec["degree"], seed=args.seed, numbering=numbering)
+    det = variant == "deterministic"
+    conv = oeq.TensorProductConv(problem, torch_op=True, deterministic=det)
+    idx = [torch.from_numpy(a).to(device) for a in ((g.rows, g.cols, g.sender_perm) if det else (g.rows, g.cols))]
+    gen = torch.Generator(device=device).manual_seed(args.seed)
+    x = torch.randn(g.node_count, problem.irreps_in1.dim, device=device, generator=gen)
+    dz = torch.randn(g.node_count, problem.irreps_out.dim, device=device, generator=gen)
+    y = spherical_harmonics(spec["lmax"], torch.from_numpy(g.vectors).to(device=device, dtype=torch.float32)).contiguous()
+    w = torch.empty(g.nnz, problem.weight_numel, device=device)
+    for lo in range(0, g.nnz, 1 << 19):
+        w[lo:lo + (1 << 19)].normal_(generator=gen)
+    small = g.nnz * (problem.weight_numel + problem.irreps_in2.dim) * 4 < (256 << 20)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device) if small else None
+    tf, tb = [], []
+    for i in range(warmup + steps):
+        if flush is not None:
+            flush.zero_()
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        e[0].record()
+        z = conv._forward_impl(x, y, w, *idx)
+        e[1].record()
+        out = conv._backward_impl(x, y, w, dz, *idx)
+        e[2].record()
+        torch.cuda.synchronize()
+        del z, out
+        if i >= warmup:
+            tf.append(e[0].elapsed_time(e[1]))
+            tb.append(e[1].elapsed_time(e[2]))
+    conv.check_device_status()
+    fwd, bwd = statistics.median(tf), statistics.median(tb)
+    fb, bb = algorithmic_bytes(problem, g.node_count, g.nnz)
+    peak, _ = measured_peak()
+    res = {"workload": workload, "variant": variant, "numbering": numbering, "nodes": g.node_count, "edges": g.nnz,
+           "forward_ms": fwd, "backward_ms": bwd, "edges_per_s": g.nnz / ((fwd + bwd) * 1e-3),
+           "hbm_frac_forward": fb / (fwd * 1e-3) / 1e9 / peak, "hbm_frac_backward": bb / (bwd * 1e-3) / 1e9 / peak,
+           "hbm_frac_fwd_bwd": (fb + bb) / ((fwd + bwd) * 1e-3) / 1e9 / peak,
+           "l2": "flushed before every step" if small else "inputs larger than L2"}
+    del conv, x, y, w, dz, idx
+    torch.cuda.empty_cache()
+    return res
+
+
+def secondary_block(torch, args, device, peaks):
+    """The other configurations, measured in this process with the same protocol (CUDA events, L2 flushed or
+    inputs larger than L2): batch 'uvu' (50 000 rows), Nequip convolution both variants, 'uvw' FP32 / FP64."""
+    from openequivariance_b200 import bench_tp
+    peak, _ = measured_peak()
+    out = {}
+    r = bench_tp.measure("uvu_mace", "f32", steps=10, warmup=3)
+    out["batch_uvu_mace_50k"] = {
+        "rows_per_s_fwd_bwd": r["rows_per_s_fwd_bwd"], "forward_ms": r["forward_ms"], "backward_ms": r["backward_ms"],
+        "hbm_frac_forward": r["forward_GBps"] / peak, "hbm_frac_backward": r["backward_GBps"] / peak,
+        "hbm_frac_fwd_bwd": (r["algorithmic_bytes"]["forward"] + r["algorithmic_bytes"]["backward"])
+                            / ((r["forward_ms"] + r["backward_ms"]) * 1e-3) / 1e9 / peak}
+    for variant in ("deterministic", "atomic"):
+        out[f"conv_nequip_{variant}"] = conv_case(torch, args, WORKLOADS["nequip"], "nequip", device, variant, "morton")
+    out["conv_mace_large_atomic_20k_nodes"] = conv_case(torch, args, WORKLOADS["mace_large"], "mace_large", device,
+                                                        "atomic", "morton", nodes=20_000)
+    for dt, pk in (("f32", peaks["tf32_tflops"]), ("f64", peaks["fp64_tflops"])):
+        r = bench_tp.measure("uvw_fc", dt, steps=10, warmup=3)
+        out[f"batch_uvw_fc_100k_{dt}"] = {
+            "forward_ms": r["forward_ms"], "backward_ms": r["backward_ms"], "rows_per_s_fwd_bwd": r["rows_per_s_fwd_bwd"],
+            "logical_tflops_forward": r["forward_contraction_TFLOPs"],
+            "logical_tflops_fwd_bwd": r["fwd_bwd_contraction_TFLOPs"],
+            # FP32 runs as 3xTF32: three tensor-core products per logical one
+            "frac_of_measured_peak_forward": r["forward_contraction_TFLOPs"] * (3 if dt == "f32" else 1) / pk,
+            "frac_of_measured_peak_fwd_bwd": r["fwd_bwd_contraction_TFLOPs"] * (3 if dt == "f32" else 1) / pk,
+            "peak": "tf32_tflops (issued = 3 x logical)" if dt == "f32" else "fp64_tflops"}
+    return out
+
 
 def run_ours(args):
     import torch
@@ -240,131 +478,179 @@ def run_ours(args):
 
     spec = WORKLOADS[args.workload]
     problem = make_problem(spec)
-    graph = build_graph(spec, args)
-    nodes, edges = graph.node_count, graph.nnz
     det = args.variant == "deterministic"
     if not det and world > 1:
         raise SystemExit("the sharded benchmark runs the deterministic variant")
-
-    if det:
-        conv = ShardedTensorProductConv(problem, graph.rows, graph.cols, nodes, device=device)
-        plan = conv.plan
-        e_lo, e_hi, owned = plan.edge_lo, plan.edge_hi, plan.owned
-    else:
-        conv = oeq.TensorProductConv(problem, torch_op=True, deterministic=False)
-        e_lo, e_hi, owned = 0, edges, nodes
-        rows_d = torch.from_numpy(graph.rows).to(device)
-        cols_d = torch.from_numpy(graph.cols).to(device)
-    local_edges = e_hi - e_lo
-
-    gen = torch.Generator(device=device).manual_seed(args.seed + rank)
-    x = torch.randn(owned, problem.irreps_in1.dim, device=device, generator=gen)
-    dz = torch.randn(owned, problem.irreps_out.dim, device=device, generator=gen)
-    vec = torch.from_numpy(graph.vectors[e_lo:e_hi]).to(device=device, dtype=torch.float32)
-    y = spherical_harmonics(spec["lmax"], vec).contiguous()
-    del vec
-    w = torch.empty(local_edges, problem.weight_numel, device=device)
-    for lo in range(0, local_edges, 1 << 19):          # fill in slices: no temporary of W's size
-        w[lo:lo + (1 << 19)].normal_(generator=gen)
-
-    def step():
-        if det:
-            return conv.forward_backward(x, y, w, dz)
-        z = conv.forward(x, y, w, rows_d, cols_d)
-        dx, dy, dw = conv.backward_helper(x, y, w, dz, rows_d, cols_d)
-        return z, dx, dy, dw
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(3, args.warmup)):
-        out = step()
-        del out
-    barrier()
-
-    # -- timed region: device events per step, fwd and bwd kernels timed separately on rank's stream
-    sampler = ClockSampler(local_rank if os.environ.get("CUDA_VISIBLE_DEVICES") is None else 0)
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
-    inner = conv.conv if det else conv
-    sampler.start()
-    barrier()
-    t0 = time.perf_counter()
-    for k in range(args.steps):
+    def measure(numbering, steps, with_parity, with_e2e):
+        """One workload instance: set-up, warm-up, timed steps, then (untimed) parity and the host-tensor step."""
+        graph = build_graph(spec, args, numbering)
+        nodes, edges = graph.node_count, graph.nnz
         if det:
-            x_full = conv.gather_senders(x)
-            ev[k][0].record()
-            z = conv.local_forward(x_full, y, w)
-            ev[k][1].record()
-            dx_all, dy, dw = conv.local_backward(x_full, y, w, dz)
-            ev[k][2].record()
-            dx = conv.scatter_sender_grads(dx_all)
-            ev[k][3].record()
-            del z, dx_all, dy, dw, dx
+            conv = ShardedTensorProductConv(problem, graph.rows, graph.cols, nodes, device=device)
+            plan = conv.plan
+            e_lo, e_hi, owned = plan.edge_lo, plan.edge_hi, plan.owned
         else:
-            ev[k][0].record()
+            conv = oeq.TensorProductConv(problem, torch_op=True, deterministic=False)
+            plan = None
+            e_lo, e_hi, owned = 0, edges, nodes
+            rows_d = torch.from_numpy(graph.rows).to(device)
+            cols_d = torch.from_numpy(graph.cols).to(device)
+        local_edges = e_hi - e_lo
+        node_lo = plan.node_lo if plan is not None else 0
+        x = seeded_rows(torch, args.seed, STREAM_X, node_lo, node_lo + owned, problem.irreps_in1.dim, device)
+        dz = seeded_rows(torch, args.seed, STREAM_DZ, node_lo, node_lo + owned, problem.irreps_out.dim, device)
+        vec = torch.from_numpy(graph.vectors[e_lo:e_hi]).to(device=device, dtype=torch.float32)
+        y = spherical_harmonics(spec["lmax"], vec).contiguous()
+        del vec
+        w = seeded_rows(torch, args.seed, STREAM_W, e_lo, e_hi, problem.weight_numel, device)
+
+        def step():
+            if det:
+                return conv.forward_backward(x, y, w, dz)
             z = conv.forward(x, y, w, rows_d, cols_d)
-            ev[k][1].record()
             dx, dy, dw = conv.backward_helper(x, y, w, dz, rows_d, cols_d)
-            ev[k][2].record()
-            ev[k][3].record()
-            del z, dx, dy, dw
-    barrier()
-    elapsed = time.perf_counter() - t0
-    clocks = sampler.stop()
-    inner.check_device_status()
+            return z, dx, dy, dw
 
-    fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
-    bwd_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
-    t = torch.tensor([elapsed, fwd_ms, bwd_ms], device=device, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    elapsed, fwd_ms_max, bwd_ms_max = t.tolist()
-    ms_per_step = elapsed / args.steps * 1e3
-    value = edges / (elapsed / args.steps)
+        for _ in range(max(3, args.warmup)):
+            out = step()
+            del out
+        barrier()
 
-    # -- roofline of the dominant kernel (backward), rank 0's launch
-    fb, bb = algorithmic_bytes(problem, owned if world > 1 else nodes, local_edges)
-    if world > 1:   # a shard reads/writes its owned and halo rows of X / dX once, owned rows of Z / dZ
-        xd, zd = problem.irreps_in1.dim, problem.irreps_out.dim
-        fb = local_edges * ((problem.weight_numel + problem.irreps_in2.dim) * 4 + 16) + (plan.local_nodes * xd + owned * zd) * 4
-        bb = local_edges * (2 * (problem.weight_numel + problem.irreps_in2.dim) * 4 + 24) + (2 * plan.local_nodes * xd + owned * zd) * 4
+        # -- timed region: device events per step, fwd and bwd passes timed separately on the rank's stream
+        sampler = ClockSampler(local_rank if os.environ.get("CUDA_VISIBLE_DEVICES") is None else 0)
+        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(steps)]
+        inner = conv.conv if det else conv
+        sampler.start()
+        barrier()
+        t0 = time.perf_counter()
+        for k in range(steps):
+            if det:
+                x_full = conv.gather_senders(x)
+                ev[k][0].record()
+                z = conv.local_forward(x_full, y, w)
+                ev[k][1].record()
+                dx_all, dy, dw = conv.local_backward(x_full, y, w, dz)
+                ev[k][2].record()
+                dx = conv.scatter_sender_grads(dx_all)
+                ev[k][3].record()
+                del z, dx_all, dy, dw, dx
+            else:
+                ev[k][0].record()
+                z = conv.forward(x, y, w, rows_d, cols_d)
+                ev[k][1].record()
+                dx, dy, dw = conv.backward_helper(x, y, w, dz, rows_d, cols_d)
+                ev[k][2].record()
+                ev[k][3].record()
+                del z, dx, dy, dw
+        barrier()
+        elapsed = time.perf_counter() - t0
+        clocks = sampler.stop()
+        inner.check_device_status()
+        launches_bwd = max(1, inner.internal.last_backward_launches())
+
+        fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
+        bwd_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
+        t = torch.tensor([elapsed, fwd_ms, bwd_ms], device=device, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed, fwd_ms_max, bwd_ms_max = t.tolist()
+        res = {"graph": graph, "conv": conv, "plan": plan, "inner": inner, "elapsed": elapsed, "steps": steps,
+               "fwd_ms": fwd_ms, "bwd_ms": bwd_ms, "fwd_ms_max": fwd_ms_max, "bwd_ms_max": bwd_ms_max,
+               "clocks": clocks, "local_edges": local_edges, "owned": owned, "launches_bwd": launches_bwd,
+               "halo_fraction": (plan.halo.size / max(1, plan.owned)) if plan is not None else 0.0}
+
+        if with_parity and det:
+            outputs = step()
+            torch.cuda.synchronize()
+            if rank == 0:
+                res["parity"] = parity_check(torch, args, spec, problem, graph, conv, plan, y, w, outputs, device)
+            del outputs
+            barrier()
+        if with_e2e:
+            res["e2e"] = run_e2e(args, torch, dist, world, device, conv, det, x, y, w, dz, edges, local_edges,
+                                 (rows_d, cols_d) if not det else None, graph=graph)
+        del x, y, w, dz
+        return res
+
+    main = measure(args.numbering, args.steps, not args.no_parity, not args.no_e2e)
+    graph, plan, inner = main["graph"], main["plan"], main["inner"]
+    nodes, edges = graph.node_count, graph.nnz
+    ms_per_step = main["elapsed"] / args.steps * 1e3
+    value = edges / (main["elapsed"] / args.steps)
+    fwd_ms, bwd_ms = main["fwd_ms"], main["bwd_ms"]
+
+    # -- roofline of the dominant pass (backward), rank 0's launches
+    fb, bb = algorithmic_bytes(problem, main["owned"] if world > 1 else nodes, main["local_edges"],
+                               x_rows=plan.local_nodes if (plan is not None and world > 1) else None)
     peak, peak_kind = measured_peak()
-    per_edge = NCU_BWD_DRAM_BYTES_PER_EDGE.get((args.workload, args.numbering))
-    traffic = per_edge * local_edges if (per_edge is not None and world == 1 and det) else None
-    roofline = {"bound": "hbm", "kernel": "oeq_uvu_kernel (conv backward)", "achieved": bb / (bwd_ms * 1e-3) / 1e9,
-                "peak": peak, "peak_source": peak_kind, "unit": "GB/s", "frac": bb / (bwd_ms * 1e-3) / 1e9 / peak,
-                "traffic": traffic, "algorithmic_bytes": bb, "ms": bwd_ms,
+    traffic, traffic_from = None, None
+    if (args.workload, args.numbering) in NCU_BWD_DRAM and world == 1 and det:
+        per_edge, traffic_from = NCU_BWD_DRAM[(args.workload, args.numbering)]
+        traffic = per_edge * main["local_edges"]
+    info_b, info_f = inner.internal.launch_info(1), inner.internal.launch_info(0)
+    launches_bwd = main["launches_bwd"]
+    roofline = {"bound": "hbm", "kernel": "conv backward pass (oeq_uvu_kernel receiver order + oeq_sum_sender_rows per edge block)"
+                if launches_bwd > 1 else "oeq_uvu_kernel (conv backward)",
+                "achieved": bb / (bwd_ms * 1e-3) / 1e9, "peak": peak, "peak_source": peak_kind, "unit": "GB/s",
+                "frac": bb / (bwd_ms * 1e-3) / 1e9 / peak, "traffic": traffic, "traffic_from": traffic_from,
+                "algorithmic_bytes": bb, "ms": bwd_ms, "launches": launches_bwd,
                 "forward": {"achieved": fb / (fwd_ms * 1e-3) / 1e9, "frac": fb / (fwd_ms * 1e-3) / 1e9 / peak,
                             "algorithmic_bytes": fb, "ms": fwd_ms},
                 "fwd_bwd_frac": (fb + bb) / ((fwd_ms + bwd_ms) * 1e-3) / 1e9 / peak}
 
-    # -- end to end through the public API with host buffers
-    e2e = None
-    if not args.no_e2e:
-        e2e = run_e2e(args, torch, dist, world, device, conv, det, x, y, w, dz, edges, local_edges,
-                      (rows_d, cols_d) if not det else None, graph=graph)
-
-    base = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        base = cpu_baseline(problem, spec, graph, 2, 1, args.seed)
-
+    line = None
     if rank == 0:
-        info = inner.internal.launch_info(1)
         line = {
             "metric": "conv_fwd_bwd_edges_per_s", "value": value, "unit": "edges/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_per_step,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic", "config": workload_config(args, spec, graph),
-            "kernel_ms": {"forward": fwd_ms_max, "backward": bwd_ms_max},
-            "roofline": roofline, "e2e": e2e, "gpu_launches": 2 * args.steps, "clocks": clocks,
-            "launch": {"backward": info, "forward": inner.internal.launch_info(0)},
+            "kernel_ms": {"forward": main["fwd_ms_max"], "backward": main["bwd_ms_max"]},
+            "roofline": roofline, "e2e": main.get("e2e"),
+            "gpu_launches": (1 + launches_bwd) * args.steps, "clocks": main["clocks"],
+            "launch": {"backward": info_b, "forward": info_f},
+            "halo_fraction": main["halo_fraction"],
         }
-        if base is not None:
-            line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        if "parity" in main:
+            line["parity"] = main["parity"]
+
+    # release the main workload before anything else is allocated
+    conv_main = main.pop("conv")
+    del conv_main, main, inner
+    torch.cuda.empty_cache()
+
+    if not args.no_secondary and det and args.workload == "mace_large":
+        other = "random" if args.numbering == "morton" else "morton"
+        rnd = measure(other, max(2, min(args.steps, 5)), False, False)
+        if rank == 0:
+            g2 = rnd["graph"]
+            line["random_numbering" if other == "random" else "morton_numbering"] = {
+                "value": g2.nnz / (rnd["elapsed"] / rnd["steps"]), "unit": "edges/s", "steps": rnd["steps"],
+                "ms_per_step": rnd["elapsed"] / rnd["steps"] * 1e3,
+                "kernel_ms": {"forward": rnd["fwd_ms_max"], "backward": rnd["bwd_ms_max"]},
+                "halo_fraction": rnd["halo_fraction"], "numbering": other,
+                "note": "halo_fraction = halo rows / owned rows of rank 0"}
+        rnd.pop("conv")
+        del rnd
+        torch.cuda.empty_cache()
+        if rank == 0 and world == 1:
+            peaks = matmul_peaks(torch)
+            line["peaks"] = peaks
+            line["secondary"] = secondary_block(torch, args, device, peaks)
+
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        base = cpu_baseline(problem, spec, graph, 2, 1, args.seed)
+        line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 
@@ -372,7 +658,8 @@ def run_e2e(args, torch, dist, world, device, conv, det, x, y, w, dz, edges, loc
     """Forward + backward with every input copied from pinned host memory and every output copied
     back, inside the timed region.  Host memory stays bounded: the per-edge weight array and its
     gradient move through one pinned tile that is re-used for every slice of the device array (the
-    bytes that cross PCIe are the full arrays).
+    bytes that cross PCIe are the full arrays; a real caller's 70 GB host array would add its own
+    page-touch cost).
 
     Deterministic variant, any number of GPUs: the public host-tensor entry point
     (``ShardedTensorProductConv.forward_backward_host``), which exchanges the halo once and pipelines
@@ -398,7 +685,7 @@ def run_e2e(args, torch, dist, world, device, conv, det, x, y, w, dz, edges, loc
             dist.all_reduce(dt, op=dist.ReduceOp.MAX)
         return {"value": edges / dt.item(), "unit": "edges/s", "h2d_bytes_per_step": int(h2d),
                 "d2h_bytes_per_step": int(d2h), "ms_per_step": dt.item() * 1e3, "steps": args.e2e_steps,
-                "note": note}
+                "warmup": 1, "note": note}
 
     if det:
         # host-tensor entry point of the sharded convolution: X of the rank's nodes goes in, the halo is
@@ -425,7 +712,8 @@ def run_e2e(args, torch, dist, world, device, conv, det, x, y, w, dz, edges, loc
             h2d, d2h = tot[0].item(), tot[1].item()
         return timed(one, h2d, d2h,
                      f"{len(streamed.slabs)} edge slabs per rank pipelined (copy in / kernels / copy out overlap); "
-                     "per-edge arrays cross PCIe through one re-used pinned tile per array; bytes summed over ranks")
+                     "per-edge arrays cross PCIe through one re-used pinned tile per array (not a full-size host "
+                     "array); bytes summed over ranks")
 
     tile = min(local_edges, 1 << 19)
     x_h, y_h, dz_h = pin(x), pin(y), pin(dz)

@@ -139,6 +139,13 @@ int oeq_tp_check(oeq_tp* h);
  * rows/cols/perm are int64. */
 int oeq_conv_create(const oeq_problem_desc* desc, int deterministic, oeq_conv** out);
 int oeq_conv_destroy(oeq_conv* h);
+/* Preferred scratch for oeq_conv_backward (the forward pass needs none).  Deterministic variant: one dX
+ * row per edge, capped at 8 GiB (environment OEQ_B200_BWD_SCRATCH_MB); the backward pass then walks the
+ * edges in receiver order, keeps the receiver's dZ slice on chip, writes each edge's dX row to the scratch
+ * and sums the rows per sender in sender_perm order (in blocks of edges when the scratch is smaller than
+ * the edge list).  The scratch is optional: with a null or small workspace the pass runs the sender-order
+ * kernel, which needs none and gives the same results up to summation order.  Atomic variant: 0.
+ * (The reference sizes a workspace for its fix-up pass here: LoopUnrollConv.py:61-72.) */
 size_t oeq_conv_workspace_bytes(const oeq_conv* h, int64_t nodes, int64_t edges);
 
 /* Replaces JITConvImpl::exec_conv (convolution.hpp:121-147).  Every row of Z is written. */
@@ -152,6 +159,11 @@ int oeq_conv_backward(oeq_conv* h, int64_t nodes, int64_t edges, const void* X, 
                       void* dX, void* dY, void* dW, void* workspace, size_t workspace_bytes, void* stream);
 
 int oeq_conv_check(oeq_conv* h);
+
+/* Number of kernels the most recent oeq_conv_backward on this handle launched (1 for the sender-order
+ * kernel; one receiver-order launch plus one row-sum launch per block of edges otherwise).  Benchmarks
+ * report it; it has no counterpart in the reference. */
+int oeq_conv_last_backward_launches(const oeq_conv* h);
 
 /* Launch geometry of the most recent specialisation, for benchmarks and tests:
  * which = 0 forward, 1 backward.  Any output pointer may be NULL. */

@@ -70,6 +70,7 @@ SYMBOLS = {
     "oeq_conv_forward": (_INT, [_P, _I64, _I64, _P, _P, _P, _P, _P, _P, _P, _SZ, _P]),
     "oeq_conv_backward": (_INT, [_P, _I64, _I64, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _SZ, _P]),
     "oeq_conv_check": (_INT, [_P]),
+    "oeq_conv_last_backward_launches": (_INT, [_P]),
     "oeq_tp_launch_info": (_INT, [_P, _INT, _PI, _PI, _PI, _PI, _PI, _PI]),
     "oeq_conv_launch_info": (_INT, [_P, _INT, _PI, _PI, _PI, _PI, _PI, _PI]),
 }
@@ -219,6 +220,9 @@ class ConvHandle(_Handle):
 
     def check(self):
         check(lib().oeq_conv_check(self.ptr))
+
+    def last_backward_launches(self):
+        return int(lib().oeq_conv_last_backward_launches(self.ptr))
 
     def launch_info(self, which):
         return self._info(lib().oeq_conv_launch_info, which)

@@ -27,16 +27,10 @@ CONFIGS = {
 }
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--config", default="uvw_fc", choices=sorted(CONFIGS))
-    ap.add_argument("--dtype", default="f32", choices=["f32", "f64"])
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--batch", type=int, default=None)
-    ap.add_argument("--forward-only", action="store_true")
-    args = ap.parse_args()
-
+def measure(config="uvw_fc", dtype="f32", steps=20, warmup=5, batch=None, forward_only=False):
+    """Time one configuration on the current device; returns the result record (a dict)."""
+    args = argparse.Namespace(config=config, dtype=dtype, steps=steps, warmup=warmup, batch=batch,
+                              forward_only=forward_only)
     cfg = CONFIGS[args.config]
     np_dt, dt = (np.float32, torch.float32) if args.dtype == "f32" else (np.float64, torch.float64)
     if cfg["kind"] == "channelwise":
@@ -85,8 +79,23 @@ def main():
             "forward_GBps": fwd_bytes / (fwd * 1e-3) / 1e9,
             "backward_GBps": None if bwd is None else bwd_bytes / (bwd * 1e-3) / 1e9,
             "forward_contraction_TFLOPs": flops / (fwd * 1e-3) / 1e12 if flops else None,
+            "fwd_bwd_contraction_TFLOPs": None if (bwd is None or not flops) else 3 * flops / ((fwd + bwd) * 1e-3) / 1e12,
+            "algorithmic_bytes": {"forward": fwd_bytes, "backward": bwd_bytes},
             "launch": {"forward": tp.internal.launch_info(0), "backward": tp.internal.launch_info(1)}}
-    print(json.dumps(line), flush=True)
+    return line
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--config", default="uvw_fc", choices=sorted(CONFIGS))
+    ap.add_argument("--dtype", default="f32", choices=["f32", "f64"])
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--batch", type=int, default=None)
+    ap.add_argument("--forward-only", action="store_true")
+    args = ap.parse_args()
+    print(json.dumps(measure(args.config, args.dtype, args.steps, args.warmup, args.batch, args.forward_only)),
+          flush=True)
 
 
 if __name__ == "__main__":

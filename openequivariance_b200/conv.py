@@ -69,9 +69,12 @@ class TensorProductConv(TensorProductBase):
         self.deterministic = deterministic
         self.conv_id = next(_conv_ids)
         self.internal = _native.ConvHandle(config, deterministic)
-        # the node-aligned segmented reduction needs no scratch memory
+        # The forward pass needs no scratch (node-aligned segmented reduction).  The deterministic backward
+        # pass takes optional scratch (one dX row per edge, capped); it is allocated on first use, per
+        # device, and kept (the reference keeps its workspace on the object too: ConvolutionBase.py:93-99).
         self.workspace_size = 0
         self.workspace_ptr = 0
+        self._scratch = {}
         self.setup_torch_module()
 
     @staticmethod
@@ -115,6 +118,29 @@ class TensorProductConv(TensorProductBase):
                                   torch.cuda.current_stream().cuda_stream)
         return z
 
+    def _backward_scratch(self, device, nodes, edges):
+        """(pointer, bytes) of the backward scratch for this call, growing the cached buffer if needed.
+        When the device cannot spare the preferred size a quarter of it is tried, then none (the library
+        then runs its scratch-free kernel)."""
+        want = self.internal.workspace_bytes(nodes, edges) if self.deterministic else 0
+        if want == 0:
+            return 0, 0
+        buf = self._scratch.get(device)
+        if buf is None or buf.numel() < want:
+            self._scratch.pop(device, None)
+            buf = None
+            for size in (want, want // 4):
+                try:
+                    buf = torch.empty(size, dtype=torch.uint8, device=device)
+                    break
+                except torch.OutOfMemoryError:
+                    continue
+            if buf is None:
+                return 0, 0
+            self._scratch[device] = buf
+        self.workspace_size, self.workspace_ptr = buf.numel(), buf.data_ptr()
+        return buf.data_ptr(), buf.numel()
+
     def _backward_impl(self, x, y, w, dz, rows, cols, perm=None):
         self._check(x, y, w, rows, cols, perm)
         if self.deterministic and perm is None:
@@ -124,9 +150,10 @@ class TensorProductConv(TensorProductBase):
         perm_ptr = perm.contiguous().data_ptr() if (perm is not None and self.deterministic) else 0
         dx, dy, dw = torch.empty_like(x), torch.empty_like(y), torch.empty_like(w)
         with torch.cuda.device(x.device):
+            ws_ptr, ws_bytes = self._backward_scratch(x.device, x.shape[0], rows.shape[0])
             self.internal.backward(x.shape[0], rows.shape[0], x.data_ptr(), y.data_ptr(), w.data_ptr(),
                                    dz.data_ptr(), rows.data_ptr(), cols.data_ptr(), perm_ptr,
-                                   dx.data_ptr(), dy.data_ptr(), dw.data_ptr(), 0, 0,
+                                   dx.data_ptr(), dy.data_ptr(), dw.data_ptr(), ws_ptr, ws_bytes,
                                    torch.cuda.current_stream().cuda_stream)
         return dx, dy, dw
 

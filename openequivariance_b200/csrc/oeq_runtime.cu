@@ -212,7 +212,9 @@ struct Mapping {
     std::vector<int> part_of_out, part_of_instr, zr_off, xr_off;
     int zpc_max = 1, xpc = 1;
     int stage_bytes = 0, extra_bytes = 0, sw_bytes = 0;
-    int threads() const { return ng * mulg * ps + 32 * ng * producer; }
+    int helper_warps = 0;                     // receiver-order backward: warps that sum the previous block's rows
+    int gz_regs = 1 << 20, gz_smem_values = 0; // receiver-order backward: dZ values in registers / parked in shared memory
+    int threads() const { return ng * mulg * ps + 32 * ng * producer + 32 * helper_warps; }
     int fixed_bytes(int stages) const { return ng * stages * 48 + ng * 128 + sw_bytes; }
     int smem(int stages) const { return fixed_bytes(stages) + ng * (stages * stage_bytes + extra_bytes); }
     int max_stages() const {
@@ -401,6 +403,79 @@ int choose_mapping(const Problem& p, int kind, Mapping& m) {
     if (env_int("OEQ_B200_VERBOSE", 0))
         fprintf(stderr, "[oeq_b200] kind %d: mulg %d nch %d ps %d ng %d threads %d stage %d B extra %d B max stages %d\n",
                 kind, m.mulg, m.nch, m.ps, m.ng, m.threads(), m.stage_bytes, m.extra_bytes, m.max_stages());
+    return OEQ_OK;
+}
+
+// Receiver-order backward pass of the convolution (uvu_kernels.cuh, run_backward_recv): one thread per
+// channel, stages as in the forward pass, two dX rows and the dY partials per group as extras.
+constexpr int K_BWD_RECV_DET = 6, K_BWD_RECV_ATOMIC = 7;
+
+bool recv_backward_supported(const Problem& p) {
+    if (p.mode != OEQ_MODE_UVU || p.shared || p.y_dim > 32) return false;
+    for (const Irrep& r : p.in2)
+        if (r.mul != 1) return false;
+    int maxmul = 1, zpc = 0, xpc = 0;
+    for (const Instr& t : p.instr) maxmul = std::max(maxmul, p.in1[t.i1].mul);
+    for (const Irrep& r : p.out) { maxmul = std::max(maxmul, r.mul); zpc += r.dim; }
+    for (const Irrep& r : p.in1) xpc += r.dim;
+    if (maxmul > 256) return false;                             // one thread per channel
+    int d1max = 1;
+    for (const Irrep& r : p.in1) d1max = std::max(d1max, r.dim);
+    // the channel's slice of dZ lives in registers (32-bit registers: twice as many for FP64 values)
+    if ((zpc + 2 * p.y_dim + 4 * d1max) * (p.elem() / 4) + 40 > 200) return false;
+    return env_int("OEQ_B200_BWD_RECV", 1) != 0;
+}
+
+int choose_mapping_recv(const Problem& p, Mapping& m) {
+    int maxmul = 1;
+    for (const Instr& t : p.instr) maxmul = std::max(maxmul, p.in1[t.i1].mul);
+    for (const Irrep& r : p.out) maxmul = std::max(maxmul, r.mul);
+    m.mulg = (maxmul + 31) / 32 * 32;
+    m.nch = 1;
+    m.ps = 1;
+    const int e = p.elem();
+    const int xb = pad16(p.x_dim * e), yb = pad16(p.y_dim * e), wb = pad16(p.w_numel * e);
+    m.sw_bytes = 0;
+    m.stage_bytes = xb + yb + wb;
+    // dZ values per channel beyond the register budget are parked in shared memory (whole output irreps)
+    int zpc = 0;
+    for (const Irrep& r : p.out) zpc += r.dim;
+    const int budget = env_int("OEQ_B200_GZ_REGS", p.dtype == OEQ_F64 ? 28 : 56);
+    m.gz_regs = budget;
+    m.gz_smem_values = 0;
+    {
+        int off = 0;
+        for (const Irrep& r : p.out) {
+            if (off >= budget) m.gz_smem_values += r.dim;
+            off += r.dim;
+        }
+    }
+    m.extra_bytes = 2 * xb + 5 * (m.mulg / 32) * yb + pad16(m.gz_smem_values * m.mulg * e);
+    m.nph = 1;
+    m.z_ph_begin = {0, p.z_dim};
+    m.w_ph_begin = {0, p.w_numel};
+    m.phase_of_instr.assign(p.instr.size(), 0);
+    // two wide groups share a CTA (one CTA per SM): 320 threads leave 200 registers per thread, which the
+    // channel's dZ slice needs; two CTAs of 160 threads would be capped at 168
+    const int want = std::max(1, std::min(8, 256 / m.mulg));
+    m.ng = 0;
+    for (int cand = want; cand >= 1 && !m.ng; --cand) {
+        m.ng = cand;
+        if (m.smem(cand > 1 ? 2 : 3) > SMEM_LIMIT && !(cand == 1 && m.smem(2) <= SMEM_LIMIT)) m.ng = 0;
+    }
+    if (!m.ng) return fail(OEQ_ERR_UNSUPPORTED, "problem rows do not fit in shared memory");
+    m.ng = env_int("OEQ_B200_NG_RECV", m.ng);
+    m.producer = env_int("OEQ_B200_PRODUCER", (m.ng <= 4 && m.mulg >= 128) ? 1 : 0);
+    if (m.ng > 4) m.producer = 0;
+    const int stages = std::min(m.max_stages(), env_int("OEQ_B200_STAGES", 4));
+    const int by_smem = stages >= 2 ? SMEM_LIMIT / (m.smem(stages) + 1024) : 1;
+    const int by_threads = 2048 / m.threads();
+    m.min_ctas = env_int("OEQ_B200_MIN_CTAS_RECV", std::max(1, std::min({by_smem, by_threads, 2})));
+    if (m.smem(2) > SMEM_LIMIT || m.ng < 1 || m.ng > 8) return fail(OEQ_ERR_INVALID, "OEQ_B200_NG_RECV override does not fit");
+    assign_partitions(p, true, m);
+    if (env_int("OEQ_B200_VERBOSE", 0))
+        fprintf(stderr, "[oeq_b200] receiver-order backward: mulg %d ng %d threads %d stage %d B extra %d B max stages %d min ctas %d\n",
+                m.mulg, m.ng, m.threads(), m.stage_bytes, m.extra_bytes, m.max_stages(), m.min_ctas);
     return OEQ_OK;
 }
 
@@ -626,6 +701,7 @@ std::string descriptor_text(const Problem& p, const Mapping& m, const UvwConfig*
         s << "};\n";
     }
     s << "constexpr int ZPC_MAX = " << m.zpc_max << ", XPC = " << m.xpc << ";\n";
+    s << "constexpr int GZ_REGS = " << m.gz_regs << ", GZ_SMEM_VALUES = " << m.gz_smem_values << ";\n";
     // cycle accounting inside the kernels is a development aid: it exists only in a library built with
     // -DOEQ_DEV_PROFILE (the shipped entry points then contain no allocation, synchronisation or printing)
 #ifdef OEQ_DEV_PROFILE
@@ -717,6 +793,8 @@ int compile_kernel(const std::string& descriptor, const std::string& main_header
     std::vector<const char*> opts = {"-arch=sm_100a", "-std=c++17", "-lineinfo", "-default-device", "-diag-suppress=177", inc.c_str()};
     std::string ptxas_v = "--ptxas-options=-v";
     if (env_int("OEQ_B200_VERBOSE", 0)) opts.push_back(ptxas_v.c_str());
+    std::string maxreg = "--maxrregcount=" + std::to_string(env_int("OEQ_B200_MAXRREG", 0));
+    if (env_int("OEQ_B200_MAXRREG", 0) > 0) opts.push_back(maxreg.c_str());
     nvrtcResult res = g_nvrtc.compile(prog, (int)opts.size(), opts.data());
     size_t log_size = 0;
     g_nvrtc.log_size(prog, &log_size);
@@ -767,6 +845,21 @@ int build_uvu(const Problem& p, int kind, Kernel& k) {
     int rc = choose_mapping(p, kind, k.map);
     if (rc) return rc;
     rc = compile_kernel(descriptor_text(p, k.map), "uvu_kernels.cuh", kind, k.code);
+    if (rc) return rc;
+    k.compiled = true;
+    return OEQ_OK;
+}
+
+int build_uvu_recv(const Problem& p, bool deterministic, Kernel& k) {
+    int rc = choose_mapping_recv(p, k.map);
+    if (rc) return rc;
+    // Deterministic variant: two helper warps per CTA sum the previous block's dX rows while the consumers
+    // work.  With two wide groups and their staging warps that makes twelve warps, three per scheduler, the
+    // same register ceiling (168) as the ten warps without helpers.
+    k.map.helper_warps = deterministic ? std::max(0, env_int("OEQ_B200_HELPER_WARPS", 2)) : 0;
+    if (k.map.threads() > 1024) k.map.helper_warps = 0;
+    const std::string macros = "#define OEQ_HELPER_WARPS " + std::to_string(k.map.helper_warps) + "\n";
+    rc = compile_kernel(descriptor_text(p, k.map) + macros, "uvu_kernels.cuh", deterministic ? K_BWD_RECV_DET : K_BWD_RECV_ATOMIC, k.code);
     if (rc) return rc;
     k.compiled = true;
     return OEQ_OK;
@@ -1006,6 +1099,10 @@ struct UvuParams {
     void* ws;
     int* status;
     int stages, flags, chunk;
+    long long e_lo, e_hi;
+    const long long* sum_cols; const long long* sum_perm; const void* sum_ws;
+    long long sum_items, sum_e_lo, sum_e_hi;
+    int sum_first, sum_chunk;
 };
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -1065,6 +1162,10 @@ struct oeq_conv {
     Kernel fwd, bwd;
     Kernel fwd_tc;              // tensor-core forward pass, when the problem qualifies
     bool has_fwd_tc = false;
+    Kernel bwd_recv;            // receiver-order backward pass (needs scratch in the deterministic variant)
+    bool has_bwd_recv = false;
+    cudaKernel_t sum_rows_fn = nullptr;
+    int last_bwd_launches = 0;  // kernel launches of the most recent oeq_conv_backward
     int* d_status = nullptr;
     cudaStream_t last_stream = nullptr;
 };
@@ -1123,15 +1224,18 @@ int oeq_precompile(const oeq_problem_desc* desc, int kinds) {
     }
     UvuTcGeometry geo;
     const bool tc = (kinds & 6) && uvu_tc_geometry(p, geo);
+    const bool recv = (kinds & 6) && recv_backward_supported(p);
     if (kinds & 2) {
         if ((rc = one(K_FWD_DET)) || (rc = one(K_BWD_DET))) return rc;
-        Kernel k;
+        Kernel k, kr;
         if (tc && (rc = build_uvu_tc(p, true, k))) return rc;
+        if (recv && (rc = build_uvu_recv(p, true, kr))) return rc;
     }
     if (kinds & 4) {
         if ((rc = one(K_FWD_ATOMIC)) || (rc = one(K_BWD_ATOMIC))) return rc;
-        Kernel k;
+        Kernel k, kr;
         if (tc && (rc = build_uvu_tc(p, false, k))) return rc;
+        if (recv && (rc = build_uvu_recv(p, false, kr))) return rc;
     }
     return OEQ_OK;
 }
@@ -1525,6 +1629,10 @@ int oeq_conv_create(const oeq_problem_desc* desc, int deterministic, oeq_conv** 
         rc = build_uvu_tc(h->prob, h->deterministic, h->fwd_tc);
         h->has_fwd_tc = !rc;
     }
+    if (!rc && recv_backward_supported(h->prob)) {
+        rc = build_uvu_recv(h->prob, h->deterministic, h->bwd_recv);
+        h->has_bwd_recv = !rc;
+    }
     if (rc) {
         delete h;
         return rc;
@@ -1539,13 +1647,24 @@ int oeq_conv_destroy(oeq_conv* h) {
     if (h->fwd.lib) cudaLibraryUnload(h->fwd.lib);
     if (h->bwd.lib) cudaLibraryUnload(h->bwd.lib);
     if (h->fwd_tc.lib) cudaLibraryUnload(h->fwd_tc.lib);
+    if (h->bwd_recv.lib) cudaLibraryUnload(h->bwd_recv.lib);
     delete h;
     return OEQ_OK;
 }
 
+// Scratch row of one edge in the deterministic receiver-order backward pass.
+static size_t recv_row_bytes(const Problem& p) { return (size_t)pad16(p.x_dim * p.elem()); }
+// Below this many scratch rows (when the edges do not all fit) the sender-order kernel is used instead.
+static long long recv_min_block_edges() { return std::max(1, env_int("OEQ_B200_BWD_MIN_BLOCK", 1 << 16)); }
+
 size_t oeq_conv_workspace_bytes(const oeq_conv* h, int64_t nodes, int64_t edges) {
-    (void)h; (void)nodes; (void)edges;
-    return 0;  // the segmented reduction is node-aligned: no scratch, no fix-up pass
+    (void)nodes;
+    // Forward: none (the segmented reduction is node-aligned: no scratch, no fix-up pass).  Deterministic
+    // backward: one dX row per edge, capped (the pass then runs over blocks of edges); optional -- without
+    // it the sender-order kernel runs.
+    if (!h || !h->deterministic || !h->has_bwd_recv || edges <= 0) return 0;
+    const size_t cap = (size_t)std::max(1, env_int("OEQ_B200_BWD_SCRATCH_MB", 8192)) << 20;
+    return std::min((size_t)edges * recv_row_bytes(h->prob), cap);
 }
 
 int oeq_conv_forward(oeq_conv* h, int64_t nodes, int64_t edges, const void* X, const void* Y, const void* W,
@@ -1598,7 +1717,6 @@ int oeq_conv_forward(oeq_conv* h, int64_t nodes, int64_t edges, const void* X, c
 int oeq_conv_backward(oeq_conv* h, int64_t nodes, int64_t edges, const void* X, const void* Y, const void* W,
                       const void* dZ, const int64_t* rows, const int64_t* cols, const int64_t* perm, void* dX,
                       void* dY, void* dW, void* workspace, size_t workspace_bytes, void* stream) {
-    (void)workspace; (void)workspace_bytes;
     if (!h) return fail(OEQ_ERR_INVALID, "null handle");
     if (nodes < 0 || edges < 0) return fail(OEQ_ERR_INVALID, "negative size");
     cudaStream_t st = (cudaStream_t)stream;
@@ -1612,13 +1730,111 @@ int oeq_conv_backward(oeq_conv* h, int64_t nodes, int64_t edges, const void* X, 
     if (h->deterministic && !perm)
         return fail(OEQ_ERR_INVALID, "deterministic backward needs the sender-order permutation");
     int rc = ensure_status(&h->d_status);
-    if (!rc) rc = load_kernel(h->bwd, "oeq_uvu_kernel", false);
     if (rc) return rc;
+    h->last_stream = st;
+    const int e = p.elem();
+    // receiver-order pass: atomic variant always (dX was cleared above); deterministic variant when the
+    // caller's scratch holds the rows of a useful block of edges
+    const size_t row = recv_row_bytes(p);
+    long long block_edges = 0;
+    if (h->has_bwd_recv) {
+        if (!h->deterministic) block_edges = edges;
+        else if (workspace && aligned16(workspace)) {
+            block_edges = (long long)std::min<size_t>(workspace_bytes / row, (size_t)edges);
+            if (block_edges < edges && block_edges < recv_min_block_edges()) block_edges = 0;
+        }
+    }
+    if (block_edges > 0) {
+        Kernel& k = h->bwd_recv;
+        if (!k.loaded) {
+            if ((rc = load_kernel(k, "oeq_uvu_kernel", false))) return rc;
+            if (h->deterministic) OEQ_CUDA(cudaLibraryGetKernel(&h->sum_rows_fn, k.lib, "oeq_sum_sender_rows"));
+        }
+        const char* Yb = (const char*)Y; const char* Wb = (const char*)W;
+        char* dYb = (char*)dY; char* dWb = (char*)dW;
+        h->last_bwd_launches = 0;
+        const int dx_bulk = ((p.x_dim * e) % 16 == 0 && aligned16(dX)) ? 32 : 0;
+        const int sum_chunk = std::max(1, env_int("OEQ_B200_SUM_CHUNK", 64));
+        auto pass1 = [&](long long e0, long long n, void* scratch, UvuParams& prm) {
+            prm.X = X; prm.dZ = dZ; prm.dX = dX;
+            prm.Y = Yb + (size_t)e0 * p.y_dim * e; prm.W = Wb + (size_t)e0 * p.w_numel * e;
+            prm.dY = dYb + (size_t)e0 * p.y_dim * e; prm.dW = dWb + (size_t)e0 * p.w_numel * e;
+            prm.rows = (const long long*)rows + e0; prm.cols = (const long long*)cols + e0;
+            prm.n_items = n; prm.n_nodes = nodes; prm.status = h->d_status;
+            prm.ws = scratch;
+        };
+        if (!h->deterministic) {
+            UvuParams prm{};
+            pass1(0, edges, nullptr, prm);
+            if ((rc = launch_uvu(k, p, prm, st, dx_bulk))) return rc;
+            h->last_bwd_launches = 1;
+            return OEQ_OK;
+        }
+        // rows of nodes that send nothing are never written by the row sum
+        OEQ_CUDA(cudaMemsetAsync(dX, 0, (size_t)nodes * p.x_dim * e, st));
+        auto sum_launch = [&](long long e0, long long n, void* scratch, bool first) -> int {
+            UvuParams sp{};
+            sp.dX = dX; sp.ws = scratch;
+            sp.rows = (const long long*)rows; sp.cols = (const long long*)cols; sp.perm = (const long long*)perm;
+            sp.n_items = edges; sp.n_nodes = nodes; sp.status = h->d_status;
+            sp.flags = first ? 64 : 0;
+            sp.chunk = sum_chunk;
+            sp.e_lo = e0; sp.e_hi = e0 + n;
+            const long long chunks = (edges + sp.chunk - 1) / sp.chunk;
+            const long long grid = std::max<long long>(1, std::min<long long>((long long)k.sm_count * 6, (chunks + 7) / 8));
+            void* args[] = {&sp};
+            OEQ_CUDA(cudaLaunchKernel((const void*)h->sum_rows_fn, dim3((unsigned)grid), dim3(256), args, 0, st));
+            ++h->last_bwd_launches;
+            return OEQ_OK;
+        };
+        // With helper warps the scratch is used as two halves: launch b writes the rows of block b into half
+        // b % 2 while its helper warps sum block b - 1 from the other half; the last block is summed by a
+        // launch of its own.  Blocks are kept above a minimum size, and a list that fits one half is still cut
+        // into a few blocks so that most of the summing hides behind the receiver-order launches.
+        const bool pipelined = k.map.helper_warps > 0 && edges >= 4 * recv_min_block_edges();
+        if (pipelined) {
+            const long long half = (long long)(workspace_bytes / row / 2);
+            long long be = std::min<long long>(half, (edges + 3) / 4);
+            be = std::max<long long>(be, std::min<long long>(half, recv_min_block_edges()));
+            if (be >= 1) {
+                char* halves[2] = {(char*)workspace, (char*)workspace + (size_t)half * row};
+                long long prev_e0 = -1, prev_n = 0;
+                int b = 0;
+                for (long long e0 = 0; e0 < edges; e0 += be, ++b) {
+                    const long long n = std::min(be, edges - e0);
+                    UvuParams prm{};
+                    pass1(e0, n, halves[b & 1], prm);
+                    if (prev_e0 >= 0) {
+                        prm.sum_cols = (const long long*)cols; prm.sum_perm = (const long long*)perm;
+                        prm.sum_ws = halves[(b - 1) & 1];
+                        prm.sum_items = edges; prm.sum_e_lo = prev_e0; prm.sum_e_hi = prev_e0 + prev_n;
+                        prm.sum_first = b == 1; prm.sum_chunk = sum_chunk;
+                    }
+                    if ((rc = launch_uvu(k, p, prm, st, dx_bulk))) return rc;
+                    ++h->last_bwd_launches;
+                    prev_e0 = e0; prev_n = n;
+                }
+                return sum_launch(prev_e0, prev_n, halves[(b - 1) & 1], b == 1);
+            }
+        }
+        bool first = true;
+        for (long long e0 = 0; e0 < edges; e0 += block_edges) {
+            const long long n = std::min(block_edges, edges - e0);
+            UvuParams prm{};
+            pass1(e0, n, workspace, prm);
+            if ((rc = launch_uvu(k, p, prm, st, dx_bulk))) return rc;
+            ++h->last_bwd_launches;
+            if ((rc = sum_launch(e0, n, workspace, first))) return rc;
+            first = false;
+        }
+        return OEQ_OK;
+    }
+    if ((rc = load_kernel(h->bwd, "oeq_uvu_kernel", false))) return rc;
+    h->last_bwd_launches = 1;
     UvuParams prm{};
     prm.X = X; prm.Y = Y; prm.W = W; prm.dZ = dZ; prm.dX = dX; prm.dY = dY; prm.dW = dW;
     prm.rows = (const long long*)rows; prm.cols = (const long long*)cols; prm.perm = (const long long*)perm;
     prm.n_items = edges; prm.n_nodes = nodes; prm.status = h->d_status;
-    h->last_stream = st;
 #ifdef OEQ_DEV_PROFILE
     if (env_int("OEQ_B200_UVU_PROFILE", 0)) {
         // cycle accounting of CTA 0's first group (development aid): synchronous, prints to stderr
@@ -1639,11 +1855,14 @@ int oeq_conv_backward(oeq_conv* h, int64_t nodes, int64_t edges, const void* X, 
     return launch_uvu(h->bwd, p, prm, st);
 }
 
+int oeq_conv_last_backward_launches(const oeq_conv* h) { return h ? h->last_bwd_launches : 0; }
+
 int oeq_conv_check(oeq_conv* h) { return h ? check_status(h->d_status, h->last_stream) : fail(OEQ_ERR_INVALID, "null handle"); }
 
 int oeq_conv_launch_info(const oeq_conv* h, int which, int* threads, int* ng, int* ps, int* stages, int* smem, int* regs) {
     if (!h) return fail(OEQ_ERR_INVALID, "null handle");
-    return launch_info(which ? h->bwd : (h->has_fwd_tc && h->fwd_tc.loaded ? h->fwd_tc : h->fwd), threads, ng, ps, stages, smem, regs);
+    if (which) return launch_info(h->has_bwd_recv && h->bwd_recv.loaded ? h->bwd_recv : h->bwd, threads, ng, ps, stages, smem, regs);
+    return launch_info(h->has_fwd_tc && h->fwd_tc.loaded ? h->fwd_tc : h->fwd, threads, ng, ps, stages, smem, regs);
 }
 
 }  // extern "C"

@@ -57,6 +57,14 @@ struct UvuParams {
     int stages;             // shared-memory stages per group
     int flags;              // bit0 X bulk-able, bit1 Y, bit2 W, bit3 Z/dZ
     int chunk;              // edges per work chunk (convolution modes)
+    long long e_lo, e_hi;   // sender-row sum: the edge range [e_lo, e_hi) whose scratch rows ws holds
+    // row sum done by the helper warps of a receiver-order launch (sum_items == 0: none): the whole edge list
+    // in sender order, the scratch rows of the previous block and that block's edge range
+    const long long* sum_cols;
+    const long long* sum_perm;
+    const T* sum_ws;
+    long long sum_items, sum_e_lo, sum_e_hi;
+    int sum_first, sum_chunk;
 };
 
 constexpr int MODE_BATCH = 0;
@@ -68,7 +76,14 @@ constexpr int NCONSUMERS = NG * G;
 // PRODUCER = 1: one extra warp per group stages that group's items and the group's warps never meet at a
 // per-item barrier (stages are handed back through "empty" mbarriers).  PRODUCER = 0: the first warp of
 // each group stages that group's items itself (better when a CTA holds many small groups).
-constexpr int NTHREADS = NCONSUMERS + 32 * NG * PRODUCER;   // one staging warp per group
+// Helper warps (deterministic receiver-order backward only): extra warps of the CTA that sum the scratch
+// rows of the previous block of edges into dX while the consumers work on the current block.
+#ifndef OEQ_HELPER_WARPS
+#define OEQ_HELPER_WARPS 0
+#endif
+constexpr int HELPER_WARPS = OEQ_HELPER_WARPS;
+constexpr int NSTAGING = 32 * NG * PRODUCER;                       // one staging warp per group
+constexpr int NTHREADS = NCONSUMERS + NSTAGING + 32 * HELPER_WARPS;
 constexpr int WARPS_PER_GROUP = G / 32;
 constexpr int DY_RING = 5;   // per-item dY partials in flight; stages are capped at DY_RING - 1
 
@@ -233,15 +248,18 @@ constexpr int log2_int(int n) {
 
 // ---------------------------------------------------------------- shared memory map
 
-template <bool BWD, int MODE>
+// RECV: the receiver-order backward pass of the convolution.  It stages what the forward pass stages
+// (X of the sender, Y, W of the edge) and keeps two per-edge dX rows and the dY partials as extras.
+template <bool BWD, int MODE, bool RECV = false>
 struct Smem {
-    using L = StageLayout<BWD>;
+    using L = StageLayout<BWD && !RECV>;
     // per-group extras
     static constexpr int ZBUF = (!BWD && MODE == MODE_BATCH) ? 2 * ZB : 0;      // staged output rows
-    static constexpr int DXBUF = BWD ? PS * XB : 0;                             // dX partials per partition
+    static constexpr int DXBUF = BWD ? (RECV ? 2 * XB : PS * XB) : 0;           // dX partials per partition / two dX rows
     static constexpr int DYSLOT = BWD ? DY_RING * WARPS_PER_GROUP * YB : 0;     // per-warp dY partials, a ring over items
     static constexpr int DWACC = (BWD && SHARED_W) ? pad16(W_NUMEL * ELEM) : 0; // shared-weight gradient
-    static constexpr int EXTRA = ZBUF + DXBUF + DYSLOT + DWACC;
+    static constexpr int GZS = RECV ? pad16(GZ_SMEM_VALUES * G * ELEM) : 0;     // parked dZ values (receiver order)
+    static constexpr int EXTRA = ZBUF + DXBUF + DYSLOT + DWACC + GZS;
 
     unsigned char* base;
     int stages;
@@ -392,8 +410,8 @@ struct ItemWalker {
 };
 
 // Stage one item into ring slot `stage` (executed by the group's first warp).
-template <int MODE, bool BWD>
-__device__ __forceinline__ void issue_item(const UvuParams& p, const Smem<BWD, MODE>& sm, int g, int stage, int lane,
+template <int MODE, bool BWD, class SMT>
+__device__ __forceinline__ void issue_item(const UvuParams& p, const SMT& sm, int g, int stage, int lane,
                                            long long e, long long s, long long r, long long lo, long long hi,
                                            int ph = 0) {
     using L = StageLayout<BWD>;
@@ -450,8 +468,10 @@ __device__ __forceinline__ void issue_item(const UvuParams& p, const Smem<BWD, M
 }
 
 // Producer warp of group g: stages the group's items as stage slots are handed back.
-template <int MODE, bool BWD>
-__device__ void run_producer(const UvuParams& p, const Smem<BWD, MODE>& sm, int g, int lane) {
+// SENDER_IN_HEADER: header slot 2 carries the edge's sender instead of the chunk's first node (the
+// receiver-order backward pass needs both end points of an edge and no node bounds).
+template <int MODE, bool BWD, bool SENDER_IN_HEADER = false, class SMT>
+__device__ void run_producer(const UvuParams& p, const SMT& sm, int g, int lane) {
     const int S = sm.stages;
     ItemWalker<MODE, BWD> walker(p, (long long)gridDim.x * NG, (long long)blockIdx.x * NG + g, lane);
     constexpr int PHASES = BWD ? NPH : 1;
@@ -473,7 +493,7 @@ __device__ void run_producer(const UvuParams& p, const Smem<BWD, MODE>& sm, int 
             const long long t0 = prof ? clock64() : 0;
             if (it >= S) ok = mbar_wait(sm.empty(g, stage), (unsigned)(((it / S) - 1) & 1), p.status, ERR_WAIT_EMPTY);
             const long long t1 = prof ? clock64() : 0;
-            if (ok) issue_item<MODE, BWD>(p, sm, g, stage, lane, e, s, r, lo, hi, ph);
+            if (ok) issue_item<MODE, BWD>(p, sm, g, stage, lane, e, s, r, SENDER_IN_HEADER ? s : lo, hi, ph);
             if (prof) {
                 prof_wait += (unsigned long long)(t1 - t0);
                 prof_issue += (unsigned long long)(clock64() - t1);
@@ -492,8 +512,8 @@ __device__ void run_producer(const UvuParams& p, const Smem<BWD, MODE>& sm, int 
 }
 
 // Wait until item `it` of group g has landed.  0: landed, 1: the group has no such item, 2: gave up.
-template <int MODE, bool BWD>
-__device__ __forceinline__ int acquire_item(const UvuParams& p, const Smem<BWD, MODE>& sm, int g, long long it) {
+template <int MODE, bool BWD, class SMT>
+__device__ __forceinline__ int acquire_item(const UvuParams& p, const SMT& sm, int g, long long it) {
     const int S = sm.stages;
     const int stage = (int)(it % S);
     volatile long long* total = sm.total(g);
@@ -515,8 +535,8 @@ __device__ __forceinline__ int acquire_item(const UvuParams& p, const Smem<BWD, 
 }
 
 // Hand stage `stage` back to the producer warp (PRODUCER mode): one arrival per consumer warp.
-template <int MODE, bool BWD>
-__device__ __forceinline__ void release_stage(const Smem<BWD, MODE>& sm, int g, int stage, int lane) {
+template <int MODE, bool BWD, class SMT>
+__device__ __forceinline__ void release_stage(const SMT& sm, int g, int stage, int lane) {
     __syncwarp();
     if (lane == 0) mbar_arrive(sm.empty(g, stage));
 }
@@ -1132,6 +1152,327 @@ __device__ void run_backward(const UvuParams& p, const Smem<true, MODE>& sm, int
     }
 }
 
+// ---------------------------------------------------------------- backward, receiver order (convolution)
+//
+// The sender-order backward pass above stages the receiver's output-gradient row (Z_DIM values) once per
+// edge; for channel-wise products that row is several times larger than everything else an edge needs, and
+// moving it from L2 into shared memory per edge is what bounds that kernel.  This pass walks the edges in
+// the order of the forward pass instead (runs of equal receivers): a thread keeps its channel's slice of
+// dZ[receiver] in registers for the whole run, an edge stages only X[sender], Y and W, and dW and dY leave
+// per edge as before.  The gradient of the first input cannot be accumulated here (one sender's edges are
+// spread over many runs), so every edge emits its dX row:
+//   deterministic: to scratch row `edge` (p.ws), summed afterwards per sender in sender_perm order by
+//                  oeq_sum_sender_rows -- a fixed order, bit-reproducible;
+//   atomic:        added into dX[sender] by one bulk reduction (element-wise add performed at L2).
+// One thread per channel, all instructions (PS == 1, NCH == 1), second input in registers.
+
+constexpr int ZPC_ALL = []() { int n = 0; for (int o = 0; o < N_OUT; ++o) n += OUT_D[o]; return n > 0 ? n : 1; }();
+constexpr int out_reg_off(int o) { int n = 0; for (int q = 0; q < o; ++q) n += OUT_D[q]; return n; }
+// Output irreps whose first value has index >= GZ_REGS (descriptor) keep their dZ slice in shared memory
+// instead of registers: a run's slice may not fit the register budget of a CTA with staging warps.
+constexpr int GZ_FIRST_SMEM = []() {
+    for (int o = 0; o < N_OUT; ++o)
+        if (out_reg_off(o) >= GZ_REGS) return out_reg_off(o);
+    return ZPC_ALL;
+}();
+constexpr int GZ_IN_REGS = GZ_FIRST_SMEM;
+
+template <int MODE>
+__device__ void run_backward_recv(const UvuParams& p, const Smem<true, MODE, true>& sm, int g, int tg) {
+    using SM = Smem<true, MODE, true>;
+    using L = typename SM::L;
+    static_assert(PS == 1 && NCH == 1 && Y_IN_REGS && !SHARED_W, "receiver-order backward: one thread per channel");
+    const int S = sm.stages;
+    const int u = tg;
+    const int lane = tg & 31;
+    const int warp = tg >> 5;
+    const bool issuer = tg < 32;
+    const long long total_groups = (long long)gridDim.x * NG;
+    const long long gid = (long long)blockIdx.x * NG + g;
+    const int bar_id = 1 + g;
+    constexpr int XS = XB / ELEM, YS = YB / ELEM;
+
+    unsigned char* ex = sm.extra(g);
+    T* dxrows = reinterpret_cast<T*>(ex);                          // [2][XS]
+    T* dyslots = reinterpret_cast<T*>(ex + SM::DXBUF);             // [DY_RING][WARPS_PER_GROUP][YS]
+    const bool dx_bulk = p.flags & 32;                             // atomic mode: dX rows meet the 16-byte rule
+
+    T gz[GZ_IN_REGS > 0 ? GZ_IN_REGS : 1];
+    T yr[Y_DIM], dyreg[Y_DIM];
+    T* gzs = reinterpret_cast<T*>(ex + SM::DXBUF + SM::DYSLOT);    // [ZPC_ALL - GZ_IN_REGS][G]
+
+    ItemWalker<MODE, false> walker(p, total_groups, gid, lane);
+    long long issued = 0;
+    bool more = true;
+    auto issue_next = [&]() {
+        if (!more) return;
+        long long e, s, r, lo, hi;
+        more = walker.next(e, s, r, lo, hi);
+        if (more) {
+            // header slot 2 carries the sender (the forward pass keeps a node bound there)
+            issue_item<MODE, false>(p, sm, g, (int)(issued % S), lane, e, s, r, s, hi);
+            ++issued;
+        } else if (lane == 0) {
+            *reinterpret_cast<volatile long long*>(sm.total(g)) = issued;
+        }
+    };
+    if constexpr (!PRODUCER) {
+        if (issuer) {
+            for (int i = 0; i < S - 1; ++i) issue_next();
+        }
+        group_sync(bar_id, G);
+    }
+
+    long long prev = -1;
+    for (long long it = 0;; ++it) {
+        const int stage = (int)(it % S);
+        if constexpr (!PRODUCER) {
+            if (issuer) issue_next();
+        }
+        if (acquire_item<MODE, false>(p, sm, g, it) != 0) break;
+        const long long* h = sm.hdr(g, stage);
+        const unsigned char* st = sm.stage(g, stage);
+        const long long item = h[0];
+        const long long node = h[1];     // receiver
+        const long long sender = h[2];
+        const T* sX = reinterpret_cast<const T*>(st + L::OFF_X);
+        const T* sY = reinterpret_cast<const T*>(st + L::OFF_Y);
+        const T* sWt = reinterpret_cast<const T*>(st + L::OFF_W);
+
+        if (node != prev) {
+            // a new run: this channel's slice of the receiver's output gradient, kept for the whole run
+            const T* zrow = p.dZ + node * (long long)Z_DIM;
+            sfor<0, N_OUT>([&](auto o_) {
+                constexpr int o = o_;
+                const bool live = (OUT_MUL[o] == CHANNELS) || (u < OUT_MUL[o]);
+#pragma unroll
+                for (int k = 0; k < OUT_D[o]; ++k) {
+                    const T v = live ? __ldg(zrow + OUT_OFF[o] + u * OUT_D[o] + k) : (T)0;
+                    if constexpr (out_reg_off(o) < GZ_REGS) gz[out_reg_off(o) + k] = v;
+                    else gzs[(out_reg_off(o) - GZ_FIRST_SMEM + k) * G + u] = v;    // private to this thread
+                }
+            });
+            prev = node;
+        }
+#pragma unroll
+        for (int j = 0; j < Y_DIM; ++j) {
+            yr[j] = sY[j];
+            dyreg[j] = (T)0;
+        }
+        T* dwrow = p.dW + item * (long long)W_NUMEL;
+        T* dxrow = dxrows + (it & 1) * XS;
+        const bool row_to_smem = MODE == MODE_DET || dx_bulk;
+        // instructions grouped by their first-input irrep: only that block of X and of dX is live at a time,
+        // and the block of the dX row leaves the registers as soon as its last instruction is done
+        sfor<0, N_IN1>([&](auto a_) {
+            constexpr int a = a_;
+            constexpr int D1 = IN1_D[a];
+            const bool live = (IN1_MUL[a] == CHANNELS) || (u < IN1_MUL[a]);
+            T x[D1], dxa[D1];
+#pragma unroll
+            for (int i = 0; i < D1; ++i) {
+                x[i] = live ? sX[IN1_OFF[a] + u * D1 + i] : (T)0;
+                dxa[i] = (T)0;
+            }
+            sfor<0, N_INSTR>([&](auto p_) {
+                constexpr int P = p_;
+                if constexpr (I_IN1[P] == a) {
+                    constexpr int b = I_IN2[P], o = I_OUT[P];
+                    constexpr int D2 = IN2_D[b];
+                    T av[D1], bv[D2];
+#pragma unroll
+                    for (int i = 0; i < D1; ++i) av[i] = (T)0;
+#pragma unroll
+                    for (int j = 0; j < D2; ++j) bv[j] = (T)0;
+                    const T w = live ? sWt[weight_offset<P>(u, 0)] : (T)0;
+                    if constexpr (out_reg_off(o) < GZ_REGS) {
+                        cg_backward<P>(x, &yr[IN2_OFF[b]], &gz[out_reg_off(o)], av, bv);
+                    } else {
+                        // this output irrep's slice of dZ is parked in shared memory ([value][channel]: no conflicts)
+                        T gs[OUT_D[o]];
+#pragma unroll
+                        for (int k = 0; k < OUT_D[o]; ++k) gs[k] = gzs[(out_reg_off(o) - GZ_FIRST_SMEM + k) * G + u];
+                        cg_backward<P>(x, &yr[IN2_OFF[b]], gs, av, bv);
+                    }
+                    T tw = (T)0;
+#pragma unroll
+                    for (int i = 0; i < D1; ++i) {
+                        tw = fma(x[i], av[i], tw);
+                        dxa[i] = fma(w, av[i], dxa[i]);
+                    }
+                    if (live) __stcs(dwrow + weight_offset<P>(u, 0), tw);
+#pragma unroll
+                    for (int j = 0; j < D2; ++j) dyreg[IN2_OFF[b] + j] = fma(w, bv[j], dyreg[IN2_OFF[b] + j]);
+                }
+            });
+            if (live) {
+#pragma unroll
+                for (int i = 0; i < D1; ++i) {
+                    if (row_to_smem) dxrow[IN1_OFF[a] + u * D1 + i] = dxa[i];
+                    else if constexpr (any_part_uses_in1(a))
+                        red_add(p.dX + sender * (long long)X_DIM + IN1_OFF[a] + u * D1 + i, dxa[i]);
+                }
+            }
+        });
+        // the stage has been read: hand it back
+        if constexpr (PRODUCER) release_stage<MODE, false>(sm, g, stage, lane);
+        const int ring = (int)(it % DY_RING);
+        {
+            constexpr int SHIFT = 5 - log2_int(next_pow2(Y_DIM));
+            warp_reduce_vector<Y_DIM>(dyreg, lane);
+            const int j = lane >> SHIFT;
+            if ((lane & ((1 << SHIFT) - 1)) == 0 && j < Y_DIM) dyslots[(ring * WARPS_PER_GROUP + warp) * YS + j] = dyreg[0];
+        }
+        // the bulk copy that read the other dX row buffer (issued one edge ago) leaves this one alone; the copy
+        // that read *this* buffer two edges ago was waited for before the previous barrier
+        if (row_to_smem) {
+            fence_async_smem();                     // this thread's part of the row, visible to the bulk copy
+            if (tg == 0) bulk_wait_read<0>();       // every earlier row copy has read its buffer: the next edge may overwrite it
+        }
+        group_sync(bar_id, G);
+        if (tg == 0 && row_to_smem) {
+            if constexpr (MODE == MODE_DET) {
+                bulk_s2g(reinterpret_cast<unsigned char*>(p.ws) + item * (long long)XB, dxrow, XB);
+            } else {
+                if constexpr (ELEM == 4) bulk_red_add_f32(reinterpret_cast<float*>(p.dX) + sender * (long long)X_DIM, dxrow, XB);
+                else bulk_red_add_f64(reinterpret_cast<double*>(p.dX) + sender * (long long)X_DIM, dxrow, XB);
+            }
+            bulk_commit();
+        }
+        {
+            const T* slots = dyslots + ring * WARPS_PER_GROUP * YS;
+            const int first = G >= 64 ? tg - 32 : tg;      // the second warp sums when there is one
+            if (first >= 0 && first < Y_DIM) {
+                T sum = (T)0;
+#pragma unroll
+                for (int w = 0; w < WARPS_PER_GROUP; ++w) sum += slots[w * YS + first];
+                p.dY[item * (long long)Y_DIM + first] = sum;
+            }
+        }
+    }
+    if (tg == 0) bulk_wait_all<0>();
+}
+
+// dX[s] = (or +=) the sum of the scratch rows of the edges that s sends, in sender_perm order, for the edges
+// of [e_lo, e_hi) whose rows `temp` holds (pitch XB bytes).  Work is dealt to `warps` warps in chunks of
+// the sender-ordered edge list; chunk ends are moved forward to the next sender boundary, so a sender's
+// edges are never split between two warps: every row of dX has one writer and a fixed summation order.
+// 32 positions are examined at a time; positions whose edge lies outside the range cost one coalesced
+// load and a ballot.  `first`: store the rows of the senders met (the host has cleared dX, so nodes that
+// send nothing stay zero); otherwise add.
+__device__ __forceinline__ long long align_sender(const long long* cols, const long long* perm, long long n, long long t,
+                                                  int lane) {
+    if (t <= 0) return 0;
+    if (t >= n) return n;
+    for (long long base = t; base < n + 32; base += 32) {
+        const long long idx = base + lane;
+        bool boundary = idx >= n;
+        if (!boundary) boundary = cols[perm[idx]] != cols[perm[idx - 1]];
+        const unsigned ballot = __ballot_sync(0xffffffffu, boundary);
+        if (ballot) return base + (__ffs(ballot) - 1);
+    }
+    return n;
+}
+
+__device__ void sum_sender_rows(const T* __restrict__ temp, T* __restrict__ dX, const long long* __restrict__ cols,
+                                const long long* __restrict__ perm, long long n_items, long long e_lo, long long e_hi,
+                                bool first, int chunk, long long warps, long long wid, int lane) {
+    constexpr int VEC = 16 / ELEM;                                  // elements per 16-byte load
+    constexpr int XS = XB / ELEM;
+    constexpr int NV = (XS / VEC + 31) / 32;                        // 16-byte pieces per lane
+    T acc[NV * VEC];
+#pragma unroll
+    for (int i = 0; i < NV * VEC; ++i) acc[i] = (T)0;
+    auto flush = [&](long long node) {
+        T* xrow = dX + node * (long long)X_DIM;
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+            const int base = (lane + 32 * v) * VEC;
+            if (base < X_DIM) {
+#pragma unroll
+                for (int q = 0; q < VEC; ++q)
+                    if (base + q < X_DIM) {
+                        if (first) xrow[base + q] = acc[v * VEC + q];
+                        else xrow[base + q] += acc[v * VEC + q];
+                    }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < NV * VEC; ++i) acc[i] = (T)0;
+    };
+    const long long n_chunks = (n_items + chunk - 1) / chunk;
+    for (long long c = wid; c < n_chunks; c += warps) {
+        const long long pos = align_sender(cols, perm, n_items, c * chunk, lane);
+        const long long end = c + 1 >= n_chunks ? n_items : align_sender(cols, perm, n_items, (c + 1) * chunk, lane);
+        long long prev = -1;
+        for (long long base = pos; base < end; base += 32) {
+            const long long k = base + lane;
+            long long e = -1, s = -1;
+            if (k < end) e = perm[k];
+            const bool in_block = e >= e_lo && e < e_hi;
+            unsigned mask = __ballot_sync(0xffffffffu, in_block);
+            if (mask == 0) continue;
+            if (in_block) s = cols[e];
+            while (mask) {
+                const int src = __ffs(mask) - 1;
+                mask &= mask - 1;
+                const long long ej = __shfl_sync(0xffffffffu, e, src);
+                const long long sj = __shfl_sync(0xffffffffu, s, src);
+                if (prev >= 0 && sj != prev) flush(prev);
+                prev = sj;
+                const T* row = temp + (ej - e_lo) * (long long)XS;
+#pragma unroll
+                for (int v = 0; v < NV; ++v) {
+                    const int b4 = (lane + 32 * v) * VEC;
+                    if (b4 < XS) {
+                        if constexpr (ELEM == 4) {
+                            const float4 t = __ldcs(reinterpret_cast<const float4*>(row + b4));
+                            acc[v * VEC + 0] += t.x; acc[v * VEC + 1] += t.y; acc[v * VEC + 2] += t.z; acc[v * VEC + 3] += t.w;
+                        } else {
+                            const double2 t = __ldcs(reinterpret_cast<const double2*>(row + b4));
+                            acc[v * VEC + 0] += t.x; acc[v * VEC + 1] += t.y;
+                        }
+                    }
+                }
+            }
+        }
+        if (prev >= 0) flush(prev);
+    }
+}
+
+template <int MODE>
+__device__ __forceinline__ void uvu_body_recv(const UvuParams& p) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    Smem<true, MODE, true> sm(smem_raw, p.stages);
+    const int tid = threadIdx.x;
+    if (tid == 0) {
+        const bool any_elem = !(p.flags & 1) || !(p.flags & 2) || !(p.flags & 4);
+        for (int g = 0; g < NG; ++g) {
+            for (int s = 0; s < p.stages; ++s) {
+                mbar_init(sm.full(g, s), 1 + (any_elem ? 32 : 0));
+                mbar_init(sm.empty(g, s), WARPS_PER_GROUP);
+            }
+            *sm.total(g) = -1;
+        }
+        fence_mbar_init();
+    }
+    __syncthreads();
+    if (tid >= NCONSUMERS + NSTAGING) {
+        if constexpr (HELPER_WARPS > 0) {
+            if (p.sum_items > 0)
+                sum_sender_rows(p.sum_ws, p.dX, p.sum_cols, p.sum_perm, p.sum_items, p.sum_e_lo, p.sum_e_hi, p.sum_first != 0,
+                                p.sum_chunk, (long long)gridDim.x * HELPER_WARPS,
+                                (long long)blockIdx.x * HELPER_WARPS + ((tid - NCONSUMERS - NSTAGING) >> 5), tid & 31);
+        }
+        return;
+    }
+    if (PRODUCER && tid >= NCONSUMERS) {
+        run_producer<MODE, false, true>(p, sm, (tid - NCONSUMERS) >> 5, tid & 31);
+        return;
+    }
+    run_backward_recv<MODE>(p, sm, tid / G, tid % G);
+}
+
 // ---------------------------------------------------------------- kernel body
 
 template <int MODE, bool BWD>
@@ -1178,6 +1519,8 @@ __device__ __forceinline__ void uvu_body(const UvuParams& p) {
 #define OEQ_K_BWD_DET 3
 #define OEQ_K_FWD_ATOMIC 4
 #define OEQ_K_BWD_ATOMIC 5
+#define OEQ_K_BWD_RECV_DET 6
+#define OEQ_K_BWD_RECV_ATOMIC 7
 
 extern "C" __global__ void __launch_bounds__(oeq::NTHREADS, oeqd::MIN_CTAS) oeq_uvu_kernel(const oeq::UvuParams p) {
 #if OEQ_KERNEL == OEQ_K_FWD_BATCH
@@ -1192,6 +1535,10 @@ extern "C" __global__ void __launch_bounds__(oeq::NTHREADS, oeqd::MIN_CTAS) oeq_
     oeq::uvu_body<oeq::MODE_ATOMIC, false>(p);
 #elif OEQ_KERNEL == OEQ_K_BWD_ATOMIC
     oeq::uvu_body<oeq::MODE_ATOMIC, true>(p);
+#elif OEQ_KERNEL == OEQ_K_BWD_RECV_DET
+    oeq::uvu_body_recv<oeq::MODE_DET>(p);
+#elif OEQ_KERNEL == OEQ_K_BWD_RECV_ATOMIC
+    oeq::uvu_body_recv<oeq::MODE_ATOMIC>(p);
 #else
 #error "OEQ_KERNEL must select one of the uvu kernels"
 #endif
@@ -1206,4 +1553,14 @@ extern "C" __global__ void oeq_reduce_partials(const oeqd::T* ws, oeqd::T* out, 
     for (long long g = 0; g < groups; ++g) s += ws[g * n + i];
     out[i] = s;
 }
+
+#if OEQ_KERNEL == OEQ_K_BWD_RECV_DET
+// The row sum of the deterministic receiver-order backward pass as a launch of its own (the last block of
+// edges, or every block when the launches carry no helper warps): see sum_sender_rows.
+extern "C" __global__ void __launch_bounds__(256) oeq_sum_sender_rows(const oeq::UvuParams p) {
+    oeq::sum_sender_rows(reinterpret_cast<const oeqd::T*>(p.ws), p.dX, p.cols, p.perm, p.n_items, p.e_lo, p.e_hi,
+                         (p.flags & 64) != 0, p.chunk, (long long)gridDim.x * (blockDim.x >> 5),
+                         (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), threadIdx.x & 31);
+}
+#endif
 #endif  // OEQ_UVU_NO_ENTRY

@@ -92,11 +92,32 @@ class ShardPlan:
                 me.send_rows.append((wanted - me.node_lo).astype(np.int64))
         return plans
 
+    @staticmethod
+    def build_one(rows, cols, nodes, rank, world):
+        """The plan of one rank with its send lists, without building the peers' plans: the rows this rank
+        ships to peer q are the distinct senders it owns among the edges of q's slice (ascending, which is
+        the order of q's halo)."""
+        rows = np.asarray(rows, dtype=np.int64)
+        cols = np.asarray(cols, dtype=np.int64)
+        me = ShardPlan(rows, cols, nodes, rank, world)
+        mine = np.nonzero((cols >= me.node_lo) & (cols < me.node_hi))[0]         # edges whose sender this rank owns
+        edge_lo = [int(np.searchsorted(rows, _owned_range(me.nodes, q, world)[0], side="left")) for q in range(world)]
+        owner = np.searchsorted(np.asarray(edge_lo[1:], dtype=np.int64), mine, side="right")   # rank holding each edge
+        me.send_rows = []
+        for q in range(world):
+            if q == rank:
+                me.send_rows.append(np.zeros(0, dtype=np.int64))
+            else:
+                me.send_rows.append((np.unique(cols[mine[owner == q]]) - me.node_lo).astype(np.int64))
+        return me
+
 
 class _ShardedConvFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, module, x_owned, y, w):
-        x_local = module.gather_senders(x_owned)
+        # a fresh tensor: it is saved for the backward pass, and a second forward before that backward must
+        # not overwrite it (the module's re-used buffer serves the calls that keep nothing)
+        x_local = module.gather_senders(x_owned, fresh=True)
         ctx.module = module
         ctx.save_for_backward(x_local, y, w)
         return module.local_forward(x_local, y, w)
@@ -121,7 +142,7 @@ class ShardedTensorProductConv:
         self.group = group
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
-        self.plan = ShardPlan.build_all(rows, cols, nodes, self.world)[self.rank]
+        self.plan = ShardPlan.build_one(rows, cols, nodes, self.rank, self.world)
         self.problem = problem
         self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
         if local_conv is None:
@@ -144,17 +165,19 @@ class ShardedTensorProductConv:
 
     # ---- exchange steps -------------------------------------------------------------
 
-    def gather_senders(self, x_owned: torch.Tensor) -> torch.Tensor:
-        """``[owned rows | halo rows]`` of X: one all-to-all of the rows the peers' edges read."""
+    def gather_senders(self, x_owned: torch.Tensor, fresh: bool = False) -> torch.Tensor:
+        """``[owned rows | halo rows]`` of X: one all-to-all of the rows the peers' edges read.  The result
+        lives in a buffer that the next call overwrites unless ``fresh`` asks for a new tensor."""
         plan = self.plan
         if x_owned.shape[0] != plan.owned:
             raise ValueError(f"rank {self.rank} owns {plan.owned} nodes, got {x_owned.shape[0]} rows")
         if self.world == 1:
             return x_owned.contiguous()
-        buf = self._x_local
+        buf = None if fresh else self._x_local
         if buf is None or buf.dtype != x_owned.dtype or buf.shape[1] != x_owned.shape[1]:
-            buf = self._x_local = torch.empty((plan.local_nodes, x_owned.shape[1]), dtype=x_owned.dtype,
-                                              device=x_owned.device)
+            buf = torch.empty((plan.local_nodes, x_owned.shape[1]), dtype=x_owned.dtype, device=x_owned.device)
+            if not fresh:
+                self._x_local = buf
         buf[:plan.owned].copy_(x_owned)
         send = x_owned.index_select(0, self.send_index)
         dist.all_to_all_single(buf[plan.owned:], send, output_split_sizes=self.recv_counts,
@@ -174,8 +197,7 @@ class ShardedTensorProductConv:
         start = 0
         for peer, count in enumerate(self.send_counts):      # fixed order; indices are unique within a peer
             if count:
-                idx = self.send_index_per_peer[peer]
-                out[idx] = out[idx] + recv[start:start + count]
+                out.index_add_(0, self.send_index_per_peer[peer], recv[start:start + count])
                 start += count
         return out
 

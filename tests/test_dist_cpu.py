@@ -60,6 +60,14 @@ def test_plan_partitions_nodes_and_edges():
                     first = sum(b.recv_counts[:a.rank])
                     assert np.array_equal(a.send_rows[b.rank] + a.node_lo,
                                           b.halo[first:first + b.recv_counts[a.rank]])
+        # a rank can build its own plan (with its send lists) without building its peers'
+        for p in plans:
+            one = ShardPlan.build_one(rows, cols, 37, p.rank, world)
+            assert np.array_equal(one.halo, p.halo) and np.array_equal(one.local_cols, p.local_cols)
+            assert np.array_equal(one.local_perm, p.local_perm) and one.recv_counts == p.recv_counts
+            assert len(one.send_rows) == world
+            for a, b in zip(one.send_rows, p.send_rows):
+                assert np.array_equal(a, b)
     with pytest.raises(ValueError):
         ShardPlan(rows[::-1], cols, 37, 0, 2)
     with pytest.raises(ValueError):
@@ -90,6 +98,16 @@ def _worker(rank, world, port, nodes, result):
                 rel_err(ws.grad.numpy(), rw[plan.edge_lo:plan.edge_hi])]
         z2, dx2, dy2, dw2 = conv.forward_backward(xs.detach(), ys.detach(), ws.detach(), dzs)
         errs.append(rel_err(dx2.numpy(), rx[plan.node_lo:plan.node_hi]))
+        # two forward passes on the same module before either backward pass (gradient accumulation, a layer
+        # applied twice): the second gather must not overwrite what the first saved
+        xa = torch.from_numpy(x[plan.node_lo:plan.node_hi]).requires_grad_(True)
+        xb = torch.from_numpy(2.0 * x[plan.node_lo:plan.node_hi]).requires_grad_(True)
+        za, zb = conv(xa, ys.detach(), ws.detach()), conv(xb, ys.detach(), ws.detach())
+        za.backward(dzs)
+        zb.backward(dzs)
+        errs.append(rel_err(xa.grad.numpy(), rx[plan.node_lo:plan.node_hi]))
+        errs.append(rel_err(xb.grad.numpy(), rx[plan.node_lo:plan.node_hi]))     # dX does not depend on X
+        errs.append(rel_err(zb.detach().numpy(), 2.0 * z_ref[plan.node_lo:plan.node_hi]))
         result[rank] = max(errs)
     finally:
         dist.destroy_process_group()

@@ -300,3 +300,47 @@ def test_periodic_radius_graph(name, nodes, lmax, deterministic):
             z2 = conv.forward(xt, yt, wt, *index)
             dx2, dy2, dw2 = conv.backward_helper(xt, yt, wt, dzt, *index)
             assert torch.equal(z, z2) and torch.equal(dx, dx2) and torch.equal(dy, dy2) and torch.equal(dw, dw2)
+
+
+@pytest.mark.parametrize("name", ["nequip_32", "mace_128"])
+def test_deterministic_backward_in_edge_blocks(name, monkeypatch):
+    """The receiver-order backward pass with scratch for only a part of the edges: it then runs block by block
+    (receiver-order launch + row sum per block, later blocks adding into dX).  Same results as the oracle, the
+    same bits run to run, and agreement with the scratch-free sender-order kernel."""
+    monkeypatch.setenv("OEQ_B200_BWD_SCRATCH_MB", "1")      # 1 MiB of scratch: a few hundred rows per block
+    monkeypatch.setenv("OEQ_B200_BWD_MIN_BLOCK", "1")
+    p = problem_by_name(name)
+    nodes = 300
+    rows, cols = random_graph(nodes, 4000, seed=41)
+    conv, (xt, yt, wt, dzt, index), (z, dx, dy, dw) = check_conv(p, nodes, rows, cols, 42, True)
+    assert conv.internal.last_backward_launches() >= 6        # several blocks, two launches each
+    dx2, dy2, dw2 = conv.backward_helper(xt, yt, wt, dzt, *index)
+    assert torch.equal(dx, dx2) and torch.equal(dy, dy2) and torch.equal(dw, dw2)
+    monkeypatch.setenv("OEQ_B200_BWD_SCRATCH_MB", "8192")
+    monkeypatch.setenv("OEQ_B200_BWD_RECV", "0")               # a new handle without the receiver-order kernel
+    old = oeq.TensorProductConv(p, torch_op=True, deterministic=True)
+    dx3, dy3, dw3 = old.backward_helper(xt, yt, wt, dzt, *index)
+    assert old.internal.last_backward_launches() == 1
+    assert rel_err(dx3.cpu().numpy(), dx.cpu().numpy()) < 1e-5
+    assert torch.equal(dy3, dy) or rel_err(dy3.cpu().numpy(), dy.cpu().numpy()) < 1e-5
+    assert rel_err(dw3.cpu().numpy(), dw.cpu().numpy()) < 1e-5
+
+
+def test_backward_without_scratch_uses_the_sender_order_kernel():
+    """A caller of the C ABI that passes no workspace still gets the deterministic backward pass."""
+    p = problem_by_name("nequip_32")
+    nodes = 50
+    rows, cols = random_graph(nodes, 600, seed=43)
+    rows, cols, order, perm = orc.coord_graph(rows, cols)
+    x, y, w, dz = conv_inputs(p, nodes, len(rows), 44)
+    conv = oeq.TensorProductConv(p, torch_op=True, deterministic=True)
+    xt, yt, wt, dzt, r, c, pm = cuda(x, y, w, dz, rows, cols, perm)
+    dx, dy, dw = torch.empty_like(xt), torch.empty_like(yt), torch.empty_like(wt)
+    conv.internal.backward(nodes, len(rows), xt.data_ptr(), yt.data_ptr(), wt.data_ptr(), dzt.data_ptr(), r.data_ptr(),
+                           c.data_ptr(), pm.data_ptr(), dx.data_ptr(), dy.data_ptr(), dw.data_ptr(), 0, 0,
+                           torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert conv.internal.last_backward_launches() == 1
+    rx, ry, rw = orc.conv_backward(p, x, y, w, dz, rows, cols)
+    assert rel_err(dx.cpu().numpy(), rx) < 1e-5 and rel_err(dy.cpu().numpy(), ry) < 1e-5
+    assert rel_err(dw.cpu().numpy(), rw) < 1e-5
