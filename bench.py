@@ -54,7 +54,11 @@ WORKLOADS = {
 # capture (dram__bytes_read.sum + dram__bytes_write.sum) of a small case of the same workload; the
 # capture's case and date are named in the line ("traffic_from").  Only the per-edge arrays scale with
 # the edge count, so this is an estimate for other sizes, and it is refreshed when the kernels change.
-NCU_BWD_DRAM = {}   # (workload, numbering) -> (bytes per edge, "what was captured")
+NCU_BWD_DRAM = {   # (workload, numbering) -> (bytes per edge, "what was captured")
+    ("mace_large", "morton"): (12.76e9 / 299832, "ncu dram__bytes_read.sum + dram__bytes_write.sum over all launches of one "
+                                                  "backward pass, 10 000 nodes / 299 832 edges, captured 2026-11-25 "
+                                                  "(profiles/conv_backward_receiver_order_mace_large.md)"),
+}
 
 
 def parse_args():
