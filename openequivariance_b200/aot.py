@@ -9,14 +9,13 @@ kernel headers, so stale entries are simply never hit.
 
 from __future__ import annotations
 
-import json
 import os
 from concurrent.futures import ProcessPoolExecutor
 
 import numpy as np
 
 from . import _native
-from .problem import ChannelwiseTPP, FullyConnectedTPProblem, TPProblem
+from .problem import ChannelwiseTPP, FullyConnectedTPProblem, SingleInstruction, TPProblem
 
 BATCH, DET, ATOMIC = _native.KIND_BATCH, _native.KIND_CONV_DET, _native.KIND_CONV_ATOMIC
 
@@ -39,16 +38,9 @@ def named_problems():
     ]
 
 
-def _golden_test_problems():
-    """Problems of the test suite, read from its fixture list when the tests are present."""
-    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "tests", "golden", "problems.json")
-    if not os.path.exists(path):
-        return []
-    with open(path) as f:
-        return json.load(f)
-
-
 def _build_entry(entry, dt):
+    """A problem from a description ``{"kind", "args", "kwargs"}`` (kinds: tpp, channelwise, fully_connected,
+    single)."""
     kind, args, kwargs = entry["kind"], entry["args"], dict(entry["kwargs"])
     kwargs.update(irrep_dtype=dt, weight_dtype=dt)
     if kind == "tpp":
@@ -56,24 +48,26 @@ def _build_entry(entry, dt):
         return TPProblem(a, b, c, [tuple(i) for i in instr], **kwargs)
     if kind == "channelwise":
         return ChannelwiseTPP(*args, **kwargs)
+    if kind == "single":
+        return SingleInstruction(*args, **kwargs)
     return FullyConnectedTPProblem(*args, **kwargs)
 
 
-def _jobs():
+def _jobs(extra):
     jobs = []
     for n, (_, make, kinds) in enumerate(named_problems()):
-        jobs.append(("named", n, "f32", kinds))
-    for n, entry in enumerate(_golden_test_problems()):
-        conv_ok = entry["kind"] == "channelwise" or entry["name"] == "readme"
+        jobs.append(("named", n, None, "f32", kinds))
+    for entry in extra:
+        conv_ok = entry["kind"] == "channelwise" or entry.get("name") == "readme"
         for dt in ("f32", "f64"):
-            jobs.append(("golden", n, dt, BATCH | ((DET | ATOMIC) if conv_ok else 0)))
+            jobs.append(("extra", 0, entry, dt, BATCH | ((DET | ATOMIC) if conv_ok else 0)))
     return jobs
 
 
 def _run(job):
-    source, n, dt_name, kinds = job
+    source, n, entry, dt_name, kinds = job
     dt = np.float32 if dt_name == "f32" else np.float64
-    problem = named_problems()[n][1](dt) if source == "named" else _build_entry(_golden_test_problems()[n], dt)
+    problem = named_problems()[n][1](dt) if source == "named" else _build_entry(entry, dt)
     for bit in (BATCH, DET, ATOMIC):
         if kinds & bit:
             try:
@@ -84,9 +78,11 @@ def _run(job):
     return job
 
 
-def precompile_all(workers: int | None = None):
+def precompile_all(extra_problems=(), workers: int | None = None):
+    """Specialise the kernels of the benchmark configurations and of ``extra_problems`` (problem descriptions
+    as in ``_build_entry``; the build entry point hands in the test suite's list)."""
     _native.lib()  # build/load once in the parent so the children find the library
-    jobs = _jobs()
+    jobs = _jobs(list(extra_problems))
     workers = workers or min(len(jobs), os.cpu_count() or 1)
     import multiprocessing
     # spawn: the children must not inherit the parent's loaded compiler library across a fork

@@ -36,6 +36,8 @@ def build_problem(entry, **overrides):
         return oeq.ChannelwiseTPP(*args, **kwargs)
     if kind == "fully_connected":
         return oeq.FullyConnectedTPProblem(*args, **kwargs)
+    if kind == "single":
+        return oeq.SingleInstruction(*args, **kwargs)
     raise ValueError(kind)
 
 

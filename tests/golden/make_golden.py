@@ -14,7 +14,8 @@ reference package's ``__init__`` builds a CUDA extension on import, so the
 package and its ``extlib`` are replaced by empty stand-ins first.
 
 Outputs (all small):
-  wigner_3j.npz          real Wigner 3j tensors for every valid l1,l2,l3 <= 4
+  wigner_3j.npz          real Wigner 3j tensors for every valid l1,l2,l3 <= 7 (the reference's roofline
+                         benchmark set, test/benchmark.py:56-70, reaches l = 7)
   problems.json          path weights / shapes / weight_numel of named problems
   numpy_tp_forward.npz   NumpyTensorProduct.forward_cpu on seeded inputs
   weight_perm.npz        reorder_weights applied to arange(weight_numel)
@@ -83,6 +84,22 @@ PROBLEMS = [
                            [[0, 0, 0, "uvu", True], [1, 1, 0, "uvu", True], [0, 1, 1, "uvu", True],
                             [1, 0, 1, "uvu", True]]],
      {"shared_weights": True, "internal_weights": False}),
+    # the reference's benchmark shapes with mixed parities and second-input multiplicity 1
+    # (openequivariance/benchmark/benchmark_configs.py:38-47)
+    ("tetris_poly_1", "fully_connected", ["1x0e + 1x1o + 1x2e + 1x3o", "1x0e + 1x1o + 1x2e + 1x3o",
+                                          "64x0e + 24x1e + 24x1o + 16x2e + 16x2o"], {}),
+    ("tetris_poly_2", "fully_connected", ["64x0e + 24x1e + 24x1o + 16x2e + 16x2o", "1x0e + 1x1o + 1x2e + 1x3o",
+                                          "0o + 6x0e"], {}),
+    ("diffdock_l1", "fully_connected", ["10x1o + 10x1e + 48x0e + 48x0o", "1x0e + 1x1o",
+                                        "10x1o + 10x1e + 48x0e + 48x0o"], {"shared_weights": False}),
+    ("diffdock_l2", "fully_connected", ["10x1o + 10x1e + 48x0e + 48x0o", "1x0e + 1x1o + 1x2e",
+                                        "10x1o + 10x1e + 48x0e + 48x0o"], {"shared_weights": False}),
+    # single instructions of the reference's roofline set (test/benchmark.py:56-70), l up to 7
+    ("roofline_1e", "single", ["128x1e", "1x1e", "128x1e", "uvu"], {}),
+    ("roofline_5e_3e", "single", ["128x5e", "1x5e", "128x3e", "uvu"], {}),
+    ("roofline_6e", "single", ["128x6e", "1x3e", "128x6e", "uvu"], {}),
+    ("roofline_7e_4e", "single", ["128x7e", "1x4e", "128x7e", "uvu"], {}),
+    ("roofline_7e_7e", "single", ["128x7e", "1x7e", "128x7e", "uvu"], {}),
 ]
 
 
@@ -95,6 +112,8 @@ def build(ref_mods, kind, args, kwargs):
         return tpp.ChannelwiseTPP(*args, **kwargs)
     if kind == "fully_connected":
         return tpp.FullyConnectedTPProblem(*args, **kwargs)
+    if kind == "single":
+        return tpp.SingleInstruction(*args, **kwargs)
     raise ValueError(kind)
 
 
@@ -111,7 +130,7 @@ def main():
 
     # 1. Wigner 3j
     tensors = {}
-    lmax = 4
+    lmax = 7
     for l1 in range(lmax + 1):
         for l2 in range(lmax + 1):
             for l3 in range(abs(l1 - l2), min(l1 + l2, lmax) + 1):
@@ -141,7 +160,7 @@ def main():
     # (NumpyTensorProduct indexes weights by output block, so it is only valid for
     # channel-wise problems: second-input multiplicity 1, one output block per instruction)
     for name, batch in [("readme", 1000), ("nequip_32", 24), ("cw_mixed", 17), ("mace_128", 3),
-                        ("mace_large_128", 2)]:
+                        ("mace_large_128", 2), ("roofline_5e_3e", 2), ("roofline_6e", 2), ("roofline_7e_7e", 2)]:
         p = built[name]
         in1, in2, w, out = get_random_buffers_forward(p, batch, 12345)
         NumpyTensorProduct(p).forward_cpu(in1, in2, out, w)

@@ -15,6 +15,8 @@ pytestmark = pytest.mark.gpu
 CASES = [
     ("readme", 1000), ("nequip_32", 257), ("cw_mixed", 100), ("mace_128", 64), ("mace_large_128", 33),
     ("uvu_v2", 50), ("uvu_mul40_v3", 37), ("uvu_norm_path", 129), ("uvu_shared", 300),
+    # single instructions of the reference's roofline benchmark set (test/benchmark.py:56-70), l up to 7
+    ("roofline_1e", 40), ("roofline_5e_3e", 24), ("roofline_6e", 24), ("roofline_7e_4e", 16), ("roofline_7e_7e", 12),
 ]
 
 
@@ -71,7 +73,8 @@ def test_readme_golden_through_host_entry_points():
     assert rel_err(dx, rx) < 1e-5 and rel_err(dy, ry) < 1e-5 and rel_err(dw, rw) < 1e-5
 
 
-@pytest.mark.parametrize("name", ["nequip_32", "cw_mixed", "mace_128", "mace_large_128"])
+@pytest.mark.parametrize("name", ["nequip_32", "cw_mixed", "mace_128", "mace_large_128", "roofline_5e_3e",
+                                  "roofline_6e", "roofline_7e_7e"])
 def test_forward_matches_reference_numpy_golden(name):
     g = load_golden("numpy_tp_forward.npz")
     p = problem_by_name(name)

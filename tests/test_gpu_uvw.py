@@ -10,7 +10,10 @@ from helpers import REL_TOL, rel_err, tp_inputs, to_oeq, to_e3nn
 
 pytestmark = pytest.mark.gpu
 
-CASES = [("uvw_small", 100), ("uvw_small", 3), ("uvw_mul40", 37), ("uvw_rowweights", 50), ("uvw_64", 70)]
+CASES = [("uvw_small", 100), ("uvw_small", 3), ("uvw_mul40", 37), ("uvw_rowweights", 50), ("uvw_64", 70),
+         # the reference's tetris-polynomial and DiffDock benchmark shapes (benchmark_configs.py:38-47): second
+         # input of multiplicity 1 with mixed parities; DiffDock carries per-row 'uvw' weights at multiplicity 48
+         ("tetris_poly_1", 60), ("tetris_poly_2", 60), ("diffdock_l1", 40), ("diffdock_l2", 24)]
 
 
 def run_case(name, batch, dtype, seed=11111):
@@ -158,3 +161,31 @@ def test_tensor_core_forward_many_tiles_mixed_multiplicities(in1, in2, out, batc
     assert rel_err(z.cpu().numpy(), fma(xt, yt, wt).cpu().numpy()) < 1e-5
     rows = np.arange(0, batch, 997)
     assert rel_err(z.cpu().numpy()[rows], orc.tp_forward(p, x[rows], y[rows], w)) < 1e-5
+
+
+def test_cross_product_closed_form():
+    """'uvw' with shared weights against an answer that can be written down: 1o x 1o -> 1e is the cross
+    product / sqrt(6) (sign from the stored Wigner tensor), contracted with W[u, v, w] and the path weight."""
+    nu, nv, nw, b = 3, 2, 4, 50
+    p = oeq.TPProblem(f"{nu}x1o", f"{nv}x1o", f"{nw}x1e", [(0, 0, 0, "uvw", True)], shared_weights=True,
+                      internal_weights=False)
+    rng = np.random.default_rng(91)
+    x = rng.normal(size=(b, nu, 3)).astype(np.float32)
+    y = rng.normal(size=(b, nv, 3)).astype(np.float32)
+    w = rng.normal(size=(nu, nv, nw)).astype(np.float32)
+    dz = rng.normal(size=(b, nw, 3)).astype(np.float32)
+    eps = np.zeros((3, 3, 3))
+    for i, j, k in ((0, 1, 2), (1, 2, 0), (2, 0, 1)):
+        eps[i, j, k], eps[j, i, k] = 1.0, -1.0
+    scale = np.sign(orc.cg(1, 1, 1)[0, 1, 2]) / np.sqrt(6.0) * p.instructions[0].path_weight
+    want_z = scale * np.einsum("uvw,ijk,bui,bvj->bwk", w.astype(np.float64), eps, x.astype(np.float64), y.astype(np.float64))
+    want_dw = scale * np.einsum("bwk,ijk,bui,bvj->uvw", dz.astype(np.float64), eps, x.astype(np.float64), y.astype(np.float64))
+    tp = oeq.TensorProduct(p, torch_op=True)
+    w_oeq = to_oeq(p, w.reshape(-1))
+    xt, yt, wt, dzt = (torch.from_numpy(np.ascontiguousarray(a)).cuda()
+                       for a in (x.reshape(b, -1), y.reshape(b, -1), w_oeq, dz.reshape(b, -1)))
+    z = tp(xt, yt, wt)
+    _, _, dw = tp.backward_helper(xt, yt, wt, dzt)
+    torch.cuda.synchronize()
+    assert rel_err(z.cpu().numpy().reshape(want_z.shape), want_z) < 1e-5
+    assert rel_err(to_e3nn(p, dw.cpu().numpy()).reshape(want_dw.shape), want_dw) < 1e-5

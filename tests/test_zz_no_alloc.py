@@ -51,3 +51,32 @@ def test_refuses_what_does_not_fit_or_needs_no_scratch():
     shared = _native.TPHandle(problem_by_name("uvu_shared"))
     assert lib.oeq_tp_backward_noalloc(shared.ptr, 0, *([buf.data_ptr()] * 7), stream) == 1
     assert lib.oeq_tp_backward_noalloc(shared.ptr, 4, 0, *([buf.data_ptr()] * 6), stream) == 1
+
+
+def test_narrowed_launch_and_a_handle_without_status_word():
+    """A weight tensor of 176 KiB leaves room for 46 partial gradients in the 8 MiB array, fewer than the CTAs
+    the regular launch would use, so the entry point has to narrow its grid; and it is the first call on a
+    new handle, which owns no status word yet.  The regular entry point (called afterwards) must agree."""
+    from openequivariance_b200 import _native
+    p = problem_by_name("uvw_64")
+    batch = 3000
+    assert p.weight_numel * 4 > (8 << 20) // 296
+    handle = _native.TPHandle(p)
+    lib = _native.lib()
+    stream = torch.cuda.current_stream().cuda_stream
+    x, y, w, dz = tp_inputs(p, batch, 7)
+    xt, yt, wt, dzt = (torch.from_numpy(a).cuda() for a in (x, y, to_oeq(p, (w / 8).astype(np.float32)), dz))
+    got = [torch.full_like(t, float("nan")) for t in (xt, yt, wt)]
+    _native.check(lib.oeq_tp_backward_noalloc(handle.ptr, batch, xt.data_ptr(), yt.data_ptr(), wt.data_ptr(),
+                                              dzt.data_ptr(), *(t.data_ptr() for t in got), stream))
+    torch.cuda.synchronize()
+    handle.check()
+    want = [torch.empty_like(t) for t in (xt, yt, wt)]
+    ws_bytes = handle.workspace_bytes(batch)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda")
+    handle.backward(batch, xt.data_ptr(), yt.data_ptr(), wt.data_ptr(), dzt.data_ptr(),
+                    *(t.data_ptr() for t in want), ws.data_ptr(), ws_bytes, stream)
+    torch.cuda.synchronize()
+    handle.check()
+    for g, e in zip(got, want):
+        assert rel_err(g.cpu().numpy(), e.cpu().numpy()) < 1e-5
