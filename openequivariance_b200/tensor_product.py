@@ -72,6 +72,10 @@ class TensorProductBase:
 
 
 class TensorProduct(TensorProductBase):
+    """``torch_op`` is kept for signature compatibility (the reference's ``TensorProduct`` requires it, its
+    ``LoopUnrollTP`` defaults it to True; this class serves under both names): the torch custom ops are
+    registered whatever its value, because device memory and streams come from torch in either case."""
+
     def __init__(self, problem: TPProblem, torch_op: bool = True):
         super().__init__(problem, torch_op=torch_op)
         if len(problem.instructions) == 0:

@@ -21,6 +21,7 @@ Outputs (all small):
   weight_perm.npz        reorder_weights applied to arange(weight_numel)
   coord_graph.npz        CoordGraph ordering of a random multigraph
   scatter_sum.npz        scatter_sum on CPU
+  bench_conventions.json flop / byte counts of the reference's benchmark records for the named problems
 """
 
 import json
@@ -207,6 +208,25 @@ def main():
     idx = torch.as_tensor(rows)
     out = scatter_sum(src=src, index=idx, dim=0, dim_size=n)
     np.savez_compressed(os.path.join(HERE, "scatter_sum.npz"), src=src.numpy(), index=rows, out=out.numpy())
+    # 7. flop and byte conventions of the reference's benchmark records
+    from openequivariance.benchmark.perf_metrics_utils import (calculate_minimum_flops_forward,
+                                                              calculate_minimum_memory_streamed_forward,
+                                                              calculate_minimum_memory_streamed_backward)
+    from openequivariance.benchmark.e3nn_lite_utils import calculate_total_nnz
+    from openequivariance.implementations.convolution.ConvolutionBase import flops_data_per_tp
+    conv = {}
+    for name, p in built.items():
+        entry = {"total_cg_nnz": int(calculate_total_nnz(p)),
+                 "minimum_flops_forward": {k: int(v) for k, v in calculate_minimum_flops_forward(p, 7).items()},
+                 "memory_forward": {k: int(v) for k, v in calculate_minimum_memory_streamed_forward(p, 7).items()},
+                 "memory_backward": {k: int(v) for k, v in calculate_minimum_memory_streamed_backward(p, 7).items()}}
+        if not p.shared_weights:
+            for direction in ("forward", "backward"):
+                ops, data, nnz = flops_data_per_tp(p, direction)
+                entry[f"conv_{direction}"] = [int(ops), int(data), int(nnz)]
+        conv[name] = entry
+    with open(os.path.join(HERE, "bench_conventions.json"), "w") as f:
+        json.dump(conv, f, indent=1)
     print("golden fixtures written to", HERE)
 
 
