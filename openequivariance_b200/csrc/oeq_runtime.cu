@@ -1791,11 +1791,15 @@ int oeq_conv_backward(oeq_conv* h, int64_t nodes, int64_t edges, const void* X, 
         // b % 2 while its helper warps sum block b - 1 from the other half; the last block is summed by a
         // launch of its own.  Blocks are kept above a minimum size, and a list that fits one half is still cut
         // into a few blocks so that most of the summing hides behind the receiver-order launches.
-        const bool pipelined = k.map.helper_warps > 0 && edges >= 4 * recv_min_block_edges();
+        // Pipelining pays when a block's receiver-order launch runs for a millisecond or more; the scratch
+        // bytes of a block are a fair proxy for that (wide rows mean much arithmetic per edge).
+        const size_t min_block_bytes = (size_t)std::max(1, env_int("OEQ_B200_PIPELINE_BLOCK_MB", 512)) << 20;
+        const long long min_block = std::max<long long>(recv_min_block_edges(), (long long)(min_block_bytes / row));
+        const bool pipelined = k.map.helper_warps > 0 && edges >= 4 * min_block;
         if (pipelined) {
             const long long half = (long long)(workspace_bytes / row / 2);
             long long be = std::min<long long>(half, (edges + 3) / 4);
-            be = std::max<long long>(be, std::min<long long>(half, recv_min_block_edges()));
+            be = std::max<long long>(be, std::min<long long>(half, min_block));
             if (be >= 1) {
                 char* halves[2] = {(char*)workspace, (char*)workspace + (size_t)half * row};
                 long long prev_e0 = -1, prev_n = 0;

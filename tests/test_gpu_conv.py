@@ -309,6 +309,9 @@ def test_deterministic_backward_in_edge_blocks(name, monkeypatch):
     same bits run to run, and agreement with the scratch-free sender-order kernel."""
     monkeypatch.setenv("OEQ_B200_BWD_SCRATCH_MB", "1")      # 1 MiB of scratch: a few hundred rows per block
     monkeypatch.setenv("OEQ_B200_BWD_MIN_BLOCK", "1")
+    if name == "mace_128":
+        monkeypatch.setenv("OEQ_B200_PIPELINE_BLOCK_MB", "1")   # blocks of a few hundred edges are pipelined too:
+        # each launch's helper warps sum the previous block while the consumers work on the current one
     p = problem_by_name(name)
     nodes = 300
     rows, cols = random_graph(nodes, 4000, seed=41)
