@@ -434,6 +434,42 @@ def conv_case(torch, args, spec, workload, device, variant, numbering, nodes=Non
     return res
 
 
+def uvw_conv_case(torch, args, device, nodes=20_000, degree=40.0, steps=5, warmup=3):
+    """Shared-weight 'uvw' convolution (64x(0e+1o+2e), harmonics to l=2) on a Nequip-sized graph: the unit-weight
+    edge sum over the edges, then the dense contraction over the nodes; forward and backward (all gradients)."""
+    import openequivariance_b200 as oeq
+    from openequivariance_b200.graph import periodic_radius_graph, spherical_harmonics
+    p = oeq.FullyConnectedTPProblem("64x0e+64x1o+64x2e", "0e+1o+2e", "64x0e+64x1o+64x2e")
+    g = periodic_radius_graph(nodes, degree, seed=args.seed, numbering="morton")
+    conv = oeq.TensorProductConv(p, torch_op=True, deterministic=True)
+    idx = [torch.from_numpy(a).to(device) for a in (g.rows, g.cols, g.sender_perm)]
+    gen = torch.Generator(device=device).manual_seed(args.seed)
+    x = torch.randn(g.node_count, p.irreps_in1.dim, device=device, generator=gen)
+    dz = torch.randn(g.node_count, p.irreps_out.dim, device=device, generator=gen)
+    w = torch.randn(p.weight_numel, device=device, generator=gen) / 8
+    y = spherical_harmonics(2, torch.from_numpy(g.vectors).to(device=device, dtype=torch.float32)).contiguous()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    tf, tb = [], []
+    for i in range(warmup + steps):
+        flush.zero_()
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        e[0].record()
+        z = conv.forward(x, y, w, *idx)
+        e[1].record()
+        out = conv.backward_helper(x, y, w, dz, *idx)
+        e[2].record()
+        torch.cuda.synchronize()
+        del z, out
+        if i >= warmup:
+            tf.append(e[0].elapsed_time(e[1]))
+            tb.append(e[1].elapsed_time(e[2]))
+    conv.check_device_status()
+    fwd, bwd = statistics.median(tf), statistics.median(tb)
+    return {"nodes": g.node_count, "edges": g.nnz, "forward_ms": fwd, "backward_ms": bwd,
+            "edges_per_s": g.nnz / ((fwd + bwd) * 1e-3),
+            "note": "backward includes a recomputation of the edge sum; weights applied once per node, not per edge"}
+
+
 def secondary_block(torch, args, device, peaks):
     """The other configurations, measured in this process with the same protocol (CUDA events, L2 flushed or
     inputs larger than L2): batch 'uvu' (50 000 rows), Nequip convolution both variants, 'uvw' FP32 / FP64."""
@@ -450,6 +486,7 @@ def secondary_block(torch, args, device, peaks):
         out[f"conv_nequip_{variant}"] = conv_case(torch, args, WORKLOADS["nequip"], "nequip", device, variant, "morton")
     out["conv_mace_large_atomic_20k_nodes"] = conv_case(torch, args, WORKLOADS["mace_large"], "mace_large", device,
                                                         "atomic", "morton", nodes=20_000)
+    out["conv_uvw_fc64_shared_20k_nodes"] = uvw_conv_case(torch, args, device)
     for dt, pk in (("f32", peaks["tf32_tflops"]), ("f64", peaks["fp64_tflops"])):
         r = bench_tp.measure("uvw_fc", dt, steps=10, warmup=3)
         out[f"batch_uvw_fc_100k_{dt}"] = {

@@ -72,7 +72,10 @@ typedef struct oeq_problem_desc {
     const oeq_irrep* out;
     const oeq_instruction* instr;
     int32_t dtype;          /* OEQ_F32 or OEQ_F64; irreps and weights share it */
-    int32_t shared_weights; /* 1: W is [weight_numel]; 0: W is [rows][weight_numel] */
+    int32_t shared_weights; /* 1: W is [weight_numel]; 0: W is [rows][weight_numel];
+                               2 ('uvu' convolution only): there is no weight array, every weight is 1 -- W and dW
+                               may be NULL and are not touched (used for the edge sum in front of a shared dense
+                               contraction; no counterpart in the reference) */
 } oeq_problem_desc;
 
 typedef struct oeq_tp oeq_tp;

@@ -106,7 +106,7 @@ def check(code: int):
 class Descriptor:
     """Owns the ctypes arrays behind one ``oeq_problem_desc``."""
 
-    def __init__(self, problem):
+    def __init__(self, problem, unit_weights=False):
         modes = {ins.connection_mode for ins in problem.instructions}
         if len(problem.instructions) == 0:
             raise ValueError("Tensor product problem has no valid intructions!")
@@ -144,15 +144,15 @@ class Descriptor:
         self.struct = _ProblemDesc(len(problem.irreps_in1), len(problem.irreps_in2), len(problem.irreps_out),
                                    len(problem.instructions), in1, in2, out, instr,
                                    1 if problem.irrep_dtype == np.float64 else 0,
-                                   1 if problem.shared_weights else 0)
+                                   2 if unit_weights else (1 if problem.shared_weights else 0))
 
     def ref(self):
         return C.byref(self.struct)
 
 
-def precompile(problem, kinds: int):
+def precompile(problem, kinds: int, unit_weights: bool = False):
     """Specialise the kernels of ``problem`` into the on-disk cache (no GPU needed)."""
-    d = Descriptor(problem)
+    d = Descriptor(problem, unit_weights=unit_weights)
     check(lib().oeq_precompile(d.ref(), kinds))
 
 
@@ -203,9 +203,9 @@ class TPHandle(_Handle):
 class ConvHandle(_Handle):
     _destroy = "oeq_conv_destroy"
 
-    def __init__(self, problem, deterministic):
+    def __init__(self, problem, deterministic, unit_weights=False):
         super().__init__()
-        self.desc = Descriptor(problem)
+        self.desc = Descriptor(problem, unit_weights=unit_weights)
         check(lib().oeq_conv_create(self.desc.ref(), 1 if deterministic else 0, C.byref(self.ptr)))
 
     def workspace_bytes(self, nodes, edges):

@@ -75,6 +75,18 @@ def _run(job):
             except _native.OeqError as err:
                 if err.code != 2:  # "unsupported problem" is a property of the problem, not a build failure
                     raise
+    # shared-weight 'uvw' problems with a second input of multiplicity 1 also serve as graph convolutions:
+    # the unit-weight edge sum and the dense stage (conv.UVWConvPlan)
+    if (problem.shared_weights and all(i.connection_mode == "uvw" for i in problem.instructions)
+            and all(mul == 1 for mul, _ in problem.irreps_in2)):
+        from .conv import UVWConvPlan
+        plan = UVWConvPlan(problem)
+        try:
+            _native.precompile(plan.edge_sum, DET | ATOMIC, unit_weights=True)
+            _native.precompile(plan.dense, BATCH)
+        except _native.OeqError as err:
+            if err.code != 2:
+                raise
     return job
 
 

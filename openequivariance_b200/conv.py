@@ -15,6 +15,11 @@ LoopUnrollConv.py:7-87, ConvolutionBase.py:45-109, 560-709):
   bit-reproducible run to run.
 * "uvu" problems whose second input has multiplicity 1 everywhere, per-edge
   weights, int64 indices.
+* "uvw" problems with *shared* weights (second input of multiplicity 1), which the reference does not
+  offer ("coming soon", reference: README.md:82-85): the dense weight contraction is linear, so the
+  per-edge products are summed per receiver first (the fused gather - product - scatter kernel with every
+  weight 1) and the weights are applied once per node, on the tensor cores, instead of once per edge
+  (``UVWConvPlan``).
 * first and second derivatives as ``torch.library`` custom ops.
 
 Unlike the reference, the deterministic backward pass reads the sender and the
@@ -53,6 +58,44 @@ class CoordGraph:
         self.transpose_perm = np.lexsort((self.rows, self.cols)).astype(self.rows.dtype)
 
 
+class UVWConvPlan:
+    """How a shared-weight "uvw" convolution is split in two fused stages.
+
+    ``Z[n, w, k] = sum_e pw_p sum_u W_p[u, w] sum_ij C_ijk x[s_e, u, i] y[e, j]`` is linear in the per-edge
+    product, so the edge sum moves inside: stage 1 is the channel-wise ("uvu") convolution with every
+    weight 1 and one output block ``mul_u x ir_out`` per instruction, ``S_p[n, u, k] = sum_e sum_ij C_ijk
+    x[s_e, u, i] y[e, j]`` (the fused gather - product - scatter kernels, no weight array); stage 2 is the
+    batch "uvw" product ``Z[n] = sum_p pw_p W_p . S_p[n]`` over *nodes*, written as ``S_p x 1x0e -> out``
+    so that the tensor-core kernels take it (the l x 0 -> l Wigner tensor is the identity / sqrt(2l+1);
+    its value is divided out of the path weight).  The weights keep their layout: instruction p has the
+    same ``(u, 1, w)`` block in both problems.
+    """
+
+    def __init__(self, config: TPProblem):
+        from .irreps import Irreps
+        from .wigner import wigner_3j
+        assert config.shared_weights, "the fused 'uvw' convolution needs shared weights"
+        for mul, _ in config.irreps_in2:
+            assert mul == 1, "the fused convolution needs multiplicity 1 for every irrep of the second input"
+        blocks, edge_instr, dense_instr, dense_pw = [], [], [], []
+        for p, ins in enumerate(config.instructions):
+            assert ins.connection_mode == "uvw" and ins.has_weight
+            mul_u = config.irreps_in1[ins.i_in1].mul
+            ir_out = config.irreps_out[ins.i_out].ir
+            blocks.append((mul_u, ir_out))
+            edge_instr.append((ins.i_in1, ins.i_in2, p, "uvu", True))
+            dense_instr.append((p, 0, ins.i_out, "uvw", True))
+            identity = float(np.asarray(wigner_3j(ir_out.l, 0, ir_out.l))[0, 0, 0])
+            dense_pw.append(ins.path_weight / identity)
+        kw = dict(irrep_dtype=config.irrep_dtype, weight_dtype=config.weight_dtype, internal_weights=False)
+        self.edge_sum = TPProblem(config.irreps_in1, config.irreps_in2, Irreps(blocks), edge_instr,
+                                  shared_weights=False, **kw)
+        self.edge_sum.instructions = [i._replace(path_weight=1.0) for i in self.edge_sum.instructions]
+        self.dense = TPProblem(Irreps(blocks), "1x0e", config.irreps_out, dense_instr, shared_weights=True, **kw)
+        self.dense.instructions = [i._replace(path_weight=w) for i, w in zip(self.dense.instructions, dense_pw)]
+        assert self.dense.weight_numel == config.weight_numel
+
+
 class TensorProductConv(TensorProductBase):
     def __init__(self, config: TPProblem, torch_op: bool = False, deterministic: bool = False,
                  idx_dtype=np.int64):
@@ -62,24 +105,65 @@ class TensorProductConv(TensorProductBase):
             raise ValueError("Tensor product problem has no valid intructions!")
         for mul, _ in self.L2:
             assert mul == 1, "the fused convolution needs multiplicity 1 for every irrep of the second input"
-        for inst in config.instructions:
-            assert inst.connection_mode == "uvu", "the fused convolution supports 'uvu' only"
-        assert not config.shared_weights, "the fused convolution needs per-edge weights"
         self.idx_dtype = idx_dtype
         self.deterministic = deterministic
         self.conv_id = next(_conv_ids)
+        self._scratch = {}
+        self.workspace_size = 0
+        self.workspace_ptr = 0
+        self.unit_weights = False
+        if all(inst.connection_mode == "uvw" for inst in config.instructions):
+            self._setup_uvw(config)
+            return
+        for inst in config.instructions:
+            assert inst.connection_mode == "uvu", "the fused convolution supports 'uvu', or 'uvw' with shared weights"
+        assert not config.shared_weights, "the fused convolution needs per-edge weights"
         self.internal = _native.ConvHandle(config, deterministic)
         # The forward pass needs no scratch (node-aligned segmented reduction).  The deterministic backward
         # pass takes optional scratch (one dX row per edge, capped); it is allocated on first use, per
         # device, and kept (the reference keeps its workspace on the object too: ConvolutionBase.py:93-99).
-        self.workspace_size = 0
-        self.workspace_ptr = 0
-        self._scratch = {}
         self.setup_torch_module()
 
     @staticmethod
     def name():
         return "LoopUnrollConv"
+
+    # ------------------------------------------------------------------ shared-weight 'uvw' convolution
+
+    def _setup_uvw(self, config):
+        from .tensor_product import TensorProduct
+        self.plan = UVWConvPlan(config)
+        self.edge_sum = _UnitWeightConv(self.plan.edge_sum, self.deterministic)
+        self.dense = TensorProduct(self.plan.dense, torch_op=True)
+        self.internal = self.edge_sum.internal
+        self._ones = {}
+        edge_sum, dense, conv = self.edge_sum, self.dense, self
+
+        def ones(ref, rows_n):
+            key = (ref.device, ref.dtype, rows_n)
+            if key not in conv._ones:
+                conv._ones = {key: torch.ones((rows_n, 1), dtype=ref.dtype, device=ref.device)}
+            return conv._ones[key]
+
+        def forward(L1_in, L2_in, weights, rows, cols, transpose_perm=None):
+            index = (rows, cols) if transpose_perm is None or not conv.deterministic else (rows, cols, transpose_perm)
+            s = edge_sum.forward(L1_in, L2_in, *index)
+            return dense.forward(s, ones(s, s.shape[0]), weights)
+
+        def backward_helper(L1_in, L2_in, weights, L3_grad, rows, cols, transpose_perm=None):
+            index = (rows, cols) if transpose_perm is None or not conv.deterministic else (rows, cols, transpose_perm)
+            s = edge_sum.forward(L1_in, L2_in, *index)
+            ds, _, dw = dense.backward_helper(s, ones(s, s.shape[0]), weights, L3_grad)
+            dx, dy = edge_sum.backward_helper(L1_in, L2_in, ds, *index)
+            return [dx, dy, dw]
+
+        self.forward = forward
+        self.backward_helper = backward_helper
+
+    def check_device_status(self):
+        self.internal.check()
+        if hasattr(self, "dense"):
+            self.dense.check_device_status()
 
     # ------------------------------------------------------------------ launches
 
@@ -271,8 +355,110 @@ class TensorProductConv(TensorProductBase):
         L2_grad[:] = dy.cpu().numpy()
         weights_grad[:] = dw.cpu().numpy()
 
-    def check_device_status(self):
-        self.internal.check()
+
+class _UnitWeightConv:
+    """The fused gather - product - scatter kernels with every weight 1 and no weight array (first stage of the
+    shared-weight "uvw" convolution): ``S = forward(X, Y, rows, cols[, sender_perm])``, first and second
+    derivatives with respect to X and Y as custom ops."""
+
+    def __init__(self, problem: TPProblem, deterministic: bool):
+        self.config, self.deterministic = problem, deterministic
+        self.L1, self.L2, self.L3 = problem.irreps_in1, problem.irreps_in2, problem.irreps_out
+        self.conv_id = next(_conv_ids)
+        self.internal = _native.ConvHandle(problem, deterministic, unit_weights=True)
+        self._scratch = None
+        self._setup_ops()
+
+    def _forward_impl(self, x, y, rows, cols, perm=None):
+        _require_cuda(x, y, rows, cols)
+        x, y, rows, cols = x.contiguous(), y.contiguous(), rows.contiguous(), cols.contiguous()
+        z = torch.empty((x.shape[0], self.L3.dim), dtype=x.dtype, device=x.device)
+        with torch.cuda.device(x.device):
+            self.internal.forward(x.shape[0], rows.shape[0], x.data_ptr(), y.data_ptr(), 0, rows.data_ptr(),
+                                  cols.data_ptr(), z.data_ptr(), 0, 0, torch.cuda.current_stream().cuda_stream)
+        return z
+
+    def _backward_impl(self, x, y, dz, rows, cols, perm=None):
+        _require_cuda(x, y, dz, rows, cols)
+        if self.deterministic and perm is None:
+            raise ValueError("the deterministic convolution needs sender_perm")
+        x, y, dz, rows, cols = x.contiguous(), y.contiguous(), dz.contiguous(), rows.contiguous(), cols.contiguous()
+        perm_ptr = perm.contiguous().data_ptr() if (perm is not None and self.deterministic) else 0
+        dx, dy = torch.empty_like(x), torch.empty_like(y)
+        with torch.cuda.device(x.device):
+            ws_ptr = ws_bytes = 0
+            want = self.internal.workspace_bytes(x.shape[0], rows.shape[0]) if self.deterministic else 0
+            if want:
+                if self._scratch is None or self._scratch.numel() < want or self._scratch.device != x.device:
+                    self._scratch = torch.empty(want, dtype=torch.uint8, device=x.device)
+                ws_ptr, ws_bytes = self._scratch.data_ptr(), self._scratch.numel()
+            self.internal.backward(x.shape[0], rows.shape[0], x.data_ptr(), y.data_ptr(), 0, dz.data_ptr(),
+                                   rows.data_ptr(), cols.data_ptr(), perm_ptr, dx.data_ptr(), dy.data_ptr(), 0,
+                                   ws_ptr, ws_bytes, torch.cuda.current_stream().cuda_stream)
+        return dx, dy
+
+    def _setup_ops(self):
+        conv = self
+        T = torch.Tensor
+        if self.deterministic:
+            @torch.library.custom_op(f"openequivariance_b200::conv_edge_sum{self.conv_id}", mutates_args=(),
+                                     device_types="cuda")
+            def forward(L1_in: T, L2_in: T, rows: T, cols: T, transpose_perm: T) -> T:
+                return conv._forward_impl(L1_in, L2_in, rows, cols, transpose_perm)
+
+            @torch.library.custom_op(f"openequivariance_b200::conv_edge_sum_backward{self.conv_id}", mutates_args=(),
+                                     device_types="cuda")
+            def backward_helper(L1_in: T, L2_in: T, L3_grad: T, rows: T, cols: T,
+                                transpose_perm: T) -> typing.List[T]:
+                return list(conv._backward_impl(L1_in, L2_in, L3_grad, rows, cols, transpose_perm))
+            n_index = 3
+        else:
+            @torch.library.custom_op(f"openequivariance_b200::conv_edge_sum{self.conv_id}", mutates_args=(),
+                                     device_types="cuda")
+            def forward(L1_in: T, L2_in: T, rows: T, cols: T) -> T:
+                return conv._forward_impl(L1_in, L2_in, rows, cols)
+
+            @torch.library.custom_op(f"openequivariance_b200::conv_edge_sum_backward{self.conv_id}", mutates_args=(),
+                                     device_types="cuda")
+            def backward_helper(L1_in: T, L2_in: T, L3_grad: T, rows: T, cols: T) -> typing.List[T]:
+                return list(conv._backward_impl(L1_in, L2_in, L3_grad, rows, cols))
+            n_index = 2
+
+        @forward.register_fake
+        def _(L1_in, L2_in, *index):
+            return L1_in.new_empty(L1_in.shape[0], conv.L3.dim)
+
+        @backward_helper.register_fake
+        def _(L1_in, L2_in, L3_grad, *index):
+            return [L1_in.new_empty(*L1_in.shape), L2_in.new_empty(*L2_in.shape)]
+
+        nones = (None,) * n_index
+
+        def setup_context(ctx, inputs, output):
+            ctx.L1_in, ctx.L2_in = inputs[:2]
+            ctx.index = inputs[2:]
+
+        def backward(ctx, grad_output):
+            gx, gy = backward_helper(ctx.L1_in, ctx.L2_in, grad_output, *ctx.index)
+            return (gx, gy) + nones
+
+        forward.register_autograd(backward, setup_context=setup_context)
+
+        def setup_context_double_backward(ctx, inputs, output):
+            ctx.L1_in, ctx.L2_in, ctx.L3_grad = inputs[:3]
+            ctx.index = inputs[3:]
+
+        def double_backward(ctx, grad_output):
+            # S is bilinear in (X, Y): d<ex,dX>+<ey,dY> / dX = dX(ey, dS), / dY = dY(ex, dS), / dS = S(ex, y) + S(x, ey)
+            x, y, ds, idx = ctx.L1_in, ctx.L2_in, ctx.L3_grad, ctx.index
+            ex, ey = grad_output[0], grad_output[1]
+            a = backward_helper(ex, ey, ds, *idx)
+            gs = forward(ex, y, *idx) + forward(x, ey, *idx)
+            return (a[0], a[1], gs) + nones
+
+        backward_helper.register_autograd(double_backward, setup_context=setup_context_double_backward)
+        self.forward = forward
+        self.backward_helper = backward_helper
 
 
 LoopUnrollConv = TensorProductConv

@@ -131,6 +131,7 @@ struct Problem {
     std::vector<Irrep> in1, in2, out;
     std::vector<Instr> instr;
     int dtype = 0, shared = 0, mode = 0;
+    int unit = 0;               // no weight array: every weight is 1 (shared_weights == 2 in the descriptor)
     int x_dim = 0, y_dim = 0, z_dim = 0, w_numel = 0;
     int elem() const { return dtype == OEQ_F64 ? 8 : 4; }
 };
@@ -153,7 +154,8 @@ int ingest(const oeq_problem_desc* d, Problem& p) {
     if (!d) return fail(OEQ_ERR_INVALID, "null problem descriptor");
     if (d->dtype != OEQ_F32 && d->dtype != OEQ_F64) return fail(OEQ_ERR_INVALID, "dtype must be OEQ_F32 or OEQ_F64");
     p.dtype = d->dtype;
-    p.shared = d->shared_weights ? 1 : 0;
+    p.unit = d->shared_weights == 2 ? 1 : 0;
+    p.shared = (d->shared_weights && !p.unit) ? 1 : 0;
     int rc;
     if ((rc = ingest_irreps(d->in1, d->n_in1, p.in1, p.x_dim, "irreps_in1"))) return rc;
     if ((rc = ingest_irreps(d->in2, d->n_in2, p.in2, p.y_dim, "irreps_in2"))) return rc;
@@ -279,7 +281,7 @@ int choose_mapping(const Problem& p, int kind, Mapping& m) {
     m.nch = (maxmul + m.mulg - 1) / m.mulg;
     const int e = p.elem();
     const int xb = pad16(p.x_dim * e), yb = pad16(p.y_dim * e), zb = pad16(p.z_dim * e);
-    const int wb = p.shared ? 0 : pad16(p.w_numel * e);
+    const int wb = (p.shared || p.unit) ? 0 : pad16(p.w_numel * e);
     m.sw_bytes = p.shared ? pad16(p.w_numel * e) : 0;
     m.stage_bytes = xb + yb + wb + (bwd ? zb : 0);
     int zpc = 0;
@@ -370,7 +372,7 @@ int choose_mapping(const Problem& p, int kind, Mapping& m) {
                 zmax = std::max(zmax, zb[q + 1] - zb[q]);
             }
             Mapping t = m;
-            t.stage_bytes = xb + yb + pad16(wmax * e) + pad16(zmax * e);
+            t.stage_bytes = xb + yb + (p.unit ? 0 : pad16(wmax * e)) + pad16(zmax * e);
             const int ng = groups_that_fit(t, best_ps);
             if (ng > best_ng) {
                 best_ng = ng;
@@ -434,7 +436,7 @@ int choose_mapping_recv(const Problem& p, Mapping& m) {
     m.nch = 1;
     m.ps = 1;
     const int e = p.elem();
-    const int xb = pad16(p.x_dim * e), yb = pad16(p.y_dim * e), wb = pad16(p.w_numel * e);
+    const int xb = pad16(p.x_dim * e), yb = pad16(p.y_dim * e), wb = p.unit ? 0 : pad16(p.w_numel * e);
     m.sw_bytes = 0;
     m.stage_bytes = xb + yb + wb;
     // dZ values per channel beyond the register budget are parked in shared memory (whole output irreps)
@@ -601,7 +603,7 @@ struct UvuTcGeometry {
 // multiplicity 1 and at most 32 components, widest multiplicity 65..128 (thread = channel, M = 128 rows),
 // at most 32 first-input components per channel (one swizzled 128-byte row) and 256 output columns.
 bool uvu_tc_geometry(const Problem& p, UvuTcGeometry& g, int npad = 0) {
-    if (p.mode != OEQ_MODE_UVU || p.shared || p.dtype != OEQ_F32) return false;
+    if (p.mode != OEQ_MODE_UVU || p.shared || p.unit || p.dtype != OEQ_F32) return false;
     // Opt-in: measured on B200 the per-edge hand-offs between the roles make this kernel about twice as slow
     // as the FMA kernel (MACE-large, 1.5 M edges: 14.0 ms against 7.2 ms), so the FMA kernel is the default.
     if (!env_int("OEQ_B200_UVU_TC", 0)) return false;
@@ -636,6 +638,7 @@ std::string descriptor_text(const Problem& p, const Mapping& m, const UvwConfig*
     s << "constexpr int X_DIM = " << p.x_dim << ", Y_DIM = " << p.y_dim << ", Z_DIM = " << p.z_dim
       << ", W_NUMEL = " << p.w_numel << ";\n";
     s << "constexpr bool SHARED_W = " << (p.shared ? "true" : "false") << ";\n";
+    s << "constexpr bool UNIT_W = " << (p.unit ? "true" : "false") << ";\n";
     s << "constexpr int N_IN1 = " << p.in1.size() << ", N_IN2 = " << p.in2.size() << ", N_OUT = " << p.out.size()
       << ", N_INSTR = " << p.instr.size() << ";\n";
     auto put_int = [](std::ostringstream& o, int v) { o << v; };
@@ -1113,7 +1116,7 @@ int launch_uvu(Kernel& k, const Problem& p, UvuParams& prm, cudaStream_t stream,
     int flags = 0;
     if ((p.x_dim * e) % 16 == 0 && aligned16(prm.X)) flags |= 1;
     if ((p.y_dim * e) % 16 == 0 && aligned16(prm.Y)) flags |= 2;
-    if (!p.shared && (p.w_numel * e) % 16 == 0 && aligned16(prm.W)) flags |= 4;
+    if (!p.shared && !p.unit && (p.w_numel * e) % 16 == 0 && aligned16(prm.W)) flags |= 4;
     const void* zlike = prm.dZ ? prm.dZ : prm.Z;
     if ((p.z_dim * e) % 16 == 0 && aligned16(zlike)) flags |= 8;
     if (env_int("OEQ_B200_NO_BULK", 0)) flags = 0;
@@ -1189,6 +1192,7 @@ int oeq_set_cache_dir(const char* path) {
 static int check_conv_problem(const Problem& p) {
     if (p.mode != OEQ_MODE_UVU) return fail(OEQ_ERR_UNSUPPORTED, "fused convolution supports 'uvu' problems only");
     if (p.shared) return fail(OEQ_ERR_UNSUPPORTED, "fused convolution needs per-edge weights (shared_weights=False)");
+    // (shared_weights == 2, "every weight is 1", is a per-edge-weight problem without the array)
     for (const Irrep& r : p.in2)
         if (r.mul != 1) return fail(OEQ_ERR_UNSUPPORTED, "fused convolution needs multiplicity 1 for every irrep of the second input");
     return OEQ_OK;
@@ -1680,7 +1684,7 @@ int oeq_conv_forward(oeq_conv* h, int64_t nodes, int64_t edges, const void* X, c
     if (edges == 0 || !h->deterministic)
         OEQ_CUDA(cudaMemsetAsync(Z, 0, (size_t)nodes * p.z_dim * p.elem(), st));
     if (edges == 0) return OEQ_OK;
-    if (!X || !Y || !W || !rows || !cols) return fail(OEQ_ERR_INVALID, "null buffer");
+    if (!X || !Y || (!W && !p.unit) || !rows || !cols) return fail(OEQ_ERR_INVALID, "null buffer");
     // the tensor-core kernel stages rows with bulk copies only: it needs 16-byte aligned X and W
     const bool tc = h->has_fwd_tc && aligned16(X) && aligned16(W) && !env_int("OEQ_B200_NO_BULK", 0);
     int rc = ensure_status(&h->d_status);
@@ -1726,7 +1730,8 @@ int oeq_conv_backward(oeq_conv* h, int64_t nodes, int64_t edges, const void* X, 
     if (edges == 0 || !h->deterministic)
         OEQ_CUDA(cudaMemsetAsync(dX, 0, (size_t)nodes * p.x_dim * p.elem(), st));
     if (edges == 0) return OEQ_OK;
-    if (!X || !Y || !W || !dZ || !rows || !cols || !dY || !dW) return fail(OEQ_ERR_INVALID, "null buffer");
+    if (!X || !Y || !dZ || !rows || !cols || !dY || ((!W || !dW) && !p.unit))
+        return fail(OEQ_ERR_INVALID, "null buffer");
     if (h->deterministic && !perm)
         return fail(OEQ_ERR_INVALID, "deterministic backward needs the sender-order permutation");
     int rc = ensure_status(&h->d_status);

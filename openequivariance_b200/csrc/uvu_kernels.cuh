@@ -92,7 +92,9 @@ constexpr int DY_RING = 5;   // per-item dY partials in flight; stages are cappe
 __host__ __device__ constexpr int pad16(int bytes) { return (bytes + 15) / 16 * 16; }
 constexpr int ELEM = sizeof(T);
 constexpr int XB = pad16(X_DIM * ELEM), YB = pad16(Y_DIM * ELEM), ZB = pad16(Z_DIM * ELEM);
-constexpr int WB = SHARED_W ? 0 : pad16(W_NUMEL * ELEM);
+// UNIT_W (descriptor): the problem has no weight array, every weight is 1 (the product summed per receiver
+// before a shared dense contraction): nothing is staged for W and no weight gradient is written.
+constexpr int WB = (SHARED_W || UNIT_W) ? 0 : pad16(W_NUMEL * ELEM);
 constexpr int SWB = SHARED_W ? pad16(W_NUMEL * ELEM) : 0;
 
 // Backward staging in phases: with NPH > 1 an edge is staged as NPH items.  Phase q carries the weights
@@ -106,7 +108,7 @@ constexpr int max_phase_width(const int* begin) {
     for (int q = 0; q < NPH; ++q) m = imax(m, begin[q + 1] - begin[q]);
     return m;
 }
-constexpr int WPHB = SHARED_W ? 0 : pad16(max_phase_width(W_PH_BEGIN) * ELEM);
+constexpr int WPHB = (SHARED_W || UNIT_W) ? 0 : pad16(max_phase_width(W_PH_BEGIN) * ELEM);
 constexpr int ZPHB = pad16(max_phase_width(Z_PH_BEGIN) * ELEM);
 
 template <bool BWD>
@@ -424,7 +426,7 @@ __device__ __forceinline__ void issue_item(const UvuParams& p, const SMT& sm, in
     // weights and output gradient: the whole row, or this phase's part of it
     const int w_lo = BWD ? W_PH_BEGIN_DEV[ph] : 0, w_n = BWD ? W_PH_BEGIN_DEV[ph + 1] - w_lo : W_NUMEL;
     const int z_lo = BWD ? Z_PH_BEGIN_DEV[ph] : 0, z_n = BWD ? Z_PH_BEGIN_DEV[ph + 1] - z_lo : Z_DIM;
-    const T* wsrc = SHARED_W ? nullptr : p.W + e * (long long)W_NUMEL + w_lo;
+    const T* wsrc = (SHARED_W || UNIT_W) ? nullptr : p.W + e * (long long)W_NUMEL + w_lo;
     const T* zsrc = BWD ? p.dZ + r * (long long)Z_DIM + z_lo : nullptr;
     const unsigned wbytes = (unsigned)pad16(w_n * ELEM), zbytes = (unsigned)pad16(z_n * ELEM);
     if (lane == 0) {
@@ -453,11 +455,11 @@ __device__ __forceinline__ void issue_item(const UvuParams& p, const SMT& sm, in
             if (yb && first) bulk_g2s_hint(st + L::OFF_Y, ysrc, YB, full, stream);
         }
     }
-    const bool any_elem = !xb || !yb || (!wb && !SHARED_W) || (BWD && !zb);
+    const bool any_elem = !xb || !yb || (!wb && !SHARED_W && !UNIT_W) || (BWD && !zb);
     if (any_elem) {
         if (!xb && first) for (int i = lane; i < X_DIM; i += 32) cp_async_elem<ELEM>((T*)(st + L::OFF_X) + i, xsrc + i);
         if (!yb && first) for (int i = lane; i < Y_DIM; i += 32) cp_async_elem<ELEM>((T*)(st + L::OFF_Y) + i, ysrc + i);
-        if constexpr (!SHARED_W) {
+        if constexpr (!SHARED_W && !UNIT_W) {
             if (!wb) for (int i = lane; i < w_n; i += 32) cp_async_elem<ELEM>((T*)(st + L::OFF_W) + i, wsrc + i);
         }
         if constexpr (BWD) {
@@ -589,7 +591,7 @@ __device__ __forceinline__ void forward_item(const T* __restrict__ sX, const T* 
                                 for (int j = 0; j < D2; ++j) y[j] = sY[IN2_OFF[b] + j];
                                 cg_forward<P>(x, y, t);
                             }
-                            const T w = sWt[weight_offset<P>(u, 0)];
+                            const T w = UNIT_W ? (T)1 : sWt[weight_offset<P>(u, 0)];
 #pragma unroll
                             for (int k = 0; k < D3; ++k)
                                 zacc[C * ZPC_MAX + ZR_OFF[o] + k] = fma(w, t[k], zacc[C * ZPC_MAX + ZR_OFF[o] + k]);
@@ -603,7 +605,7 @@ __device__ __forceinline__ void forward_item(const T* __restrict__ sX, const T* 
 #pragma unroll
                                 for (int k = 0; k < D3; ++k) t[k] = (T)0;
                                 cg_forward<P>(x, y, t);
-                                const T w = sWt[weight_offset<P>(u, v)];
+                                const T w = UNIT_W ? (T)1 : sWt[weight_offset<P>(u, v)];
 #pragma unroll
                                 for (int k = 0; k < D3; ++k)
                                     zacc[C * ZPC_MAX + ZR_OFF[o] + k] = fma(w, t[k], zacc[C * ZPC_MAX + ZR_OFF[o] + k]);
@@ -833,7 +835,7 @@ __device__ __forceinline__ void backward_item(const XR& xr, const YR& yr, const 
                 for (int i = 0; i < D1; ++i) av[i] = (T)0;
 #pragma unroll
                 for (int j = 0; j < D2; ++j) bv[j] = (T)0;
-                const T w = live ? sWt[weight_offset<P>(u, 0) - WBASE] : (T)0;
+                const T w = live ? (UNIT_W ? (T)1 : sWt[weight_offset<P>(u, 0) - WBASE]) : (T)0;
                 if constexpr (Y_IN_REGS) {
                     cg_backward<P>(x, &yr[IN2_OFF[b]], gz, av, bv);
                 } else {
@@ -850,7 +852,7 @@ __device__ __forceinline__ void backward_item(const XR& xr, const YR& yr, const 
                 }
                 if (live) {
                     if constexpr (SHARED_W) dwrow[weight_offset<P>(u, 0)] += tw;
-                    else __stcs(dwrow + weight_offset<P>(u, 0), tw);   // written once, never re-read here
+                    else if constexpr (!UNIT_W) __stcs(dwrow + weight_offset<P>(u, 0), tw);   // written once, never re-read here
                 }
                 if constexpr (Y_IN_REGS) {
 #pragma unroll
@@ -870,7 +872,7 @@ __device__ __forceinline__ void backward_item(const XR& xr, const YR& yr, const 
                     for (int j = 0; j < D2; ++j) { y[j] = sY[IN2_OFF[b] + v * D2 + j]; bv[j] = (T)0; }
 #pragma unroll
                     for (int i = 0; i < D1; ++i) av[i] = (T)0;
-                    const T w = live ? sWt[weight_offset<P>(u, v) - WBASE] : (T)0;
+                    const T w = live ? (UNIT_W ? (T)1 : sWt[weight_offset<P>(u, v) - WBASE]) : (T)0;
                     cg_backward<P>(x, y, gz, av, bv);
                     T tw = (T)0;
 #pragma unroll
@@ -880,7 +882,7 @@ __device__ __forceinline__ void backward_item(const XR& xr, const YR& yr, const 
                     }
                     if (live) {
                         if constexpr (SHARED_W) dwrow[weight_offset<P>(u, v)] += tw;
-                        else __stcs(dwrow + weight_offset<P>(u, v), tw);
+                        else if constexpr (!UNIT_W) __stcs(dwrow + weight_offset<P>(u, v), tw);
                     }
                     // reduce this (instruction, v) over the warp's channels; lane 0 owns the warp's slot
 #pragma unroll
@@ -1284,7 +1286,7 @@ __device__ void run_backward_recv(const UvuParams& p, const Smem<true, MODE, tru
                     for (int i = 0; i < D1; ++i) av[i] = (T)0;
 #pragma unroll
                     for (int j = 0; j < D2; ++j) bv[j] = (T)0;
-                    const T w = live ? sWt[weight_offset<P>(u, 0)] : (T)0;
+                    const T w = live ? (UNIT_W ? (T)1 : sWt[weight_offset<P>(u, 0)]) : (T)0;
                     if constexpr (out_reg_off(o) < GZ_REGS) {
                         cg_backward<P>(x, &yr[IN2_OFF[b]], &gz[out_reg_off(o)], av, bv);
                     } else {
@@ -1300,7 +1302,9 @@ __device__ void run_backward_recv(const UvuParams& p, const Smem<true, MODE, tru
                         tw = fma(x[i], av[i], tw);
                         dxa[i] = fma(w, av[i], dxa[i]);
                     }
-                    if (live) __stcs(dwrow + weight_offset<P>(u, 0), tw);
+                    if constexpr (!UNIT_W) {
+                        if (live) __stcs(dwrow + weight_offset<P>(u, 0), tw);
+                    }
 #pragma unroll
                     for (int j = 0; j < D2; ++j) dyreg[IN2_OFF[b] + j] = fma(w, bv[j], dyreg[IN2_OFF[b] + j]);
                 }
@@ -1446,7 +1450,7 @@ __device__ __forceinline__ void uvu_body_recv(const UvuParams& p) {
     Smem<true, MODE, true> sm(smem_raw, p.stages);
     const int tid = threadIdx.x;
     if (tid == 0) {
-        const bool any_elem = !(p.flags & 1) || !(p.flags & 2) || !(p.flags & 4);
+        const bool any_elem = !(p.flags & 1) || !(p.flags & 2) || (!(p.flags & 4) && !UNIT_W);
         for (int g = 0; g < NG; ++g) {
             for (int s = 0; s < p.stages; ++s) {
                 mbar_init(sm.full(g, s), 1 + (any_elem ? 32 : 0));
@@ -1482,7 +1486,7 @@ __device__ __forceinline__ void uvu_body(const UvuParams& p) {
     const int tid = threadIdx.x;
 
     if (tid == 0) {
-        const bool any_elem = !(p.flags & 1) || !(p.flags & 2) || (!(p.flags & 4) && !SHARED_W) || (BWD && !(p.flags & 8));
+        const bool any_elem = !(p.flags & 1) || !(p.flags & 2) || (!(p.flags & 4) && !SHARED_W && !UNIT_W) || (BWD && !(p.flags & 8));
         for (int g = 0; g < NG; ++g) {
             for (int s = 0; s < p.stages; ++s) {
                 mbar_init(sm.full(g, s), 1 + (any_elem ? 32 : 0));
