@@ -434,6 +434,49 @@ def conv_case(torch, args, spec, workload, device, variant, numbering, nodes=Non
     return res
 
 
+def second_derivative_case(torch, device, steps=10, warmup=3, batch=50_000):
+    """Second derivatives of the batch 'uvu' product (MACE irreps, 50 000 rows): the one-pass kernel against the
+    composition of four backward and three forward launches that the reference uses."""
+    import openequivariance_b200 as oeq
+    p = oeq.ChannelwiseTPP("128x0e+128x1o+128x2e", "1x0e+1x1o+1x2e+1x3o", "128x0e+128x1o+128x2e")
+    tp = oeq.TensorProduct(p, torch_op=True)
+    gen = torch.Generator(device=device).manual_seed(3)
+    mk = lambda n: torch.randn(batch, n, device=device, generator=gen)
+    x, y, w, dz = mk(p.irreps_in1.dim), mk(p.irreps_in2.dim), mk(p.weight_numel), mk(p.irreps_out.dim)
+    ex, ey, ew = mk(p.irreps_in1.dim), mk(p.irreps_in2.dim), mk(p.weight_numel)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+
+    def composed():
+        a = tp.backward_helper(ex, ey, w, dz)
+        b = tp.backward_helper(x, y, ew, dz)
+        c = tp.backward_helper(ex, y, w, dz)
+        d = tp.backward_helper(x, ey, w, dz)
+        gz = tp(ex, y, w) + tp(x, ey, w) + tp(x, y, ew)
+        return a[0] + b[0], a[1] + b[1], c[2] + d[2], gz
+
+    def timed(fn):
+        ts = []
+        for i in range(warmup + steps):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            if i >= warmup:
+                ts.append(a.elapsed_time(b))
+        return statistics.median(ts)
+
+    fused = timed(lambda: tp._double_backward_impl(x, y, w, dz, ex, ey, ew))
+    comp = timed(composed)
+    tp.check_device_status()
+    xd, yd, zd, wn = p.irreps_in1.dim, p.irreps_in2.dim, p.irreps_out.dim, p.weight_numel
+    bytes_ = batch * (3 * xd + 3 * yd + 3 * wn + 2 * zd) * 4          # seven arrays in, four out
+    peak, _ = measured_peak()
+    return {"one_pass_ms": fused, "composed_ms": comp, "rows_per_s": batch / (fused * 1e-3),
+            "hbm_frac_one_pass": bytes_ / (fused * 1e-3) / 1e9 / peak, "algorithmic_bytes": bytes_}
+
+
 def uvw_conv_case(torch, args, device, nodes=20_000, degree=40.0, steps=5, warmup=3):
     """Shared-weight 'uvw' convolution (64x(0e+1o+2e), harmonics to l=2) on a Nequip-sized graph: the unit-weight
     edge sum over the edges, then the dense contraction over the nodes; forward and backward (all gradients)."""
@@ -486,6 +529,7 @@ def secondary_block(torch, args, device, peaks):
         out[f"conv_nequip_{variant}"] = conv_case(torch, args, WORKLOADS["nequip"], "nequip", device, variant, "morton")
     out["conv_mace_large_atomic_20k_nodes"] = conv_case(torch, args, WORKLOADS["mace_large"], "mace_large", device,
                                                         "atomic", "morton", nodes=20_000)
+    out["batch_uvu_mace_50k_second_derivatives"] = second_derivative_case(torch, device)
     out["conv_uvw_fc64_shared_20k_nodes"] = uvw_conv_case(torch, args, device)
     for dt, pk in (("f32", peaks["tf32_tflops"]), ("f64", peaks["fp64_tflops"])):
         r = bench_tp.measure("uvw_fc", dt, steps=10, warmup=3)

@@ -130,6 +130,17 @@ int oeq_tp_backward(oeq_tp* h, int64_t batch, const void* X, const void* Y, cons
 int oeq_tp_backward_noalloc(oeq_tp* h, int64_t batch, const void* X, const void* Y, const void* W, const void* dZ,
                             void* dX, void* dY, void* dW, void* stream);
 
+/* Second derivatives in one pass.  With dX, dY, dW the results of oeq_tp_backward for (X, Y, W, dZ), this gives the
+ * gradient of <EX, dX> + <EY, dY> + <EW, dW> with respect to X, Y, W and dZ (GX, GY, GW, GdZ; every element written).
+ * The reference composes this from four backward and three forward launches
+ * (openequivariance/implementations/TensorProductBase.py:284-296); this entry point reads a row's seven arrays once.
+ * Available for 'uvu' problems with per-row weights and a second input of multiplicity 1 whose rows fit two
+ * shared-memory stages (oeq_tp_has_double_backward); otherwise OEQ_ERR_UNSUPPORTED, and the caller composes it. */
+int oeq_tp_has_double_backward(const oeq_tp* h);
+int oeq_tp_double_backward(oeq_tp* h, int64_t batch, const void* X, const void* Y, const void* W, const void* dZ,
+                           const void* EX, const void* EY, const void* EW, void* GX, void* GY, void* GW, void* GdZ,
+                           void* stream);
+
 /* Reads the handle's device status word (synchronises the stream it last ran on):
  * OEQ_OK, or OEQ_ERR_DEVICE_WAIT if a kernel abandoned a bounded wait. */
 int oeq_tp_check(oeq_tp* h);

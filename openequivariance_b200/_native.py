@@ -63,6 +63,8 @@ SYMBOLS = {
     "oeq_tp_workspace_bytes": (_SZ, [_P, _I64]),
     "oeq_tp_backward": (_INT, [_P, _I64, _P, _P, _P, _P, _P, _P, _P, _P, _SZ, _P]),
     "oeq_tp_backward_noalloc": (_INT, [_P, _I64, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "oeq_tp_has_double_backward": (_INT, [_P]),
+    "oeq_tp_double_backward": (_INT, [_P, _I64, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "oeq_tp_check": (_INT, [_P]),
     "oeq_conv_create": (_INT, [C.POINTER(_ProblemDesc), _INT, C.POINTER(_P)]),
     "oeq_conv_destroy": (_INT, [_P]),
@@ -192,6 +194,12 @@ class TPHandle(_Handle):
 
     def backward(self, batch, x, y, w, dz, dx, dy, dw, ws, ws_bytes, stream):
         check(lib().oeq_tp_backward(self.ptr, batch, x, y, w, dz, dx, dy, dw, ws, ws_bytes, stream))
+
+    def has_double_backward(self):
+        return bool(lib().oeq_tp_has_double_backward(self.ptr))
+
+    def double_backward(self, batch, x, y, w, dz, ex, ey, ew, gx, gy, gw, gdz, stream):
+        check(lib().oeq_tp_double_backward(self.ptr, batch, x, y, w, dz, ex, ey, ew, gx, gy, gw, gdz, stream))
 
     def check(self):
         check(lib().oeq_tp_check(self.ptr))

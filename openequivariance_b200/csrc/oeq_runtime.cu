@@ -853,6 +853,55 @@ int build_uvu(const Problem& p, int kind, Kernel& k) {
     return OEQ_OK;
 }
 
+// One-pass second derivatives of the batch 'uvu' product (uvu_kernels.cuh, run_double_backward): per-row
+// weights, second input of multiplicity 1 with at most 32 components, at most 256 channels; a row's seven
+// arrays form one stage.
+constexpr int K_DBL_BATCH = 8;
+
+bool double_backward_supported(const Problem& p) {
+    if (p.mode != OEQ_MODE_UVU || p.shared || p.unit || p.y_dim > 32) return false;
+    for (const Irrep& r : p.in2)
+        if (r.mul != 1) return false;
+    int maxmul = 1, zpc = 0, d1max = 1;
+    for (const Instr& t : p.instr) maxmul = std::max(maxmul, p.in1[t.i1].mul);
+    for (const Irrep& r : p.out) { maxmul = std::max(maxmul, r.mul); zpc += r.dim; }
+    for (const Irrep& r : p.in1) d1max = std::max(d1max, r.dim);
+    if (maxmul > 256) return false;
+    if ((zpc + 3 * p.y_dim + 5 * d1max) * (p.elem() / 4) + 40 > 232) return false;   // registers per thread
+    return env_int("OEQ_B200_FUSED_DOUBLE_BACKWARD", 1) != 0;
+}
+
+int build_uvu_dbl(const Problem& p, Kernel& k) {
+    Mapping& m = k.map;
+    int maxmul = 1;
+    for (const Instr& t : p.instr) maxmul = std::max(maxmul, p.in1[t.i1].mul);
+    for (const Irrep& r : p.out) maxmul = std::max(maxmul, r.mul);
+    m.mulg = (maxmul + 31) / 32 * 32;
+    m.nch = 1; m.ps = 1; m.producer = 1;
+    const int e = p.elem();
+    const int xb = pad16(p.x_dim * e), yb = pad16(p.y_dim * e), wb = pad16(p.w_numel * e), zb = pad16(p.z_dim * e);
+    m.sw_bytes = 0;
+    m.stage_bytes = 2 * xb + 2 * yb + 2 * wb + zb;
+    m.extra_bytes = 5 * (m.mulg / 32) * yb;
+    m.nph = 1;
+    m.z_ph_begin = {0, p.z_dim};
+    m.w_ph_begin = {0, p.w_numel};
+    m.phase_of_instr.assign(p.instr.size(), 0);
+    m.ng = 0;
+    for (int cand = std::max(1, std::min(4, 256 / m.mulg)); cand >= 1 && !m.ng; --cand) {
+        m.ng = cand;
+        if (m.smem(2) > SMEM_LIMIT) m.ng = 0;
+    }
+    if (!m.ng) return fail(OEQ_ERR_UNSUPPORTED, "a row's seven arrays do not fit two shared-memory stages");
+    const int stages = std::min(m.max_stages(), 4);
+    m.min_ctas = std::max(1, std::min({stages >= 2 ? SMEM_LIMIT / (m.smem(stages) + 1024) : 1, 2048 / m.threads(), 2}));
+    assign_partitions(p, true, m);
+    int rc = compile_kernel(descriptor_text(p, m), "uvu_kernels.cuh", K_DBL_BATCH, k.code);
+    if (rc) return rc;
+    k.compiled = true;
+    return OEQ_OK;
+}
+
 int build_uvu_recv(const Problem& p, bool deterministic, Kernel& k) {
     int rc = choose_mapping_recv(p, k.map);
     if (rc) return rc;
@@ -1106,12 +1155,13 @@ struct UvuParams {
     const long long* sum_cols; const long long* sum_perm; const void* sum_ws;
     long long sum_items, sum_e_lo, sum_e_hi;
     int sum_first, sum_chunk;
+    const void* EX; const void* EY; const void* EW;
 };
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 int launch_uvu(Kernel& k, const Problem& p, UvuParams& prm, cudaStream_t stream, int extra_flags = 0,
-               long long max_ctas = 0, long long* ctas_out = nullptr) {
+               long long max_ctas = 0, long long* ctas_out = nullptr, int clear_flags = 0) {
     const int e = p.elem();
     int flags = 0;
     if ((p.x_dim * e) % 16 == 0 && aligned16(prm.X)) flags |= 1;
@@ -1120,7 +1170,7 @@ int launch_uvu(Kernel& k, const Problem& p, UvuParams& prm, cudaStream_t stream,
     const void* zlike = prm.dZ ? prm.dZ : prm.Z;
     if ((p.z_dim * e) % 16 == 0 && aligned16(zlike)) flags |= 8;
     if (env_int("OEQ_B200_NO_BULK", 0)) flags = 0;
-    prm.flags = flags | extra_flags;
+    prm.flags = (flags & ~clear_flags) | extra_flags;
     prm.stages = k.stages;
     prm.chunk = std::max(1, env_int("OEQ_B200_CHUNK", 128));
     long long want = (prm.n_items + k.map.ng - 1) / k.map.ng;
@@ -1150,6 +1200,8 @@ struct oeq_tp {
     Kernel bwd_dw_tc;           // tensor-core weight gradient of the same class of problems
     Kernel bwd_dxy_tc;          // tensor-core dX / dY of the same class of problems (when its tiles fit)
     bool has_bwd_tc = false, has_dxy_tc = false;
+    Kernel dbl;                 // one-pass second derivatives ('uvu', per-row weights)
+    bool has_dbl = false;
     TcBwdGeometry tc_bwd;
     void* d_packed_t = nullptr; // weights transposed, split and swizzled for the dX/dY kernel
     cudaKernel_t pack_t_fn = nullptr;
@@ -1222,6 +1274,11 @@ int oeq_precompile(const oeq_problem_desc* desc, int kinds) {
     };
     if (kinds & 1) {
         if ((rc = one(K_FWD_BATCH)) || (rc = one(K_BWD_BATCH))) return rc;
+        if (double_backward_supported(p)) {
+            Kernel k;
+            rc = build_uvu_dbl(p, k);
+            if (rc && rc != OEQ_ERR_UNSUPPORTED) return rc;
+        }
     }
     if (kinds & 6) {
         if ((rc = check_conv_problem(p))) return rc;
@@ -1265,6 +1322,11 @@ int oeq_tp_create(const oeq_problem_desc* desc, oeq_tp** out) {
             h->has_dxy_tc = rc == OEQ_OK;
         }
     }
+    if (!rc && double_backward_supported(h->prob)) {
+        const int rc2 = build_uvu_dbl(h->prob, h->dbl);
+        if (rc2 == OEQ_OK) h->has_dbl = true;
+        else if (rc2 != OEQ_ERR_UNSUPPORTED) rc = rc2;
+    }
     if (rc) {
         delete h;
         return rc;
@@ -1278,7 +1340,7 @@ int oeq_tp_destroy(oeq_tp* h) {
     if (h->d_status) cudaFree(h->d_status);
     if (h->d_packed) cudaFree(h->d_packed);
     if (h->d_packed_t) cudaFree(h->d_packed_t);
-    for (Kernel* k : {&h->fwd, &h->bwd, &h->fwd_tc, &h->bwd_dw_tc, &h->bwd_dxy_tc})
+    for (Kernel* k : {&h->fwd, &h->bwd, &h->fwd_tc, &h->bwd_dw_tc, &h->bwd_dxy_tc, &h->dbl})
         if (k->lib) cudaLibraryUnload(k->lib);
     delete h;
     return OEQ_OK;
@@ -1502,6 +1564,37 @@ int oeq_tp_backward(oeq_tp* h, int64_t batch, const void* X, const void* Y, cons
         OEQ_CUDA(cudaLaunchKernel((const void*)h->bwd.reduce_fn, dim3((n + 127) / 128), dim3(128), args, 0, st));
     }
     return OEQ_OK;
+}
+
+int oeq_tp_has_double_backward(const oeq_tp* h) { return h && h->has_dbl ? 1 : 0; }
+
+int oeq_tp_double_backward(oeq_tp* h, int64_t batch, const void* X, const void* Y, const void* W, const void* dZ,
+                           const void* EX, const void* EY, const void* EW, void* GX, void* GY, void* GW, void* GdZ,
+                           void* stream) {
+    if (!h) return fail(OEQ_ERR_INVALID, "null handle");
+    if (!h->has_dbl) return fail(OEQ_ERR_UNSUPPORTED, "no one-pass second-derivative kernel for this problem: compose it from "
+                                                      "oeq_tp_forward and oeq_tp_backward");
+    if (batch < 0) return fail(OEQ_ERR_INVALID, "negative batch");
+    if (batch == 0) return OEQ_OK;
+    if (!X || !Y || !W || !dZ || !EX || !EY || !EW || !GX || !GY || !GW || !GdZ) return fail(OEQ_ERR_INVALID, "null buffer");
+    int rc = ensure_status(&h->d_status);
+    if (!rc) rc = load_kernel(h->dbl, "oeq_uvu_kernel", false);
+    if (rc) return rc;
+    const Problem& p = h->prob;
+    const int e = p.elem();
+    UvuParams prm{};
+    prm.X = X; prm.Y = Y; prm.W = W; prm.dZ = dZ; prm.EX = EX; prm.EY = EY; prm.EW = EW;
+    prm.dX = GX; prm.dY = GY; prm.dW = GW; prm.Z = GdZ;
+    prm.n_items = batch; prm.n_nodes = batch; prm.status = h->d_status;
+    h->last_stream = (cudaStream_t)stream;
+    // launch_uvu derives the bulk-copy bits from X, Y, W, dZ; a cotangent that breaks the 16-byte rule clears
+    // the bit of its pair
+    int clear = 0;
+    if (!aligned16(EX)) clear |= 1;
+    if (!aligned16(EY)) clear |= 2;
+    if (!aligned16(EW)) clear |= 4;
+    (void)e;
+    return launch_uvu(h->dbl, p, prm, (cudaStream_t)stream, 0, 0, nullptr, clear);
 }
 
 static int check_status(int* d_status, cudaStream_t st) {

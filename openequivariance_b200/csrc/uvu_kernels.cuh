@@ -65,6 +65,10 @@ struct UvuParams {
     const T* sum_ws;
     long long sum_items, sum_e_lo, sum_e_hi;
     int sum_first, sum_chunk;
+    // second derivatives (batch product): the cotangents of dX, dY, dW
+    const T* EX;
+    const T* EY;
+    const T* EW;
 };
 
 constexpr int MODE_BATCH = 0;
@@ -1477,6 +1481,244 @@ __device__ __forceinline__ void uvu_body_recv(const UvuParams& p) {
     run_backward_recv<MODE>(p, sm, tid / G, tid % G);
 }
 
+// ---------------------------------------------------------------- second derivatives, batch product, one pass
+//
+// With Z = T(x, y, w) trilinear and the first derivatives dX, dY, dW taken against dZ, the gradient of
+// <ex, dX> + <ey, dY> + <ew, dW> with respect to (x, y, w, dZ) is
+//   gx = dX(ey, w) + dX(y, ew),  gy = dY(ex, w) + dY(x, ew),  gw = dW(ex, y) + dW(x, ey),
+//   gdz = T(ex, y, w) + T(x, ey, w) + T(x, y, ew)
+// which the reference (and this library's general path) evaluates with four backward and three forward launches
+// (reference: openequivariance/implementations/TensorProductBase.py:284-296).  All seven terms share the row's
+// x, y, w, dZ and the products P_ij = sum_k C_ijk dZ_k, so this kernel loads a row's seven arrays once and emits
+// the four results: per instruction and (i, j) pair
+//   q_j = w ey_j + ew y_j,  r_i = w ex_i + ew x_i
+//   gx_i += q_j P_ij,  gy_j += r_i P_ij,  gw += (ex_i y_j + x_i ey_j) P_ij,
+//   gdz_k += C_ijk (r_i y_j + w x_i ey_j)
+// 7 FMAs per pair and 2 per coefficient, against 4 x (3 per pair + 1 per coefficient) + 3 x (1 + 1) composed.
+// One thread per channel, per-row weights, second input of multiplicity 1 kept in registers.
+
+struct DblLayout {
+    static constexpr int OFF_X = 0;
+    static constexpr int OFF_EX = OFF_X + XB;
+    static constexpr int OFF_Y = OFF_EX + XB;
+    static constexpr int OFF_EY = OFF_Y + YB;
+    static constexpr int OFF_W = OFF_EY + YB;
+    static constexpr int OFF_EW = OFF_W + WB;
+    static constexpr int OFF_DZ = OFF_EW + WB;
+    static constexpr int BYTES = OFF_DZ + ZB;
+};
+
+struct DblSmem {
+    using L = DblLayout;
+    static constexpr int DYSLOT = DY_RING * WARPS_PER_GROUP * YB;
+    static constexpr int EXTRA = DYSLOT;
+    static constexpr int CTRL = 128;
+    unsigned char* base;
+    int stages;
+    __device__ DblSmem(unsigned char* b, int s) : base(b), stages(s) {}
+    __device__ unsigned long long* full(int g, int s) const { return reinterpret_cast<unsigned long long*>(base) + (g * stages + s) * 2; }
+    __device__ unsigned long long* empty(int g, int s) const { return full(g, s) + 1; }
+    __device__ long long* hdr(int g, int s) const { return reinterpret_cast<long long*>(base + NG * stages * 16) + (g * stages + s) * 4; }
+    __device__ long long* total(int g) const { return reinterpret_cast<long long*>(base + NG * stages * 48 + g * CTRL); }
+    __device__ unsigned char* group_base(int g) const { return base + NG * stages * 48 + NG * CTRL + (long long)g * (stages * L::BYTES + EXTRA); }
+    __device__ unsigned char* stage(int g, int s) const { return group_base(g) + s * L::BYTES; }
+    __device__ unsigned char* extra(int g) const { return group_base(g) + stages * L::BYTES; }
+};
+
+// Staging warp of group g: rows gid, gid + groups, ... ; seven copies per row on the stage's barrier.
+template <int INSTANCE>     // templates: compiled only in the translation unit that asks for this kernel
+__device__ void run_producer_dbl(const UvuParams& p, const DblSmem& sm, int g, int lane) {
+    using L = DblLayout;
+    const int S = sm.stages;
+    const long long groups = (long long)gridDim.x * NG, gid = (long long)blockIdx.x * NG + g;
+    volatile long long* total = sm.total(g);
+    long long it = 0;
+    bool ok = true;
+    // per array: a bulk copy when it meets the 16-byte rule (flags bit 0 X and EX, 1 Y and EY, 2 W and EW, 3 dZ),
+    // element copies by the whole warp otherwise
+    const int bit[7] = {1, 1, 2, 2, 4, 4, 8};
+    const bool any_elem = (p.flags & 15) != 15;
+    for (long long row = gid; row < p.n_items && ok; row += groups, ++it) {
+        const int stage = (int)(it % S);
+        if (it >= S) ok = mbar_wait(sm.empty(g, stage), (unsigned)(((it / S) - 1) & 1), p.status, ERR_WAIT_EMPTY);
+        if (!ok) break;
+        unsigned char* st = sm.stage(g, stage);
+        unsigned long long* full = sm.full(g, stage);
+        const T* src[7] = {p.X + row * X_DIM, p.EX + row * X_DIM, p.Y + row * Y_DIM, p.EY + row * Y_DIM,
+                           p.W + row * (long long)W_NUMEL, p.EW + row * (long long)W_NUMEL, p.dZ + row * (long long)Z_DIM};
+        const int off[7] = {L::OFF_X, L::OFF_EX, L::OFF_Y, L::OFF_EY, L::OFF_W, L::OFF_EW, L::OFF_DZ};
+        const int len[7] = {X_DIM, X_DIM, Y_DIM, Y_DIM, W_NUMEL, W_NUMEL, Z_DIM};
+        if (lane == 0) {
+            sm.hdr(g, stage)[0] = row;
+            unsigned bytes = 0;
+#pragma unroll
+            for (int a = 0; a < 7; ++a)
+                if (p.flags & bit[a]) bytes += (unsigned)pad16(len[a] * ELEM);
+            mbar_arrive_expect_tx(full, bytes);
+#pragma unroll
+            for (int a = 0; a < 7; ++a)
+                if (p.flags & bit[a]) bulk_g2s(st + off[a], src[a], (unsigned)pad16(len[a] * ELEM), full);
+        }
+        if (any_elem) {
+#pragma unroll
+            for (int a = 0; a < 7; ++a)
+                if (!(p.flags & bit[a]))
+                    for (int i = lane; i < len[a]; i += 32) cp_async_elem<ELEM>((T*)(st + off[a]) + i, src[a] + i);
+            cp_async_arrive_noinc(full);
+        }
+    }
+    if (lane == 0) *total = it;
+    asm volatile("cp.async.wait_all;" ::: "memory");
+}
+
+template <int INSTANCE>
+__device__ void run_double_backward(const UvuParams& p, const DblSmem& sm, int g, int tg) {
+    using L = DblLayout;
+    static_assert(PS == 1 && NCH == 1 && Y_IN_REGS && !SHARED_W && !UNIT_W && PRODUCER, "one thread per channel");
+    const int S = sm.stages;
+    const int u = tg, lane = tg & 31, warp = tg >> 5;
+    const int bar_id = 1 + g;
+    constexpr int YS = YB / ELEM;
+    T* dyslots = reinterpret_cast<T*>(sm.extra(g));
+    for (long long it = 0;; ++it) {
+        const int stage = (int)(it % S);
+        int got = 2;
+        {
+            volatile long long* total = sm.total(g);
+            for (unsigned spin = 0; spin < WAIT_LIMIT; ++spin) {
+                if (mbar_try_wait(sm.full(g, stage), (unsigned)((it / S) & 1))) { got = 0; break; }
+                const long long n = *total;
+                if (n >= 0 && it >= n) { got = 1; break; }
+            }
+            if (got == 2 && p.status) atomicCAS(p.status, 0, ERR_WAIT_FULL);
+        }
+        if (got != 0) break;
+        const long long row = sm.hdr(g, stage)[0];
+        const unsigned char* st = sm.stage(g, stage);
+        const T* sX = reinterpret_cast<const T*>(st + L::OFF_X);
+        const T* sEX = reinterpret_cast<const T*>(st + L::OFF_EX);
+        const T* sY = reinterpret_cast<const T*>(st + L::OFF_Y);
+        const T* sEY = reinterpret_cast<const T*>(st + L::OFF_EY);
+        const T* sW = reinterpret_cast<const T*>(st + L::OFF_W);
+        const T* sEW = reinterpret_cast<const T*>(st + L::OFF_EW);
+        const T* sdZ = reinterpret_cast<const T*>(st + L::OFF_DZ);
+        T yr[Y_DIM], eyr[Y_DIM], gyreg[Y_DIM];
+#pragma unroll
+        for (int j = 0; j < Y_DIM; ++j) { yr[j] = sY[j]; eyr[j] = sEY[j]; gyreg[j] = (T)0; }
+        T gdz[ZPC_ALL];
+#pragma unroll
+        for (int k = 0; k < ZPC_ALL; ++k) gdz[k] = (T)0;
+        T* gwrow = p.dW + row * (long long)W_NUMEL;
+        T* gxrow = p.dX + row * (long long)X_DIM;
+        sfor<0, N_IN1>([&](auto a_) {
+            constexpr int a = a_;
+            constexpr int D1 = IN1_D[a];
+            const bool live = (IN1_MUL[a] == CHANNELS) || (u < IN1_MUL[a]);
+            T x[D1], ex[D1], gxa[D1];
+#pragma unroll
+            for (int i = 0; i < D1; ++i) {
+                x[i] = live ? sX[IN1_OFF[a] + u * D1 + i] : (T)0;
+                ex[i] = live ? sEX[IN1_OFF[a] + u * D1 + i] : (T)0;
+                gxa[i] = (T)0;
+            }
+            sfor<0, N_INSTR>([&](auto p_) {
+                constexpr int P = p_;
+                if constexpr (I_IN1[P] == a) {
+                    constexpr int b = I_IN2[P], o = I_OUT[P];
+                    constexpr int D2 = IN2_D[b], D3 = OUT_D[o];
+                    const T w = live ? sW[weight_offset<P>(u, 0)] : (T)0;
+                    const T ew = live ? sEW[weight_offset<P>(u, 0)] : (T)0;
+                    T gz[D3], q[D2], r[D1], wx[D1];
+#pragma unroll
+                    for (int k = 0; k < D3; ++k) gz[k] = live ? sdZ[OUT_OFF[o] + u * D3 + k] : (T)0;
+#pragma unroll
+                    for (int j = 0; j < D2; ++j) q[j] = fma(w, eyr[IN2_OFF[b] + j], ew * yr[IN2_OFF[b] + j]);
+#pragma unroll
+                    for (int i = 0; i < D1; ++i) { r[i] = fma(w, ex[i], ew * x[i]); wx[i] = w * x[i]; }
+                    T gw = (T)0, pij = (T)0, tij = (T)0;
+                    sfor<CG_BEGIN[P], CG_BEGIN[P + 1]>([&](auto n) {
+                        constexpr int N = n;
+                        constexpr int I = CG_I[N], J = CG_J[N], K = CG_K[N];
+                        if constexpr (cg_pair_first<P, N>()) {
+                            pij = (T)CG_V[N] * gz[K];
+                            tij = fma(r[I], yr[IN2_OFF[b] + J], wx[I] * eyr[IN2_OFF[b] + J]);
+                        } else {
+                            pij = fma((T)CG_V[N], gz[K], pij);
+                        }
+                        gdz[out_reg_off(o) + K] = fma((T)CG_V[N], tij, gdz[out_reg_off(o) + K]);
+                        if constexpr (cg_pair_last<P, N>()) {
+                            gxa[I] = fma(q[J], pij, gxa[I]);
+                            gyreg[IN2_OFF[b] + J] = fma(r[I], pij, gyreg[IN2_OFF[b] + J]);
+                            gw = fma(fma(ex[I], yr[IN2_OFF[b] + J], x[I] * eyr[IN2_OFF[b] + J]), pij, gw);
+                        }
+                    });
+                    if (live) __stcs(gwrow + weight_offset<P>(u, 0), gw);
+                }
+            });
+            if (live) {
+#pragma unroll
+                for (int i = 0; i < D1; ++i) __stcs(gxrow + IN1_OFF[a] + u * D1 + i, gxa[i]);
+            }
+        });
+        // the stage has been read: hand it back
+        __syncwarp();
+        if (lane == 0) mbar_arrive(sm.empty(g, stage));
+        // gradient with respect to dZ: this channel's slice of the row
+        {
+            T* zrow = p.Z + row * (long long)Z_DIM;
+            sfor<0, N_OUT>([&](auto o_) {
+                constexpr int o = o_;
+                if ((OUT_MUL[o] == CHANNELS) || (u < OUT_MUL[o])) {
+#pragma unroll
+                    for (int k = 0; k < OUT_D[o]; ++k) __stcs(zrow + OUT_OFF[o] + u * OUT_D[o] + k, gdz[out_reg_off(o) + k]);
+                }
+            });
+        }
+        // gradient with respect to y: over the channels of the warp, then over the warps
+        const int ring = (int)(it % DY_RING);
+        {
+            constexpr int SHIFT = 5 - log2_int(next_pow2(Y_DIM));
+            warp_reduce_vector<Y_DIM>(gyreg, lane);
+            const int j = lane >> SHIFT;
+            if ((lane & ((1 << SHIFT) - 1)) == 0 && j < Y_DIM) dyslots[(ring * WARPS_PER_GROUP + warp) * YS + j] = gyreg[0];
+        }
+        group_sync(bar_id, G);
+        {
+            const T* slots = dyslots + ring * WARPS_PER_GROUP * YS;
+            if (tg < Y_DIM) {
+                T sum = (T)0;
+#pragma unroll
+                for (int w2 = 0; w2 < WARPS_PER_GROUP; ++w2) sum += slots[w2 * YS + tg];
+                p.dY[row * (long long)Y_DIM + tg] = sum;
+            }
+        }
+    }
+}
+
+template <int INSTANCE>
+__device__ __forceinline__ void uvu_body_dbl(const UvuParams& p) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    DblSmem sm(smem_raw, p.stages);
+    const int tid = threadIdx.x;
+    if (tid == 0) {
+        const bool any_elem = (p.flags & 15) != 15;
+        for (int g = 0; g < NG; ++g) {
+            for (int s = 0; s < p.stages; ++s) {
+                mbar_init(sm.full(g, s), 1 + (any_elem ? 32 : 0));
+                mbar_init(sm.empty(g, s), WARPS_PER_GROUP);
+            }
+            *sm.total(g) = -1;
+        }
+        fence_mbar_init();
+    }
+    __syncthreads();
+    if (tid >= NCONSUMERS) {
+        run_producer_dbl<INSTANCE>(p, sm, (tid - NCONSUMERS) >> 5, tid & 31);
+        return;
+    }
+    run_double_backward<INSTANCE>(p, sm, tid / G, tid % G);
+}
+
 // ---------------------------------------------------------------- kernel body
 
 template <int MODE, bool BWD>
@@ -1525,6 +1767,7 @@ __device__ __forceinline__ void uvu_body(const UvuParams& p) {
 #define OEQ_K_BWD_ATOMIC 5
 #define OEQ_K_BWD_RECV_DET 6
 #define OEQ_K_BWD_RECV_ATOMIC 7
+#define OEQ_K_DBL_BATCH 8
 
 extern "C" __global__ void __launch_bounds__(oeq::NTHREADS, oeqd::MIN_CTAS) oeq_uvu_kernel(const oeq::UvuParams p) {
 #if OEQ_KERNEL == OEQ_K_FWD_BATCH
@@ -1543,6 +1786,8 @@ extern "C" __global__ void __launch_bounds__(oeq::NTHREADS, oeqd::MIN_CTAS) oeq_
     oeq::uvu_body_recv<oeq::MODE_DET>(p);
 #elif OEQ_KERNEL == OEQ_K_BWD_RECV_ATOMIC
     oeq::uvu_body_recv<oeq::MODE_ATOMIC>(p);
+#elif OEQ_KERNEL == OEQ_K_DBL_BATCH
+    oeq::uvu_body_dbl<0>(p);
 #else
 #error "OEQ_KERNEL must select one of the uvu kernels"
 #endif

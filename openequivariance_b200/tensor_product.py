@@ -87,6 +87,7 @@ class TensorProduct(TensorProductBase):
         self.is_uvw = problem.instructions[0].connection_mode == "uvw"
         self.tp_id = next(_op_ids)
         self.internal = _native.TPHandle(problem)
+        self._has_fused_double_backward = self.internal.has_double_backward()
         self._workspace = None
         # both modes need torch to drive device memory and streams
         self.setup_torch_custom_op()
@@ -141,6 +142,19 @@ class TensorProduct(TensorProductBase):
                                    torch.cuda.current_stream().cuda_stream)
         return dx, dy, dw
 
+    def _double_backward_impl(self, x, y, w, dz, ex, ey, ew):
+        """Gradients of ``<ex, dX> + <ey, dY> + <ew, dW>`` with respect to (x, y, w, dz) in one launch (problems
+        for which the library has the one-pass kernel: ``self._has_fused_double_backward``)."""
+        _require_cuda(x, y, w, dz, ex, ey, ew)
+        self._check_shapes(x, y, w)
+        x, y, w, dz, ex, ey, ew = (t.contiguous() for t in (x, y, w, dz, ex, ey, ew))
+        gx, gy, gw, gdz = torch.empty_like(x), torch.empty_like(y), torch.empty_like(w), torch.empty_like(dz)
+        with torch.cuda.device(x.device):
+            self.internal.double_backward(x.shape[0], x.data_ptr(), y.data_ptr(), w.data_ptr(), dz.data_ptr(),
+                                          ex.data_ptr(), ey.data_ptr(), ew.data_ptr(), gx.data_ptr(), gy.data_ptr(),
+                                          gw.data_ptr(), gdz.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        return gx, gy, gw, gdz
+
     def forward_raw(self, batch, L1_in, L2_in, L3_out, weights, stream=0):
         """Launch on raw device pointers (argument order of the reference's
         ``forward_raw``, TensorProductBase.py:41-49)."""
@@ -194,6 +208,9 @@ class TensorProduct(TensorProductBase):
             #   d/dx    = dX(ey, w, dz) + dX(y, ew, dz)     and likewise for y and w.
             x, y, w, dz = ctx.L1_in, ctx.L2_in, ctx.weights, ctx.L3_grad
             ex, ey, ew = grad_output[0], grad_output[1], grad_output[2]
+            if tp._has_fused_double_backward and not torch.is_grad_enabled():
+                # nothing differentiates through this result: one launch that reads the row's arrays once
+                return tp._double_backward_impl(x, y, w, dz, ex, ey, ew)
             a = backward_helper(ex, ey, w, dz)   # dX(ey, w), dY(ex, w)
             b = backward_helper(x, y, ew, dz)    # dX(y, ew), dY(x, ew)
             c = backward_helper(ex, y, w, dz)    # dW(ex, y)

@@ -61,8 +61,9 @@ def test_kernels_specialise_without_a_gpu(tmp_path):
     try:
         _native.precompile(problem_by_name("readme"), _native.KIND_BATCH | _native.KIND_CONV_DET)
         files = sorted(os.listdir(tmp_path))
-        # batch forward/backward, convolution forward, sender-order and receiver-order backward
-        assert len(files) == 5 and all(f.endswith(".cubin") for f in files)
+        # batch forward / backward / one-pass second derivatives, convolution forward, sender-order and
+        # receiver-order backward
+        assert len(files) == 6 and all(f.endswith(".cubin") for f in files)
         _native.precompile(problem_by_name("readme"), _native.KIND_BATCH)
         assert sorted(os.listdir(tmp_path)) == files
     finally:

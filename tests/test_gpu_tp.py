@@ -149,6 +149,57 @@ def test_autograd_and_double_backward():
         assert rel_err(got.cpu().numpy(), want) < 1e-11
 
 
+@pytest.mark.parametrize("name,dtype,batch", [("readme", np.float64, 77), ("nequip_32", np.float64, 45),
+                                              ("uvu_norm_path", np.float64, 19), ("mace_128", np.float32, 40),
+                                              ("mace_large_128", np.float32, 11), ("roofline_6e", np.float32, 9)])
+def test_one_pass_second_derivatives(name, dtype, batch):
+    """The one-pass kernel for the gradient of <ex,dX> + <ey,dY> + <ew,dW> against the oracle (autograd of
+    autograd on the CPU) and against the composition of four backward and three forward launches; it is what
+    autograd's second backward pass runs when nothing differentiates through its result."""
+    p = problem_by_name(name, irrep_dtype=dtype, weight_dtype=dtype)
+    tp = oeq.TensorProduct(p, torch_op=True)
+    assert tp._has_fused_double_backward
+    x, y, w, dz = tp_inputs(p, batch, 15)
+    rng = np.random.default_rng(16)
+    ex, ey, ew = (rng.normal(size=a.shape).astype(dtype) for a in (x, y, w))
+    dev = [torch.from_numpy(a).cuda() for a in (x, y, w, dz, ex, ey, ew)]
+    got = tp._double_backward_impl(*dev)
+    torch.cuda.synchronize()
+    tp.check_device_status()
+    ref = orc.tp_double_backward(p, x, y, w, dz, ex, ey, ew)
+    tol = REL_TOL[dtype] if dtype == np.float32 else 1e-11
+    for g, r in zip(got, ref):
+        assert rel_err(g.cpu().numpy(), r) < tol
+    # composition, as the reference does it
+    xt, yt, wt, dzt, ext, eyt, ewt = dev
+    a = tp.backward_helper(ext, eyt, wt, dzt)
+    b = tp.backward_helper(xt, yt, ewt, dzt)
+    c = tp.backward_helper(ext, yt, wt, dzt)
+    d = tp.backward_helper(xt, eyt, wt, dzt)
+    gz = tp(ext, yt, wt) + tp(xt, eyt, wt) + tp(xt, yt, ewt)
+    for g, r in zip(got, (a[0] + b[0], a[1] + b[1], c[2] + d[2], gz)):
+        assert rel_err(g.cpu().numpy(), r.cpu().numpy()) < 10 * tol
+    # through autograd: second backward without create_graph takes the one-pass kernel
+    xg, yg, wg, dzg = (t.clone().requires_grad_(True) for t in (xt, yt, wt, dzt))
+    z = tp(xg, yg, wg)
+    dx, dy, dw = torch.autograd.grad(z, (xg, yg, wg), dzg, create_graph=True)
+    grads = torch.autograd.grad((dx * ext).sum() + (dy * eyt).sum() + (dw * ewt).sum(), (xg, yg, wg, dzg))
+    for g, r in zip(grads, got):
+        assert torch.equal(g, r)
+
+
+def test_second_derivatives_fall_back_to_composition():
+    """Shared weights and second inputs of higher multiplicity have no one-pass kernel: the C ABI says so and the
+    front end composes."""
+    from openequivariance_b200 import _native
+    for name in ("uvu_shared", "uvu_v2", "uvw_small"):
+        tp = oeq.TensorProduct(problem_by_name(name), torch_op=True)
+        assert not tp._has_fused_double_backward
+        buf = torch.zeros(1 << 16, device="cuda")
+        rc = _native.lib().oeq_tp_double_backward(tp.internal.ptr, 4, *([buf.data_ptr()] * 11), 0)
+        assert rc == 2 and b"compose" in _native.lib().oeq_last_error()
+
+
 def test_shared_weight_gradient_is_reproducible():
     p = problem_by_name("uvu_shared")
     tp = oeq.TensorProduct(p, torch_op=True)
