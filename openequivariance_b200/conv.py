@@ -225,7 +225,8 @@ class TensorProductConv(TensorProductBase):
         self.workspace_size, self.workspace_ptr = buf.numel(), buf.data_ptr()
         return buf.data_ptr(), buf.numel()
 
-    def _backward_impl(self, x, y, w, dz, rows, cols, perm=None):
+    def _backward_impl(self, x, y, w, dz, rows, cols, perm=None, scratch=True):
+        """``scratch=False`` runs the deterministic pass without scratch memory (the sender-order kernel)."""
         self._check(x, y, w, rows, cols, perm)
         if self.deterministic and perm is None:
             raise ValueError("the deterministic convolution needs sender_perm")
@@ -234,7 +235,7 @@ class TensorProductConv(TensorProductBase):
         perm_ptr = perm.contiguous().data_ptr() if (perm is not None and self.deterministic) else 0
         dx, dy, dw = torch.empty_like(x), torch.empty_like(y), torch.empty_like(w)
         with torch.cuda.device(x.device):
-            ws_ptr, ws_bytes = self._backward_scratch(x.device, x.shape[0], rows.shape[0])
+            ws_ptr, ws_bytes = self._backward_scratch(x.device, x.shape[0], rows.shape[0]) if scratch else (0, 0)
             self.internal.backward(x.shape[0], rows.shape[0], x.data_ptr(), y.data_ptr(), w.data_ptr(),
                                    dz.data_ptr(), rows.data_ptr(), cols.data_ptr(), perm_ptr,
                                    dx.data_ptr(), dy.data_ptr(), dw.data_ptr(), ws_ptr, ws_bytes,

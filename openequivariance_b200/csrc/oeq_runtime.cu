@@ -1219,7 +1219,7 @@ struct oeq_conv {
     bool has_fwd_tc = false;
     Kernel bwd_recv;            // receiver-order backward pass (needs scratch in the deterministic variant)
     bool has_bwd_recv = false;
-    cudaKernel_t sum_rows_fn = nullptr;
+    cudaKernel_t sum_rows_fn = nullptr, clear_fn = nullptr;
     int last_bwd_launches = 0;  // kernel launches of the most recent oeq_conv_backward
     int* d_status = nullptr;
     cudaStream_t last_stream = nullptr;
@@ -1846,7 +1846,10 @@ int oeq_conv_backward(oeq_conv* h, int64_t nodes, int64_t edges, const void* X, 
         Kernel& k = h->bwd_recv;
         if (!k.loaded) {
             if ((rc = load_kernel(k, "oeq_uvu_kernel", false))) return rc;
-            if (h->deterministic) OEQ_CUDA(cudaLibraryGetKernel(&h->sum_rows_fn, k.lib, "oeq_sum_sender_rows"));
+            if (h->deterministic) {
+                OEQ_CUDA(cudaLibraryGetKernel(&h->sum_rows_fn, k.lib, "oeq_sum_sender_rows"));
+                OEQ_CUDA(cudaLibraryGetKernel(&h->clear_fn, k.lib, "oeq_clear"));
+            }
         }
         const char* Yb = (const char*)Y; const char* Wb = (const char*)W;
         char* dYb = (char*)dY; char* dWb = (char*)dW;
@@ -1868,8 +1871,15 @@ int oeq_conv_backward(oeq_conv* h, int64_t nodes, int64_t edges, const void* X, 
             h->last_bwd_launches = 1;
             return OEQ_OK;
         }
-        // rows of nodes that send nothing are never written by the row sum
-        OEQ_CUDA(cudaMemsetAsync(dX, 0, (size_t)nodes * p.x_dim * e, st));
+        // rows of nodes that send nothing are never written by the row sum (cleared by a kernel: a memset call
+        // may land on a copy engine behind the caller's host transfers)
+        {
+            unsigned long long words = (unsigned long long)nodes * p.x_dim * e / 4;
+            void* ptr = dX;
+            void* args[] = {&ptr, &words};
+            const unsigned grid = (unsigned)std::max<unsigned long long>(1, std::min<unsigned long long>((unsigned long long)k.sm_count * 8, (words / 4 + 255) / 256));
+            OEQ_CUDA(cudaLaunchKernel((const void*)h->clear_fn, dim3(grid), dim3(256), args, 0, st));
+        }
         auto sum_launch = [&](long long e0, long long n, void* scratch, bool first) -> int {
             UvuParams sp{};
             sp.dX = dX; sp.ws = scratch;
@@ -1891,7 +1901,7 @@ int oeq_conv_backward(oeq_conv* h, int64_t nodes, int64_t edges, const void* X, 
         // into a few blocks so that most of the summing hides behind the receiver-order launches.
         // Pipelining pays when a block's receiver-order launch runs for a millisecond or more; the scratch
         // bytes of a block are a fair proxy for that (wide rows mean much arithmetic per edge).
-        const size_t min_block_bytes = (size_t)std::max(1, env_int("OEQ_B200_PIPELINE_BLOCK_MB", 512)) << 20;
+        const size_t min_block_bytes = (size_t)std::max(1, env_int("OEQ_B200_PIPELINE_BLOCK_MB", 1024)) << 20;
         const long long min_block = std::max<long long>(recv_min_block_edges(), (long long)(min_block_bytes / row));
         const bool pipelined = k.map.helper_warps > 0 && edges >= 4 * min_block;
         if (pipelined) {

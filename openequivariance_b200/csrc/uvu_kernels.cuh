@@ -1804,6 +1804,23 @@ extern "C" __global__ void oeq_reduce_partials(const oeqd::T* ws, oeqd::T* out, 
 }
 
 #if OEQ_KERNEL == OEQ_K_BWD_RECV_DET
+// Clears `bytes` bytes (a multiple of 4) at a 4-byte aligned address.  A kernel rather than a memset call: a
+// memset may be served by a copy engine, where it would queue behind host transfers that other streams have
+// in flight and stall the stream that runs the backward pass.
+extern "C" __global__ void oeq_clear(unsigned int* ptr, unsigned long long words) {
+    const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
+    unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
+    // 16-byte stores over the aligned middle, words at the ragged ends
+    const unsigned long long head = ((16 - (reinterpret_cast<unsigned long long>(ptr) & 15)) & 15) / 4;
+    const unsigned long long h = head < words ? head : words;
+    const unsigned long long quads = (words - h) / 4;
+    uint4* mid = reinterpret_cast<uint4*>(ptr + h);
+    for (unsigned long long q = i; q < quads; q += stride) mid[q] = make_uint4(0u, 0u, 0u, 0u);
+    if (i < h) ptr[i] = 0u;
+    const unsigned long long tail0 = h + quads * 4;
+    if (i < words - tail0) ptr[tail0 + i] = 0u;
+}
+
 // The row sum of the deterministic receiver-order backward pass as a launch of its own (the last block of
 // edges, or every block when the launches carry no helper warps): see sum_sender_rows.
 extern "C" __global__ void __launch_bounds__(256) oeq_sum_sender_rows(const oeq::UvuParams p) {

@@ -168,6 +168,8 @@ def test_streamed_host_tensors(name, slab_edges):
     nodes = 120
     rows, cols = random_graph(nodes, 1500, seed=12)
     conv, (xt, yt, wt, dzt, index), (z, dx, dy, dw) = check_conv(p, nodes, rows, cols, 13, True)
+    # the slab pipeline runs the backward pass without scratch memory (sender-order kernel): same bits as that
+    dx, dy, dw = conv._backward_impl(xt, yt, wt, dzt, *index, scratch=False)
     rows_s, cols_s = index[0].cpu().numpy(), index[1].cpu().numpy()
     streamed = StreamedTensorProductConv(p, rows_s, cols_s, nodes, slab_edges=slab_edges)
     pin = lambda t: torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t)
@@ -194,6 +196,7 @@ def test_sharded_host_tensor_step_on_one_rank():
     nodes = 90
     rows, cols = random_graph(nodes, 1100, seed=31)
     conv, (xt, yt, wt, dzt, index), (z, dx, dy, dw) = check_conv(p, nodes, rows, cols, 32, True)
+    dx, dy, dw = conv._backward_impl(xt, yt, wt, dzt, *index, scratch=False)     # what the slab pipeline runs
     sharded = ShardedTensorProductConv(p, index[0].cpu().numpy(), index[1].cpu().numpy(), nodes)
     pin = lambda t: torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t)
     x_h, y_h, w_h, dz_h = pin(xt), pin(yt), pin(wt), pin(dzt)
