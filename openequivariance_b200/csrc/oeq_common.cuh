@@ -153,6 +153,10 @@ __device__ __forceinline__ void cp_async_elem(void* dst_smem, const void* src_gm
     asm volatile("cp.async.ca.shared.global [%0], [%1], %2;" ::"r"(smem_u32(dst_smem)), "l"(src_gmem), "n"(BYTES)
                  : "memory");
 }
+// 16-byte variant (both addresses 16-byte aligned), bypassing L1.
+__device__ __forceinline__ void cp_async_16(void* dst_smem, const void* src_gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src_gmem) : "memory");
+}
 // Arrive on `bar` once all prior cp.async of this thread have landed (the
 // arrival is one of the barrier's expected arrivals: ".noinc").
 __device__ __forceinline__ void cp_async_arrive_noinc(unsigned long long* bar) {

@@ -1170,7 +1170,15 @@ int launch_uvu(Kernel& k, const Problem& p, UvuParams& prm, cudaStream_t stream,
     const void* zlike = prm.dZ ? prm.dZ : prm.Z;
     if ((p.z_dim * e) % 16 == 0 && aligned16(zlike)) flags |= 8;
     if (env_int("OEQ_B200_NO_BULK", 0)) flags = 0;
-    prm.flags = (flags & ~clear_flags) | extra_flags;
+    flags &= ~clear_flags;
+    {
+        // short rows: 16-byte cp.async from all lanes instead of one bulk copy issued by one lane
+        const int limit = env_int("OEQ_B200_VEC_COPY_BYTES", 0);
+        const int row_bytes[4] = {p.x_dim * e, p.y_dim * e, p.w_numel * e, p.z_dim * e};
+        for (int a = 0; a < 4; ++a)
+            if ((flags & (1 << a)) && row_bytes[a] <= limit) flags = (flags & ~(1 << a)) | (256 << a);
+    }
+    prm.flags = flags | extra_flags;
     prm.stages = k.stages;
     prm.chunk = std::max(1, env_int("OEQ_B200_CHUNK", 128));
     long long want = (prm.n_items + k.map.ng - 1) / k.map.ng;

@@ -55,7 +55,9 @@ struct UvuParams {
     T* ws;                  // scratch: per-group partial sums of shared-weight gradients
     int* status;
     int stages;             // shared-memory stages per group
-    int flags;              // bit0 X bulk-able, bit1 Y, bit2 W, bit3 Z/dZ
+    int flags;              // bit0 X bulk-able, bit1 Y, bit2 W, bit3 Z/dZ; bits 8..11: the same arrays staged by
+                            // 16-byte cp.async from all lanes instead (short rows: one bulk copy per row costs
+                            // the issuing lane more than the row is worth)
     int chunk;              // edges per work chunk (convolution modes)
     long long e_lo, e_hi;   // sender-row sum: the edge range [e_lo, e_hi) whose scratch rows ws holds
     // row sum done by the helper warps of a receiver-order launch (sum_items == 0: none): the whole edge list
@@ -461,13 +463,22 @@ __device__ __forceinline__ void issue_item(const UvuParams& p, const SMT& sm, in
     }
     const bool any_elem = !xb || !yb || (!wb && !SHARED_W && !UNIT_W) || (BWD && !zb);
     if (any_elem) {
-        if (!xb && first) for (int i = lane; i < X_DIM; i += 32) cp_async_elem<ELEM>((T*)(st + L::OFF_X) + i, xsrc + i);
-        if (!yb && first) for (int i = lane; i < Y_DIM; i += 32) cp_async_elem<ELEM>((T*)(st + L::OFF_Y) + i, ysrc + i);
+        // rows that are not bulk copied: 16-byte pieces by all lanes when the row allows it, single elements otherwise
+        auto stage_row = [&](unsigned char* dst, const T* src, int n, bool vec) {
+            if (vec) {
+                const int pieces = pad16(n * ELEM) / 16;
+                for (int i = lane; i < pieces; i += 32) cp_async_16(dst + 16 * i, reinterpret_cast<const unsigned char*>(src) + 16 * i);
+            } else {
+                for (int i = lane; i < n; i += 32) cp_async_elem<ELEM>((T*)dst + i, src + i);
+            }
+        };
+        if (!xb && first) stage_row(st + L::OFF_X, xsrc, X_DIM, p.flags & 256);
+        if (!yb && first) stage_row(st + L::OFF_Y, ysrc, Y_DIM, p.flags & 512);
         if constexpr (!SHARED_W && !UNIT_W) {
-            if (!wb) for (int i = lane; i < w_n; i += 32) cp_async_elem<ELEM>((T*)(st + L::OFF_W) + i, wsrc + i);
+            if (!wb) stage_row(st + L::OFF_W, wsrc, w_n, p.flags & 1024);
         }
         if constexpr (BWD) {
-            if (!zb) for (int i = lane; i < z_n; i += 32) cp_async_elem<ELEM>((T*)(st + L::OFF_DZ) + i, zsrc + i);
+            if (!zb) stage_row(st + L::OFF_DZ, zsrc, z_n, p.flags & 2048);
         }
         cp_async_arrive_noinc(full);
     }
@@ -1421,25 +1432,53 @@ __device__ void sum_sender_rows(const T* __restrict__ temp, T* __restrict__ dX, 
             unsigned mask = __ballot_sync(0xffffffffu, in_block);
             if (mask == 0) continue;
             if (in_block) s = cols[e];
+            // Short rows: the loads of up to U rows go out together (a row at a time would pay the DRAM latency
+            // per row); the rows are still added one after the other, in order.
+            constexpr int U = (NV * VEC <= 16) ? 4 : (NV * VEC <= 32 ? 2 : 1);
             while (mask) {
-                const int src = __ffs(mask) - 1;
-                mask &= mask - 1;
-                const long long ej = __shfl_sync(0xffffffffu, e, src);
-                const long long sj = __shfl_sync(0xffffffffu, s, src);
-                if (prev >= 0 && sj != prev) flush(prev);
-                prev = sj;
-                const T* row = temp + (ej - e_lo) * (long long)XS;
+                long long ej[U], sj[U];
+                T val[U][NV * VEC];
+                int n = 0;
 #pragma unroll
-                for (int v = 0; v < NV; ++v) {
-                    const int b4 = (lane + 32 * v) * VEC;
-                    if (b4 < XS) {
-                        if constexpr (ELEM == 4) {
-                            const float4 t = __ldcs(reinterpret_cast<const float4*>(row + b4));
-                            acc[v * VEC + 0] += t.x; acc[v * VEC + 1] += t.y; acc[v * VEC + 2] += t.z; acc[v * VEC + 3] += t.w;
-                        } else {
-                            const double2 t = __ldcs(reinterpret_cast<const double2*>(row + b4));
-                            acc[v * VEC + 0] += t.x; acc[v * VEC + 1] += t.y;
+                for (int q = 0; q < U; ++q) {
+                    ej[q] = 0; sj[q] = -1;
+                    if (mask) {
+                        const int src = __ffs(mask) - 1;
+                        mask &= mask - 1;
+                        ej[q] = __shfl_sync(0xffffffffu, e, src);
+                        sj[q] = __shfl_sync(0xffffffffu, s, src);
+                        n = q + 1;
+                    }
+                }
+#pragma unroll
+                for (int q = 0; q < U; ++q) {
+                    if (q < n) {
+                        const T* row = temp + (ej[q] - e_lo) * (long long)XS;
+#pragma unroll
+                        for (int v = 0; v < NV; ++v) {
+                            const int b4 = (lane + 32 * v) * VEC;
+                            if (b4 < XS) {
+                                if constexpr (ELEM == 4) {
+                                    const float4 t = __ldcs(reinterpret_cast<const float4*>(row + b4));
+                                    val[q][v * VEC + 0] = t.x; val[q][v * VEC + 1] = t.y; val[q][v * VEC + 2] = t.z; val[q][v * VEC + 3] = t.w;
+                                } else {
+                                    const double2 t = __ldcs(reinterpret_cast<const double2*>(row + b4));
+                                    val[q][v * VEC + 0] = t.x; val[q][v * VEC + 1] = t.y;
+                                }
+                            } else {
+#pragma unroll
+                                for (int c = 0; c < VEC; ++c) val[q][v * VEC + c] = (T)0;
+                            }
                         }
+                    }
+                }
+#pragma unroll
+                for (int q = 0; q < U; ++q) {
+                    if (q < n) {
+                        if (prev >= 0 && sj[q] != prev) flush(prev);
+                        prev = sj[q];
+#pragma unroll
+                        for (int i = 0; i < NV * VEC; ++i) acc[i] += val[q][i];
                     }
                 }
             }
