@@ -179,6 +179,11 @@ int oeq_conv_check(oeq_conv* h);
  * report it; it has no counterpart in the reference. */
 int oeq_conv_last_backward_launches(const oeq_conv* h);
 
+/* Exercises the error path of the kernels' bounded waits without harming the device: one thread polls a barrier
+ * that nothing completes `polls` times (at most 2^20), gives up, and the call reports what oeq_*_check would report,
+ * OEQ_ERR_DEVICE_WAIT.  The context stays usable.  No counterpart in the reference (its kernels have no waits). */
+int oeq_selftest_bounded_wait(int polls, void* stream);
+
 /* Launch geometry of the most recent specialisation, for benchmarks and tests:
  * which = 0 forward, 1 backward.  Any output pointer may be NULL. */
 int oeq_tp_launch_info(const oeq_tp* h, int which, int* threads, int* groups_per_cta, int* partitions,

@@ -73,6 +73,7 @@ SYMBOLS = {
     "oeq_conv_backward": (_INT, [_P, _I64, _I64, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _SZ, _P]),
     "oeq_conv_check": (_INT, [_P]),
     "oeq_conv_last_backward_launches": (_INT, [_P]),
+    "oeq_selftest_bounded_wait": (_INT, [_INT, _P]),
     "oeq_tp_launch_info": (_INT, [_P, _INT, _PI, _PI, _PI, _PI, _PI, _PI]),
     "oeq_conv_launch_info": (_INT, [_P, _INT, _PI, _PI, _PI, _PI, _PI, _PI]),
 }

@@ -31,6 +31,7 @@
 #include <vector>
 
 #include "../../include/oeq_b200.h"
+#include "oeq_common.cuh"
 
 namespace {
 
@@ -1973,6 +1974,35 @@ int oeq_conv_backward(oeq_conv* h, int64_t nodes, int64_t edges, const void* X, 
     }
 #endif
     return launch_uvu(h->bwd, p, prm, st);
+}
+
+// ---------------------------------------------------------------- self-test of the bounded waits
+
+// One thread waits on a shared-memory barrier that nothing ever completes, polls `polls` times, gives up, records
+// the code in *status and returns: the path every staged kernel takes when a copy never lands.
+__global__ void oeq_wait_probe_kernel(int* status, unsigned polls) {
+    __shared__ unsigned long long bar;
+    if (threadIdx.x == 0) {
+        oeq::mbar_init(&bar, 1);
+        oeq::fence_mbar_init();
+        bool done = false;
+        for (unsigned spin = 0; spin < polls && !done; ++spin) done = oeq::mbar_try_wait(&bar, 0u);
+        if (!done) atomicCAS(status, 0, oeq::ERR_WAIT_FULL);
+    }
+}
+
+int oeq_selftest_bounded_wait(int polls, void* stream) {
+    if (polls < 1 || polls > (1 << 20)) return fail(OEQ_ERR_INVALID, "polls must be in 1 .. 2^20");
+    int* d_status = nullptr;
+    int rc = ensure_status(&d_status);
+    if (rc) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    oeq_wait_probe_kernel<<<1, 32, 0, st>>>(d_status, (unsigned)polls);
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) rc = check_status(d_status, st);      // OEQ_ERR_DEVICE_WAIT is the expected answer
+    cudaFree(d_status);
+    if (e != cudaSuccess) return fail(OEQ_ERR_CUDA, std::string("wait probe: ") + cudaGetErrorString(e));
+    return rc;
 }
 
 int oeq_conv_last_backward_launches(const oeq_conv* h) { return h ? h->last_bwd_launches : 0; }

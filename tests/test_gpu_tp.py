@@ -239,3 +239,16 @@ def test_rejects_cpu_tensors_and_bad_shapes():
     with pytest.raises(ValueError):
         tp._forward_impl(torch.zeros(3, 4, device="cuda"), torch.zeros(3, 7, device="cuda"),
                          torch.zeros(3, 1, device="cuda"))
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_context_survives():
+    """Every staged kernel polls its barriers a bounded number of times and records a code when it gives up.
+    The library's probe makes exactly that happen (a barrier that nothing completes, a short poll limit): the
+    call must report the device-wait error, and the next launch on the same context must work."""
+    from openequivariance_b200 import _native
+    lib = _native.lib()
+    stream = torch.cuda.current_stream().cuda_stream
+    assert lib.oeq_selftest_bounded_wait(2000, stream) == 5          # OEQ_ERR_DEVICE_WAIT
+    assert b"bounded wait" in lib.oeq_last_error()
+    assert lib.oeq_selftest_bounded_wait(0, stream) == 1             # rejected argument
+    run_case("readme", 100, np.float32)
