@@ -477,6 +477,56 @@ def second_derivative_case(torch, device, steps=10, warmup=3, batch=50_000):
             "hbm_frac_one_pass": bytes_ / (fused * 1e-3) / 1e9 / peak, "algorithmic_bytes": bytes_}
 
 
+def conv_second_derivative_case(torch, args, device, nodes=20_000, degree=40.0, steps=5, warmup=3):
+    """Second derivatives of the deterministic convolution (MACE irreps to l=2, 20 000 nodes x ~40 neighbours): two
+    fused launches (plus the row sum) against the four backward and three forward launches the reference composes."""
+    import openequivariance_b200 as oeq
+    from openequivariance_b200.graph import periodic_radius_graph
+    p = oeq.ChannelwiseTPP("128x0e+128x1o+128x2e", "1x0e+1x1o+1x2e+1x3o", "128x0e+128x1o+128x2e")
+    g = periodic_radius_graph(nodes, degree, seed=args.seed, numbering="morton")
+    conv = oeq.TensorProductConv(p, torch_op=True, deterministic=True)
+    idx = [torch.from_numpy(a).to(device) for a in (g.rows, g.cols, g.sender_perm)]
+    gen = torch.Generator(device=device).manual_seed(args.seed + 1)
+    n, e = g.node_count, g.nnz
+    mk = lambda r, c: torch.randn(r, c, device=device, generator=gen)
+    xd, yd, zd, wn = p.irreps_in1.dim, p.irreps_in2.dim, p.irreps_out.dim, p.weight_numel
+    x, y, w, dz = mk(n, xd), mk(e, yd), mk(e, wn), mk(n, zd)
+    ex, ey, ew = mk(n, xd), mk(e, yd), mk(e, wn)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+
+    def composed():
+        a = conv._backward_impl(ex, ey, w, dz, *idx)
+        b = conv._backward_impl(x, y, ew, dz, *idx)
+        c = conv._backward_impl(ex, y, w, dz, *idx)
+        d = conv._backward_impl(x, ey, w, dz, *idx)
+        gz = conv._forward_impl(ex, y, w, *idx) + conv._forward_impl(x, ey, w, *idx) + conv._forward_impl(x, y, ew, *idx)
+        return a[0] + b[0], a[1] + b[1], c[2] + d[2], gz
+
+    def timed(fn):
+        ts, out = [], None
+        for i in range(warmup + steps):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            out = fn()
+            b.record()
+            torch.cuda.synchronize()
+            if i >= warmup:
+                ts.append(a.elapsed_time(b))
+        return statistics.median(ts), out
+
+    fused_ms, got = timed(lambda: conv._double_backward_impl(x, y, w, dz, ex, ey, ew, *idx))
+    comp_ms, want = timed(composed)
+    conv.check_device_status()
+    err = max(float((a - b).abs().max() / b.abs().max()) for a, b in zip(got, want))
+    # per edge: Y, W and their cotangents read twice (once per launch), GY, GW written; per node: X, EX twice, dZ, GX, GdZ
+    bytes_ = (e * (4 * yd + 4 * wn + yd + wn) + n * (4 * xd + zd + xd + zd)) * 4
+    peak, _ = measured_peak()
+    return {"nodes": n, "edges": e, "fused_ms": fused_ms, "composed_ms": comp_ms,
+            "edges_per_s": e / (fused_ms * 1e-3), "max_rel_diff_vs_composed": err,
+            "hbm_frac_fused": bytes_ / (fused_ms * 1e-3) / 1e9 / peak, "algorithmic_bytes": bytes_}
+
+
 def uvw_conv_case(torch, args, device, nodes=20_000, degree=40.0, steps=5, warmup=3):
     """Shared-weight 'uvw' convolution (64x(0e+1o+2e), harmonics to l=2) on a Nequip-sized graph: the unit-weight
     edge sum over the edges, then the dense contraction over the nodes; forward and backward (all gradients)."""
@@ -530,6 +580,7 @@ def secondary_block(torch, args, device, peaks):
     out["conv_mace_large_atomic_20k_nodes"] = conv_case(torch, args, WORKLOADS["mace_large"], "mace_large", device,
                                                         "atomic", "morton", nodes=20_000)
     out["batch_uvu_mace_50k_second_derivatives"] = second_derivative_case(torch, device)
+    out["conv_uvu_mace_20k_nodes_second_derivatives"] = conv_second_derivative_case(torch, args, device)
     out["conv_uvw_fc64_shared_20k_nodes"] = uvw_conv_case(torch, args, device)
     for dt, pk in (("f32", peaks["tf32_tflops"]), ("f64", peaks["fp64_tflops"])):
         r = bench_tp.measure("uvw_fc", dt, steps=10, warmup=3)

@@ -90,7 +90,8 @@ int oeq_set_kernel_dir(const char* path);
 int oeq_set_cache_dir(const char* path);
 
 /* Specialise (or fetch from the cache) the kernels of a problem without touching a
- * GPU.  kinds is a bit mask: 1 batch TP, 2 deterministic conv, 4 atomic conv. */
+ * GPU.  kinds is a bit mask: 1 batch TP, 2 deterministic conv, 4 atomic conv, 8 (with 2 or 4) also the
+ * second-derivative kernels of that convolution. */
 int oeq_precompile(const oeq_problem_desc* desc, int kinds);
 
 /* ---- batch tensor product --------------------------------------------------------
@@ -178,6 +179,23 @@ int oeq_conv_check(oeq_conv* h);
  * kernel; one receiver-order launch plus one row-sum launch per block of edges otherwise).  Benchmarks
  * report it; it has no counterpart in the reference. */
 int oeq_conv_last_backward_launches(const oeq_conv* h);
+
+/* Second derivatives of the convolution in two fused launches (plus the row sum of the deterministic variant).
+ * With dX, dY, dW the results of oeq_conv_backward for the output gradient dZ, and EX [nodes, x_dim], EY [edges,
+ * y_dim], EW [edges, weight_numel] cotangents of those three, this computes the gradients of
+ * <EX, dX> + <EY, dY> + <EW, dW> with respect to X, Y, W and dZ: GX [nodes, x_dim], GY, GW (per edge) and GdZ
+ * [nodes, z_dim].  The reference composes them from four backward and three forward launches of the same graph
+ * (openequivariance/implementations/convolution/ConvolutionBase.py, double_backward of the registered op); here an
+ * edge's rows and cotangent rows are staged once per launch.  rows/cols/perm as for oeq_conv_backward; the
+ * deterministic variant needs scratch of oeq_conv_workspace_bytes (it returns OEQ_ERR_UNSUPPORTED without it, and the
+ * caller composes the result from oeq_conv_forward / oeq_conv_backward instead).  The kernels are compiled at the
+ * first call.  oeq_conv_has_double_backward: 1 when the problem qualifies (per-edge weights, one thread per
+ * channel), else 0. */
+int oeq_conv_has_double_backward(const oeq_conv* h);
+int oeq_conv_double_backward(oeq_conv* h, int64_t nodes, int64_t edges, const void* X, const void* Y, const void* W,
+                             const void* dZ, const void* EX, const void* EY, const void* EW, const int64_t* rows,
+                             const int64_t* cols, const int64_t* sender_perm, void* GX, void* GY, void* GW, void* GdZ,
+                             void* workspace, size_t workspace_bytes, void* stream);
 
 /* Exercises the error path of the kernels' bounded waits without harming the device: one thread polls a barrier
  * that nothing completes `polls` times (at most 2^20), gives up, and the call reports what oeq_*_check would report,

@@ -18,10 +18,12 @@ import numpy as np
 from .wigner import cg_nonzeros
 
 OEQ_OK = 0
+OEQ_ERR_UNSUPPORTED = 2
 ERR_NAMES = {1: "invalid argument", 2: "unsupported problem", 3: "kernel specialisation failed",
              4: "CUDA error", 5: "device-side wait abandoned"}
 
 KIND_BATCH, KIND_CONV_DET, KIND_CONV_ATOMIC = 1, 2, 4
+KIND_CONV_SECOND = 8    # with a convolution kind: also the second-derivative kernels of that convolution
 
 
 class OeqError(RuntimeError):
@@ -73,6 +75,8 @@ SYMBOLS = {
     "oeq_conv_backward": (_INT, [_P, _I64, _I64, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _SZ, _P]),
     "oeq_conv_check": (_INT, [_P]),
     "oeq_conv_last_backward_launches": (_INT, [_P]),
+    "oeq_conv_has_double_backward": (_INT, [_P]),
+    "oeq_conv_double_backward": (_INT, [_P, _I64, _I64] + [_P] * 14 + [_P, _SZ, _P]),
     "oeq_selftest_bounded_wait": (_INT, [_INT, _P]),
     "oeq_tp_launch_info": (_INT, [_P, _INT, _PI, _PI, _PI, _PI, _PI, _PI]),
     "oeq_conv_launch_info": (_INT, [_P, _INT, _PI, _PI, _PI, _PI, _PI, _PI]),
@@ -232,6 +236,14 @@ class ConvHandle(_Handle):
 
     def last_backward_launches(self):
         return int(lib().oeq_conv_last_backward_launches(self.ptr))
+
+    def has_double_backward(self):
+        return bool(lib().oeq_conv_has_double_backward(self.ptr))
+
+    def double_backward(self, nodes, edges, x, y, w, dz, ex, ey, ew, rows, cols, perm, gx, gy, gw, gdz,
+                        ws, ws_bytes, stream):
+        check(lib().oeq_conv_double_backward(self.ptr, nodes, edges, x, y, w, dz, ex, ey, ew, rows, cols, perm,
+                                             gx, gy, gw, gdz, ws, ws_bytes, stream))
 
     def launch_info(self, which):
         return self._info(lib().oeq_conv_launch_info, which)

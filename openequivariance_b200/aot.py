@@ -71,7 +71,8 @@ def _run(job):
     for bit in (BATCH, DET, ATOMIC):
         if kinds & bit:
             try:
-                _native.precompile(problem, bit)
+                # convolutions: with the two second-derivative kernels, where the problem has them
+                _native.precompile(problem, bit if bit == BATCH else bit | _native.KIND_CONV_SECOND)
             except _native.OeqError as err:
                 if err.code != 2:  # "unsupported problem" is a property of the problem, not a build failure
                     raise

@@ -242,6 +242,33 @@ class TensorProductConv(TensorProductBase):
                                    torch.cuda.current_stream().cuda_stream)
         return dx, dy, dw
 
+    def _has_fused_double_backward(self):
+        return self.internal.has_double_backward()
+
+    def _double_backward_impl(self, x, y, w, dz, ex, ey, ew, rows, cols, perm=None):
+        """Gradients of ``<ex, dX> + <ey, dY> + <ew, dW>`` with respect to (x, y, w, dz) in two fused launches, or
+        ``None`` when the library cannot run them here (no scratch memory for the deterministic variant)."""
+        self._check(x, y, w, rows, cols, perm)
+        if self.deterministic and perm is None:
+            raise ValueError("the deterministic convolution needs sender_perm")
+        x, y, w, dz, ex, ey, ew = (t.contiguous() for t in (x, y, w, dz, ex, ey, ew))
+        rows, cols = rows.contiguous(), cols.contiguous()
+        perm_ptr = perm.contiguous().data_ptr() if (perm is not None and self.deterministic) else 0
+        gx, gy, gw, gdz = torch.empty_like(x), torch.empty_like(y), torch.empty_like(w), torch.empty_like(dz)
+        with torch.cuda.device(x.device):
+            ws_ptr, ws_bytes = self._backward_scratch(x.device, x.shape[0], rows.shape[0])
+            try:
+                self.internal.double_backward(x.shape[0], rows.shape[0], x.data_ptr(), y.data_ptr(), w.data_ptr(),
+                                              dz.data_ptr(), ex.data_ptr(), ey.data_ptr(), ew.data_ptr(),
+                                              rows.data_ptr(), cols.data_ptr(), perm_ptr, gx.data_ptr(),
+                                              gy.data_ptr(), gw.data_ptr(), gdz.data_ptr(), ws_ptr, ws_bytes,
+                                              torch.cuda.current_stream().cuda_stream)
+            except _native.OeqError as err:
+                if err.code == _native.OEQ_ERR_UNSUPPORTED:
+                    return None
+                raise
+        return gx, gy, gw, gdz
+
     def exec_conv_rawptrs(self, L1_in, L2_in, weights, L3_out, rows, cols, nnz, node_count, workspace=0,
                           stream=0):
         """Launch on raw device pointers; argument order of the reference's
@@ -324,6 +351,11 @@ class TensorProductConv(TensorProductBase):
             # same trilinear identity as the batch product, with the graph held fixed
             x, y, w, dz, idx = ctx.L1_in, ctx.L2_in, ctx.weights, ctx.L3_grad, ctx.index
             ex, ey, ew = grad_output[0], grad_output[1], grad_output[2]
+            if not torch.is_grad_enabled() and conv._has_fused_double_backward():
+                # nothing differentiates through this result: two launches that stage an edge's rows once each
+                fused = conv._double_backward_impl(x, y, w, dz, ex, ey, ew, *idx)
+                if fused is not None:
+                    return tuple(fused) + nones
             a = backward_helper(ex, ey, w, dz, *idx)
             b = backward_helper(x, y, ew, dz, *idx)
             c = backward_helper(ex, y, w, dz, *idx)

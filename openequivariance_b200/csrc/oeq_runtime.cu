@@ -918,6 +918,70 @@ int build_uvu_recv(const Problem& p, bool deterministic, Kernel& k) {
     return OEQ_OK;
 }
 
+// Second derivatives of the convolution in two launches (uvu_kernels.cuh, DBLC): a forward-like walk for the
+// gradient with respect to dZ and a receiver-order walk for the gradients with respect to X, Y, W.  Stages
+// carry the cotangent rows next to X, Y, W.
+constexpr int K_DBLC_Z_DET = 40, K_DBLC_Z_ATOMIC = 41, K_DBLC_G_DET = 42, K_DBLC_G_ATOMIC = 43;
+
+bool conv_double_backward_supported(const Problem& p) {
+    if (p.unit || !recv_backward_supported(p)) return false;
+    int zpc = 0, xpc = 0;
+    for (const Irrep& r : p.out) zpc += r.dim;
+    for (const Irrep& r : p.in1) xpc += r.dim;
+    if ((zpc + 3 * xpc + 2 * p.y_dim) * (p.elem() / 4) + 48 > 240) return false;    // registers of the forward-like walk
+    return env_int("OEQ_B200_FUSED_DOUBLE_BACKWARD", 1) != 0;
+}
+
+int build_uvu_dblc(const Problem& p, bool deterministic, bool grads, Kernel& k) {
+    Mapping& m = k.map;
+    const int e = p.elem();
+    const int xb = pad16(p.x_dim * e), yb = pad16(p.y_dim * e), wb = pad16(p.w_numel * e);
+    int rc;
+    if (grads) {
+        if ((rc = choose_mapping_recv(p, m))) return rc;
+        // fewer dZ values in registers than the first-derivative pass: the cotangents take their place
+        const int budget = env_int("OEQ_B200_GZ_REGS_DBL", p.dtype == OEQ_F64 ? 14 : 32);
+        m.gz_regs = budget;
+        m.gz_smem_values = 0;
+        int off = 0;
+        for (const Irrep& r : p.out) {
+            if (off >= budget) m.gz_smem_values += r.dim;
+            off += r.dim;
+        }
+        m.extra_bytes = 2 * xb + 5 * (m.mulg / 32) * yb + pad16(m.gz_smem_values * m.mulg * e);
+    } else {
+        int maxmul = 1;
+        for (const Instr& t : p.instr) maxmul = std::max(maxmul, p.in1[t.i1].mul);
+        for (const Irrep& r : p.out) maxmul = std::max(maxmul, r.mul);
+        m.mulg = (maxmul + 31) / 32 * 32;
+        m.nch = 1; m.ps = 1;
+        m.sw_bytes = 0;
+        m.extra_bytes = 0;
+        m.nph = 1;
+        m.z_ph_begin = {0, p.z_dim};
+        m.w_ph_begin = {0, p.w_numel};
+        m.phase_of_instr.assign(p.instr.size(), 0);
+    }
+    m.helper_warps = 0;
+    m.stage_bytes = 2 * (xb + yb + wb);
+    m.ng = 0;
+    for (int cand = std::max(1, std::min(8, 256 / m.mulg)); cand >= 1 && !m.ng; --cand) {
+        m.ng = cand;
+        if (m.smem(2) > SMEM_LIMIT) m.ng = 0;
+    }
+    if (!m.ng) return fail(OEQ_ERR_UNSUPPORTED, "an edge's rows and cotangent rows do not fit two shared-memory stages");
+    m.producer = (m.ng <= 4 && m.mulg >= 128) ? 1 : 0;
+    const int stages = std::min(m.max_stages(), 4);
+    m.min_ctas = std::max(1, std::min({stages >= 2 ? SMEM_LIMIT / (m.smem(stages) + 1024) : 1, 2048 / m.threads(), 2}));
+    assign_partitions(p, grads, m);
+    const int kind = grads ? (deterministic ? K_DBLC_G_DET : K_DBLC_G_ATOMIC) : (deterministic ? K_DBLC_Z_DET : K_DBLC_Z_ATOMIC);
+    const std::string macros = "#define OEQ_HELPER_WARPS 0\n";
+    rc = compile_kernel(descriptor_text(p, m) + macros, "uvu_kernels.cuh", kind, k.code);
+    if (rc) return rc;
+    k.compiled = true;
+    return OEQ_OK;
+}
+
 constexpr int K_FWD_DET_TC = 30, K_FWD_ATOMIC_TC = 31;
 
 int build_uvu_tc(const Problem& p, bool deterministic, Kernel& k) {
@@ -1229,6 +1293,9 @@ struct oeq_conv {
     Kernel bwd_recv;            // receiver-order backward pass (needs scratch in the deterministic variant)
     bool has_bwd_recv = false;
     cudaKernel_t sum_rows_fn = nullptr, clear_fn = nullptr;
+    Kernel dbl_z, dbl_g;        // second derivatives in two launches; compiled at first use
+    int dbl_state = 0;          // 0 not tried, 1 ready, -1 not available
+    cudaKernel_t dbl_sum_fn = nullptr, dbl_clear_fn = nullptr;
     int last_bwd_launches = 0;  // kernel launches of the most recent oeq_conv_backward
     int* d_status = nullptr;
     cudaStream_t last_stream = nullptr;
@@ -1306,6 +1373,16 @@ int oeq_precompile(const oeq_problem_desc* desc, int kinds) {
         Kernel k, kr;
         if (tc && (rc = build_uvu_tc(p, false, k))) return rc;
         if (recv && (rc = build_uvu_recv(p, false, kr))) return rc;
+    }
+    if ((kinds & 8) && (kinds & 6) && conv_double_backward_supported(p)) {
+        for (int det = 0; det < 2; ++det) {
+            if (!(kinds & (det ? 2 : 4))) continue;
+            for (int grads = 0; grads < 2; ++grads) {
+                Kernel k;
+                rc = build_uvu_dblc(p, det != 0, grads != 0, k);
+                if (rc && rc != OEQ_ERR_UNSUPPORTED) return rc;
+            }
+        }
     }
     return OEQ_OK;
 }
@@ -1754,6 +1831,8 @@ int oeq_conv_destroy(oeq_conv* h) {
     if (h->bwd.lib) cudaLibraryUnload(h->bwd.lib);
     if (h->fwd_tc.lib) cudaLibraryUnload(h->fwd_tc.lib);
     if (h->bwd_recv.lib) cudaLibraryUnload(h->bwd_recv.lib);
+    if (h->dbl_z.lib) cudaLibraryUnload(h->dbl_z.lib);
+    if (h->dbl_g.lib) cudaLibraryUnload(h->dbl_g.lib);
     delete h;
     return OEQ_OK;
 }
@@ -1974,6 +2053,110 @@ int oeq_conv_backward(oeq_conv* h, int64_t nodes, int64_t edges, const void* X, 
     }
 #endif
     return launch_uvu(h->bwd, p, prm, st);
+}
+
+// ---------------------------------------------------------------- second derivatives of the convolution
+
+int oeq_conv_has_double_backward(const oeq_conv* h) {
+    return h && h->dbl_state >= 0 && conv_double_backward_supported(h->prob) ? 1 : 0;
+}
+
+int oeq_conv_double_backward(oeq_conv* h, int64_t nodes, int64_t edges, const void* X, const void* Y, const void* W,
+                             const void* dZ, const void* EX, const void* EY, const void* EW, const int64_t* rows,
+                             const int64_t* cols, const int64_t* perm, void* GX, void* GY, void* GW, void* GdZ,
+                             void* workspace, size_t workspace_bytes, void* stream) {
+    if (!h) return fail(OEQ_ERR_INVALID, "null handle");
+    if (nodes < 0 || edges < 0) return fail(OEQ_ERR_INVALID, "negative size");
+    if (!oeq_conv_has_double_backward(h)) return fail(OEQ_ERR_UNSUPPORTED, "no fused second derivatives for this problem");
+    cudaStream_t st = (cudaStream_t)stream;
+    const Problem& p = h->prob;
+    if (nodes == 0) return OEQ_OK;
+    if (!GX || !GdZ) return fail(OEQ_ERR_INVALID, "null buffer");
+    const int e = p.elem();
+    if (edges == 0) {
+        OEQ_CUDA(cudaMemsetAsync(GX, 0, (size_t)nodes * p.x_dim * e, st));
+        OEQ_CUDA(cudaMemsetAsync(GdZ, 0, (size_t)nodes * p.z_dim * e, st));
+        return OEQ_OK;
+    }
+    if (!X || !Y || !W || !dZ || !EX || !EY || !EW || !rows || !cols || !GY || !GW) return fail(OEQ_ERR_INVALID, "null buffer");
+    if (h->deterministic && !perm) return fail(OEQ_ERR_INVALID, "deterministic second derivatives need the sender-order permutation");
+    const size_t row = recv_row_bytes(p);
+    long long block_edges = edges;
+    if (h->deterministic) {
+        if (!workspace || !aligned16(workspace)) return fail(OEQ_ERR_UNSUPPORTED, "deterministic second derivatives need scratch memory");
+        block_edges = (long long)std::min<size_t>(workspace_bytes / row, (size_t)edges);
+        if (block_edges < edges && block_edges < recv_min_block_edges())
+            return fail(OEQ_ERR_UNSUPPORTED, "deterministic second derivatives need more scratch memory");
+    }
+    int rc = ensure_status(&h->d_status);
+    if (rc) return rc;
+    if (h->dbl_state == 0) {
+        rc = build_uvu_dblc(p, h->deterministic, false, h->dbl_z);
+        if (!rc) rc = build_uvu_dblc(p, h->deterministic, true, h->dbl_g);
+        if (!rc) rc = load_kernel(h->dbl_z, "oeq_uvu_kernel", false);
+        if (!rc) rc = load_kernel(h->dbl_g, "oeq_uvu_kernel", false);
+        if (!rc) {
+            OEQ_CUDA(cudaLibraryGetKernel(&h->dbl_sum_fn, h->dbl_g.lib, "oeq_sum_sender_rows"));
+            OEQ_CUDA(cudaLibraryGetKernel(&h->dbl_clear_fn, h->dbl_g.lib, "oeq_clear"));
+        }
+        h->dbl_state = rc ? -1 : 1;
+        if (rc) return rc;
+    }
+    h->last_stream = st;
+    // bulk copies of a kind of row only when the row and its cotangent row both qualify
+    int clear = 0;
+    if (!aligned16(EX)) clear |= 1;
+    if (!aligned16(EY)) clear |= 2;
+    if (!aligned16(EW)) clear |= 4;
+    // gradient with respect to dZ: the forward walk over all edges
+    if (!h->deterministic) OEQ_CUDA(cudaMemsetAsync(GdZ, 0, (size_t)nodes * p.z_dim * e, st));
+    {
+        UvuParams prm{};
+        prm.X = X; prm.Y = Y; prm.W = W; prm.Z = GdZ; prm.EX = EX; prm.EY = EY; prm.EW = EW;
+        prm.rows = (const long long*)rows; prm.cols = (const long long*)cols;
+        prm.n_items = edges; prm.n_nodes = nodes; prm.status = h->d_status;
+        if ((rc = launch_uvu(h->dbl_z, p, prm, st, 0, 0, nullptr, clear))) return rc;
+    }
+    // gradients with respect to X, Y, W: the receiver-order walk, GX through scratch rows or bulk reductions
+    Kernel& k = h->dbl_g;
+    {
+        unsigned long long words = (unsigned long long)nodes * p.x_dim * e / 4;
+        void* ptr = GX;
+        void* args[] = {&ptr, &words};
+        const unsigned grid = (unsigned)std::max<unsigned long long>(1, std::min<unsigned long long>((unsigned long long)k.sm_count * 8, (words / 4 + 255) / 256));
+        OEQ_CUDA(cudaLaunchKernel((const void*)h->dbl_clear_fn, dim3(grid), dim3(256), args, 0, st));
+    }
+    const int dx_bulk = ((p.x_dim * e) % 16 == 0 && aligned16(GX)) ? 32 : 0;
+    const int sum_chunk = std::max(1, env_int("OEQ_B200_SUM_CHUNK", 64));
+    bool first = true;
+    for (long long e0 = 0; e0 < edges; e0 += block_edges) {
+        const long long n = std::min(block_edges, edges - e0);
+        const size_t yo = (size_t)e0 * p.y_dim * e, wo = (size_t)e0 * p.w_numel * e;
+        UvuParams prm{};
+        prm.X = X; prm.dZ = dZ; prm.dX = GX; prm.EX = EX;
+        prm.Y = (const char*)Y + yo; prm.W = (const char*)W + wo;
+        prm.EY = (const char*)EY + yo; prm.EW = (const char*)EW + wo;
+        prm.dY = (char*)GY + yo; prm.dW = (char*)GW + wo;
+        prm.rows = (const long long*)rows + e0; prm.cols = (const long long*)cols + e0;
+        prm.n_items = n; prm.n_nodes = nodes; prm.status = h->d_status;
+        prm.ws = h->deterministic ? workspace : nullptr;
+        if ((rc = launch_uvu(k, p, prm, st, dx_bulk, 0, nullptr, clear))) return rc;
+        if (h->deterministic) {
+            UvuParams sp{};
+            sp.dX = GX; sp.ws = workspace;
+            sp.rows = (const long long*)rows; sp.cols = (const long long*)cols; sp.perm = (const long long*)perm;
+            sp.n_items = edges; sp.n_nodes = nodes; sp.status = h->d_status;
+            sp.flags = first ? 64 : 0;
+            sp.chunk = sum_chunk;
+            sp.e_lo = e0; sp.e_hi = e0 + n;
+            const long long chunks = (edges + sp.chunk - 1) / sp.chunk;
+            const long long grid = std::max<long long>(1, std::min<long long>((long long)k.sm_count * 6, (chunks + 7) / 8));
+            void* args[] = {&sp};
+            OEQ_CUDA(cudaLaunchKernel((const void*)h->dbl_sum_fn, dim3((unsigned)grid), dim3(256), args, 0, st));
+            first = false;
+        }
+    }
+    return OEQ_OK;
 }
 
 // ---------------------------------------------------------------- self-test of the bounded waits

@@ -35,8 +35,31 @@
 #pragma once
 #include "oeq_common.cuh"
 
+// kernels of this file, selected by OEQ_KERNEL
+#define OEQ_K_FWD_BATCH 0
+#define OEQ_K_BWD_BATCH 1
+#define OEQ_K_FWD_DET 2
+#define OEQ_K_BWD_DET 3
+#define OEQ_K_FWD_ATOMIC 4
+#define OEQ_K_BWD_ATOMIC 5
+#define OEQ_K_BWD_RECV_DET 6
+#define OEQ_K_BWD_RECV_ATOMIC 7
+#define OEQ_K_DBL_BATCH 8
+// second derivatives of the convolution: gradient with respect to dZ (forward-like walk), and the gradients with
+// respect to X, Y, W (receiver-order backward-like walk)
+#define OEQ_K_DBLC_Z_DET 40
+#define OEQ_K_DBLC_Z_ATOMIC 41
+#define OEQ_K_DBLC_G_DET 42
+#define OEQ_K_DBLC_G_ATOMIC 43
+
 namespace oeq {
 using namespace oeqd;
+
+#if defined(OEQ_KERNEL) && OEQ_KERNEL >= 40 && OEQ_KERNEL <= 43
+constexpr bool DBLC = true;     // stages also carry the cotangents EX (at the sender), EY, EW
+#else
+constexpr bool DBLC = false;
+#endif
 
 struct UvuParams {
     const T* X;
@@ -123,7 +146,10 @@ struct StageLayout {
     static constexpr int OFF_Y = OFF_X + XB;
     static constexpr int OFF_W = OFF_Y + YB;
     static constexpr int OFF_DZ = OFF_W + (BWD ? WPHB : WB);
-    static constexpr int BYTES = OFF_DZ + (BWD ? ZPHB : 0);
+    static constexpr int OFF_EX = OFF_DZ + (BWD ? ZPHB : 0);       // cotangent rows (second derivatives of the
+    static constexpr int OFF_EY = OFF_EX + (DBLC ? XB : 0);        // convolution only)
+    static constexpr int OFF_EW = OFF_EY + (DBLC ? YB : 0);
+    static constexpr int BYTES = OFF_EW + (DBLC ? WB : 0);
 };
 
 constexpr bool fwd_part_uses_in1(int q, int a) {
@@ -215,6 +241,23 @@ __device__ __forceinline__ void cg_backward(const XA& x, const YA& y, const GA& 
         if constexpr (cg_pair_last<P, N>()) {
             a[CG_I[N]] = fma(y[CG_J[N]], pij, a[CG_I[N]]);
             b[CG_J[N]] = fma(x[CG_I[N]], pij, b[CG_J[N]]);
+        }
+    });
+}
+
+// Second-derivative form of the above (convolution): with r = w ex + ew x,
+//   ay_i += y_j P_ij;  aey_i += ey_j P_ij;  b_j += r_i P_ij.
+template <int P, class RA, class YA, class EA, class GA, class AA, class BA>
+__device__ __forceinline__ void cg_backward_dbl(const RA& r, const YA& y, const EA& ey, const GA& g, AA& ay, AA& aey, BA& b) {
+    T pij = (T)0;
+    sfor<CG_BEGIN[P], CG_BEGIN[P + 1]>([&](auto n) {
+        constexpr int N = n;
+        if constexpr (cg_pair_first<P, N>()) pij = (T)CG_V[N] * g[CG_K[N]];
+        else pij = fma((T)CG_V[N], g[CG_K[N]], pij);
+        if constexpr (cg_pair_last<P, N>()) {
+            ay[CG_I[N]] = fma(y[CG_J[N]], pij, ay[CG_I[N]]);
+            aey[CG_I[N]] = fma(ey[CG_J[N]], pij, aey[CG_I[N]]);
+            b[CG_J[N]] = fma(r[CG_I[N]], pij, b[CG_J[N]]);
         }
     });
 }
@@ -446,7 +489,13 @@ __device__ __forceinline__ void issue_item(const UvuParams& p, const SMT& sm, in
         if (yb && first) bytes += YB;
         if (wb && !SHARED_W) bytes += wbytes;
         if (BWD && zb) bytes += zbytes;
+        if constexpr (DBLC) bytes += (xb ? XB : 0) + (yb ? YB : 0) + (wb ? WB : 0);
         mbar_arrive_expect_tx(full, bytes);
+        if constexpr (DBLC) {
+            if (xb) bulk_g2s(st + L::OFF_EX, p.EX + s * X_DIM, XB, full);
+            if (yb) bulk_g2s(st + L::OFF_EY, p.EY + e * Y_DIM, YB, full);
+            if (wb) bulk_g2s(st + L::OFF_EW, p.EW + e * (long long)W_NUMEL, WB, full);
+        }
         if constexpr (MODE == MODE_BATCH) {
             if (BWD && zb) bulk_g2s(st + L::OFF_DZ, zsrc, zbytes, full);
             if (wb && !SHARED_W) bulk_g2s(st + L::OFF_W, wsrc, wbytes, full);
@@ -479,6 +528,11 @@ __device__ __forceinline__ void issue_item(const UvuParams& p, const SMT& sm, in
         }
         if constexpr (BWD) {
             if (!zb) stage_row(st + L::OFF_DZ, zsrc, z_n, p.flags & 2048);
+        }
+        if constexpr (DBLC) {
+            if (!xb) stage_row(st + L::OFF_EX, p.EX + s * X_DIM, X_DIM, false);
+            if (!yb) stage_row(st + L::OFF_EY, p.EY + e * Y_DIM, Y_DIM, false);
+            if (!wb) stage_row(st + L::OFF_EW, p.EW + e * (long long)W_NUMEL, W_NUMEL, false);
         }
         cp_async_arrive_noinc(full);
     }
@@ -633,6 +687,47 @@ __device__ __forceinline__ void forward_item(const T* __restrict__ sX, const T* 
     });
 }
 
+// Forward-like pass of the convolution's second derivatives: this edge's contribution to the gradient with
+// respect to dZ, T(ex, y, w) + T(x, ey, w) + T(x, y, ew), as one contraction: with r_i = w ex_i + ew x_i,
+//   t_ij = r_i y_j + (w x_i) ey_j,   z_k += C_ijk t_ij.
+template <class ZA>
+__device__ __forceinline__ void forward_item_dbl(const T* __restrict__ sX, const T* __restrict__ sEX,
+                                                 const T* __restrict__ sY, const T* __restrict__ sEY,
+                                                 const T* __restrict__ sW, const T* __restrict__ sEW, int u, ZA& zacc) {
+    T yr[Y_DIM], eyr[Y_DIM];
+#pragma unroll
+    for (int j = 0; j < Y_DIM; ++j) { yr[j] = sY[j]; eyr[j] = sEY[j]; }
+    sfor<0, N_IN1>([&](auto a_) {
+        constexpr int a = a_;
+        constexpr int D1 = IN1_D[a];
+        const bool live = (IN1_MUL[a] == CHANNELS) || (u < IN1_MUL[a]);
+        T x[D1], ex[D1];
+#pragma unroll
+        for (int i = 0; i < D1; ++i) {
+            x[i] = live ? sX[IN1_OFF[a] + u * D1 + i] : (T)0;
+            ex[i] = live ? sEX[IN1_OFF[a] + u * D1 + i] : (T)0;
+        }
+        sfor<0, N_INSTR>([&](auto p_) {
+            constexpr int P = p_;
+            if constexpr (I_IN1[P] == a) {
+                constexpr int b = I_IN2[P], o = I_OUT[P];
+                const T w = live ? sW[weight_offset<P>(u, 0)] : (T)0;
+                const T ew = live ? sEW[weight_offset<P>(u, 0)] : (T)0;
+                T r[D1], wx[D1];
+#pragma unroll
+                for (int i = 0; i < D1; ++i) { r[i] = fma(w, ex[i], ew * x[i]); wx[i] = w * x[i]; }
+                T tij = (T)0;
+                sfor<CG_BEGIN[P], CG_BEGIN[P + 1]>([&](auto n) {
+                    constexpr int N = n;
+                    if constexpr (cg_pair_first<P, N>())
+                        tij = fma(r[CG_I[N]], yr[IN2_OFF[b] + CG_J[N]], wx[CG_I[N]] * eyr[IN2_OFF[b] + CG_J[N]]);
+                    zacc[ZR_OFF[o] + CG_K[N]] = fma((T)CG_V[N], tij, zacc[ZR_OFF[o] + CG_K[N]]);
+                });
+            }
+        });
+    });
+}
+
 // Visit every (output irrep, k) register of partition Q / channel chunk C.
 template <int Q, int C, class F>
 __device__ __forceinline__ void for_each_out(int u, F&& f) {
@@ -741,15 +836,21 @@ __device__ void run_forward(const UvuParams& p, const Smem<false, MODE>& sm, int
         const T* sX = reinterpret_cast<const T*>(st + L::OFF_X);
         const T* sY = reinterpret_cast<const T*>(st + L::OFF_Y);
         const T* sWt = SHARED_W ? sWshared : reinterpret_cast<const T*>(st + L::OFF_W);
-        sfor<0, PS>([&](auto q_) {
-            constexpr int Q = q_;
-            if (part == Q) {
-                sfor<0, NCH>([&](auto c_) {
-                    constexpr int C = c_;
-                    forward_item<Q, C>(sX, sY, sWt, u0 + C * MULG, zacc);
-                });
-            }
-        });
+        if constexpr (DBLC) {
+            static_assert(!DBLC || (PS == 1 && NCH == 1 && Y_IN_REGS && !SHARED_W && !UNIT_W), "one thread per channel");
+            forward_item_dbl(sX, reinterpret_cast<const T*>(st + L::OFF_EX), sY, reinterpret_cast<const T*>(st + L::OFF_EY),
+                             sWt, reinterpret_cast<const T*>(st + L::OFF_EW), u0, zacc);
+        } else {
+            sfor<0, PS>([&](auto q_) {
+                constexpr int Q = q_;
+                if (part == Q) {
+                    sfor<0, NCH>([&](auto c_) {
+                        constexpr int C = c_;
+                        forward_item<Q, C>(sX, sY, sWt, u0 + C * MULG, zacc);
+                    });
+                }
+            });
+        }
         if constexpr (MODE != MODE_BATCH) {
             if (hi >= 0) {                       // the chunk ends: close its last node and its empty tail
                 flush(node);
@@ -1199,6 +1300,7 @@ __device__ void run_backward_recv(const UvuParams& p, const Smem<true, MODE, tru
     using SM = Smem<true, MODE, true>;
     using L = typename SM::L;
     static_assert(PS == 1 && NCH == 1 && Y_IN_REGS && !SHARED_W, "receiver-order backward: one thread per channel");
+    static_assert(!DBLC || !UNIT_W, "second derivatives need the weight array");
     const int S = sm.stages;
     const int u = tg;
     const int lane = tg & 31;
@@ -1255,6 +1357,10 @@ __device__ void run_backward_recv(const UvuParams& p, const Smem<true, MODE, tru
         const T* sX = reinterpret_cast<const T*>(st + L::OFF_X);
         const T* sY = reinterpret_cast<const T*>(st + L::OFF_Y);
         const T* sWt = reinterpret_cast<const T*>(st + L::OFF_W);
+        // second derivatives: the cotangents of dX (at the sender), dY and dW of this edge
+        const T* sEX = reinterpret_cast<const T*>(st + L::OFF_EX);
+        const T* sEY = reinterpret_cast<const T*>(st + L::OFF_EY);
+        const T* sEW = reinterpret_cast<const T*>(st + L::OFF_EW);
 
         if (node != prev) {
             // a new run: this channel's slice of the receiver's output gradient, kept for the whole run
@@ -1286,14 +1392,54 @@ __device__ void run_backward_recv(const UvuParams& p, const Smem<true, MODE, tru
             constexpr int D1 = IN1_D[a];
             const bool live = (IN1_MUL[a] == CHANNELS) || (u < IN1_MUL[a]);
             T x[D1], dxa[D1];
+            T ex[DBLC ? D1 : 1];
 #pragma unroll
             for (int i = 0; i < D1; ++i) {
                 x[i] = live ? sX[IN1_OFF[a] + u * D1 + i] : (T)0;
                 dxa[i] = (T)0;
+                if constexpr (DBLC) ex[i] = live ? sEX[IN1_OFF[a] + u * D1 + i] : (T)0;
             }
             sfor<0, N_INSTR>([&](auto p_) {
                 constexpr int P = p_;
-                if constexpr (I_IN1[P] == a) {
+                if constexpr (I_IN1[P] == a && DBLC) {
+                    // gx = w A(ey) + ew A(y),  gy = B(w ex + ew x),  gw = <ex, A(y)> + <x, A(ey)>  with
+                    // A_i(v) = sum_j v_j P_ij, B_j(v) = sum_i v_i P_ij, P_ij = sum_k C_ijk dZ_k
+                    constexpr int b = I_IN2[P], o = I_OUT[P];
+                    constexpr int D2 = IN2_D[b];
+                    const T w = live ? sWt[weight_offset<P>(u, 0)] : (T)0;
+                    const T ew = live ? sEW[weight_offset<P>(u, 0)] : (T)0;
+                    T r[D1], ay[D1], aey[D1], bv[D2], eyv[D2];
+#pragma unroll
+                    for (int i = 0; i < D1; ++i) {
+                        r[i] = fma(w, ex[i], ew * x[i]);
+                        ay[i] = (T)0;
+                        aey[i] = (T)0;
+                    }
+#pragma unroll
+                    for (int j = 0; j < D2; ++j) {
+                        bv[j] = (T)0;
+                        eyv[j] = sEY[IN2_OFF[b] + j];      // one address for the whole warp: a broadcast read
+                    }
+                    if constexpr (out_reg_off(o) < GZ_REGS) {
+                        cg_backward_dbl<P>(r, &yr[IN2_OFF[b]], eyv, &gz[out_reg_off(o)], ay, aey, bv);
+                    } else {
+                        T gs[OUT_D[o]];
+#pragma unroll
+                        for (int k = 0; k < OUT_D[o]; ++k) gs[k] = gzs[(out_reg_off(o) - GZ_FIRST_SMEM + k) * G + u];
+                        cg_backward_dbl<P>(r, &yr[IN2_OFF[b]], eyv, gs, ay, aey, bv);
+                    }
+                    T tw = (T)0;
+#pragma unroll
+                    for (int i = 0; i < D1; ++i) {
+                        tw = fma(ex[i], ay[i], tw);
+                        tw = fma(x[i], aey[i], tw);
+                        dxa[i] = fma(w, aey[i], dxa[i]);
+                        dxa[i] = fma(ew, ay[i], dxa[i]);
+                    }
+                    if (live) __stcs(dwrow + weight_offset<P>(u, 0), tw);
+#pragma unroll
+                    for (int j = 0; j < D2; ++j) dyreg[IN2_OFF[b] + j] += bv[j];
+                } else if constexpr (I_IN1[P] == a) {
                     constexpr int b = I_IN2[P], o = I_OUT[P];
                     constexpr int D2 = IN2_D[b];
                     T av[D1], bv[D2];
@@ -1798,15 +1944,6 @@ __device__ __forceinline__ void uvu_body(const UvuParams& p) {
 // One entry point per translation unit, selected by OEQ_KERNEL (other kernel files include this
 // header for its building blocks and define OEQ_UVU_NO_ENTRY).
 #ifndef OEQ_UVU_NO_ENTRY
-#define OEQ_K_FWD_BATCH 0
-#define OEQ_K_BWD_BATCH 1
-#define OEQ_K_FWD_DET 2
-#define OEQ_K_BWD_DET 3
-#define OEQ_K_FWD_ATOMIC 4
-#define OEQ_K_BWD_ATOMIC 5
-#define OEQ_K_BWD_RECV_DET 6
-#define OEQ_K_BWD_RECV_ATOMIC 7
-#define OEQ_K_DBL_BATCH 8
 
 extern "C" __global__ void __launch_bounds__(oeq::NTHREADS, oeqd::MIN_CTAS) oeq_uvu_kernel(const oeq::UvuParams p) {
 #if OEQ_KERNEL == OEQ_K_FWD_BATCH
@@ -1827,6 +1964,14 @@ extern "C" __global__ void __launch_bounds__(oeq::NTHREADS, oeqd::MIN_CTAS) oeq_
     oeq::uvu_body_recv<oeq::MODE_ATOMIC>(p);
 #elif OEQ_KERNEL == OEQ_K_DBL_BATCH
     oeq::uvu_body_dbl<0>(p);
+#elif OEQ_KERNEL == OEQ_K_DBLC_Z_DET
+    oeq::uvu_body<oeq::MODE_DET, false>(p);
+#elif OEQ_KERNEL == OEQ_K_DBLC_Z_ATOMIC
+    oeq::uvu_body<oeq::MODE_ATOMIC, false>(p);
+#elif OEQ_KERNEL == OEQ_K_DBLC_G_DET
+    oeq::uvu_body_recv<oeq::MODE_DET>(p);
+#elif OEQ_KERNEL == OEQ_K_DBLC_G_ATOMIC
+    oeq::uvu_body_recv<oeq::MODE_ATOMIC>(p);
 #else
 #error "OEQ_KERNEL must select one of the uvu kernels"
 #endif
@@ -1842,7 +1987,7 @@ extern "C" __global__ void oeq_reduce_partials(const oeqd::T* ws, oeqd::T* out, 
     out[i] = s;
 }
 
-#if OEQ_KERNEL == OEQ_K_BWD_RECV_DET
+#if OEQ_KERNEL == OEQ_K_BWD_RECV_DET || OEQ_KERNEL == OEQ_K_DBLC_G_DET || OEQ_KERNEL == OEQ_K_DBLC_G_ATOMIC
 // Clears `bytes` bytes (a multiple of 4) at a 4-byte aligned address.  A kernel rather than a memset call: a
 // memset may be served by a copy engine, where it would queue behind host transfers that other streams have
 // in flight and stall the stream that runs the backward pass.

@@ -140,6 +140,77 @@ def test_autograd_and_double_backward():
         assert rel_err(a.cpu().numpy(), b.numpy()) < 1e-11
 
 
+@pytest.mark.parametrize("deterministic", [True, False])
+@pytest.mark.parametrize("name,dtype,tol", [("nequip_32", np.float32, 2e-5), ("mace_128", np.float32, 2e-5),
+                                            ("readme", np.float64, 1e-11), ("uvu_norm_path", np.float64, 1e-11)])
+def test_fused_second_derivatives(name, dtype, tol, deterministic):
+    """Second derivatives in two fused launches (taken when nothing differentiates through the result) against
+    the oracle's autograd and against the composed path (four backward and three forward launches)."""
+    p = problem_by_name(name, irrep_dtype=dtype, weight_dtype=dtype)
+    nodes = 40
+    rows, cols = random_graph(nodes, 700, seed=21)
+    rows, cols, order, perm = orc.coord_graph(rows, cols)
+    x, y, w, dz = conv_inputs(p, nodes, len(rows), 22)
+    x[5] = 0  # (values only; node 5 still sends)
+    conv = oeq.TensorProductConv(p, torch_op=True, deterministic=deterministic)
+    assert conv._has_fused_double_backward()
+    r, c, pm = cuda(rows, cols, perm)
+    index = (r, c, pm) if deterministic else (r, c)
+    xt, yt, wt, dzt = (t.requires_grad_(True) for t in cuda(x, y, w, dz))
+    rng = np.random.default_rng(23)
+    ex, ey, ew = (torch.from_numpy(rng.normal(size=a.shape).astype(dtype)).cuda() for a in (x, y, w))
+
+    def second(create_graph):
+        z = conv.forward(xt, yt, wt, *index)
+        dx, dy, dw = torch.autograd.grad(z, (xt, yt, wt), dzt, create_graph=True)
+        scalar = (dx * ex).sum() + (dy * ey).sum() + (dw * ew).sum()
+        return torch.autograd.grad(scalar, (xt, yt, wt, dzt), create_graph=create_graph)
+
+    fused = second(False)
+    composed = [t.detach() for t in second(True)]
+    conv.check_device_status()
+    cx, cy, cw, cdz = (torch.from_numpy(a.astype(np.float64)).requires_grad_(True) for a in (x, y, w, dz))
+    zz = orc.conv_torch(p, cx, cy, cw, torch.from_numpy(rows), torch.from_numpy(cols))
+    gx, gy, gw = torch.autograd.grad(zz, (cx, cy, cw), cdz, create_graph=True)
+    s = (gx * ex.cpu().double()).sum() + (gy * ey.cpu().double()).sum() + (gw * ew.cpu().double()).sum()
+    want = torch.autograd.grad(s, (cx, cy, cw, cdz))
+    for a, b, cmp in zip(fused, want, composed):
+        assert rel_err(a.cpu().numpy(), b.numpy()) < tol
+        assert rel_err(a.cpu().numpy(), cmp.cpu().numpy()) < tol
+    if deterministic:
+        again = second(False)
+        for a, b in zip(fused, again):
+            assert torch.equal(a, b)
+
+
+def test_fused_second_derivatives_edge_blocks(monkeypatch):
+    """Scratch smaller than the edge list: the receiver-order walk runs over blocks of edges."""
+    monkeypatch.setenv("OEQ_B200_BWD_SCRATCH_MB", "1")
+    monkeypatch.setenv("OEQ_B200_BWD_MIN_BLOCK", "64")
+    p = problem_by_name("mace_128")
+    nodes = 300
+    rows, cols = random_graph(nodes, 6000, seed=31)
+    rows, cols, order, perm = orc.coord_graph(rows, cols)
+    x, y, w, dz = conv_inputs(p, nodes, len(rows), 32)
+    conv = oeq.TensorProductConv(p, torch_op=True, deterministic=True)
+    r, c, pm = cuda(rows, cols, perm)
+    xt, yt, wt, dzt = cuda(x, y, w, dz)
+    assert conv.internal.workspace_bytes(nodes, len(rows)) < len(rows) * p.irreps_in1.dim * 4
+    rng = np.random.default_rng(33)
+    ex, ey, ew = (torch.from_numpy(rng.normal(size=a.shape).astype(np.float32)).cuda() for a in (x, y, w))
+    got = conv._double_backward_impl(xt, yt, wt, dzt, ex, ey, ew, r, c, pm)
+    assert got is not None
+    a = conv._backward_impl(ex, ey, wt, dzt, r, c, pm)
+    b = conv._backward_impl(xt, yt, ew, dzt, r, c, pm)
+    cc = conv._backward_impl(ex, yt, wt, dzt, r, c, pm)
+    d = conv._backward_impl(xt, ey, wt, dzt, r, c, pm)
+    gz = (conv._forward_impl(ex, yt, wt, r, c, pm) + conv._forward_impl(xt, ey, wt, r, c, pm)
+          + conv._forward_impl(xt, yt, ew, r, c, pm))
+    conv.check_device_status()
+    for u, v in zip(got, (a[0] + b[0], a[1] + b[1], cc[2] + d[2], gz)):
+        assert rel_err(u.cpu().numpy(), v.cpu().numpy()) < 2e-5
+
+
 def test_readme_call_sequence():
     """The reference README's convolution example (3 nodes, 4 edges), atomic then deterministic."""
     p = problem_by_name("readme")
