@@ -217,12 +217,15 @@ struct Mapping {
     int stage_bytes = 0, extra_bytes = 0, sw_bytes = 0;
     int helper_warps = 0;                     // receiver-order backward: warps that sum the previous block's rows
     int gz_regs = 1 << 20, gz_smem_values = 0; // receiver-order backward: dZ values in registers / parked in shared memory
+    int epi = 1;                              // edges per staged item (uvu_kernels.cuh, EPI)
+    int stage_cap = 4;                        // most stages a group takes
+    int chunk_floor = 32;                     // smallest chunk of consecutive edges a launch may deal out
     int threads() const { return ng * mulg * ps + 32 * ng * producer + 32 * helper_warps; }
-    int fixed_bytes(int stages) const { return ng * stages * 48 + ng * 128 + sw_bytes; }
+    int fixed_bytes(int stages) const { return ng * stages * (16 + 8 * (epi > 1 ? 4 + 2 * epi : 4)) + ng * 128 + sw_bytes; }
     int smem(int stages) const { return fixed_bytes(stages) + ng * (stages * stage_bytes + extra_bytes); }
     int max_stages() const {
         int s = 0;
-        while (s < 4 && smem(s + 1) <= SMEM_LIMIT) ++s;
+        while (s < stage_cap && smem(s + 1) <= SMEM_LIMIT) ++s;
         return s;
     }
 };
@@ -271,6 +274,29 @@ void assign_partitions(const Problem& p, bool bwd, Mapping& m) {
         x += p.in1[a].dim;
     }
     m.xpc = std::max(1, x);
+}
+
+// Narrow self-staging groups (one warp per group) of the receiver-order walks stage runs of consecutive edges:
+// the per-item fixed cost (list walk, copies, hand-off) is shared by up to `epi` edges.  Re-fits the group count.
+void apply_edges_per_item(const Problem& p, Mapping& m, int extra_per_group) {
+    m.epi = 1;
+    const int want = env_int("OEQ_B200_EPI", 2);
+    if (want <= 1 || want > 8 || m.producer || m.mulg * m.ps > 32 || p.shared) return;
+    const int e = p.elem();
+    const int xb = pad16(p.x_dim * e);
+    const int wrow = p.unit ? 0 : p.w_numel * e;
+    Mapping t = m;
+    t.epi = want;
+    t.stage_bytes = want * xb + pad16(want * p.y_dim * e) + pad16(want * wrow);
+    t.extra_bytes = extra_per_group;
+    // two stages of `want` edges keep as many edges in flight as four stages of one
+    t.stage_cap = std::max(2, std::min(4, env_int("OEQ_B200_EPI_STAGES", 2)));
+    while (t.ng > 1 && t.smem(t.stage_cap) > SMEM_LIMIT) --t.ng;
+    if (t.smem(t.stage_cap) > SMEM_LIMIT) return;
+    m = t;
+    const int stages = std::min(m.max_stages(), env_int("OEQ_B200_STAGES", 4));
+    const int by_smem = stages >= 2 ? SMEM_LIMIT / (m.smem(stages) + 1024) : 1;
+    m.min_ctas = std::max(1, std::min({by_smem, 2048 / m.threads(), 2}));
 }
 
 int choose_mapping(const Problem& p, int kind, Mapping& m) {
@@ -402,6 +428,9 @@ int choose_mapping(const Problem& p, int kind, Mapping& m) {
     }
     if (m.smem(2) > SMEM_LIMIT || m.ng * m.mulg * m.ps > 992 || m.ng < 1 || m.ng > 8)
         return fail(OEQ_ERR_INVALID, "OEQ_B200_PS / OEQ_B200_NG override does not fit");
+    if (!bwd && !batch) apply_edges_per_item(p, m, m.extra_bytes);
+    // deterministic walks align every chunk at a segment boundary (two dependent index reads per chunk)
+    m.chunk_floor = (kind == K_FWD_DET || kind == K_BWD_DET) ? 64 : 32;
     assign_partitions(p, bwd, m);
     if (env_int("OEQ_B200_VERBOSE", 0))
         fprintf(stderr, "[oeq_b200] kind %d: mulg %d nch %d ps %d ng %d threads %d stage %d B extra %d B max stages %d\n",
@@ -475,6 +504,7 @@ int choose_mapping_recv(const Problem& p, Mapping& m) {
     const int by_threads = 2048 / m.threads();
     m.min_ctas = env_int("OEQ_B200_MIN_CTAS_RECV", std::max(1, std::min({by_smem, by_threads, 2})));
     if (m.smem(2) > SMEM_LIMIT || m.ng < 1 || m.ng > 8) return fail(OEQ_ERR_INVALID, "OEQ_B200_NG_RECV override does not fit");
+    apply_edges_per_item(p, m, m.extra_bytes);
     assign_partitions(p, true, m);
     if (env_int("OEQ_B200_VERBOSE", 0))
         fprintf(stderr, "[oeq_b200] receiver-order backward: mulg %d ng %d threads %d stage %d B extra %d B max stages %d min ctas %d\n",
@@ -682,7 +712,7 @@ std::string descriptor_text(const Problem& p, const Mapping& m, const UvwConfig*
         o << buf;
     });
     s << "constexpr int MULG = " << m.mulg << ", NCH = " << m.nch << ", PS = " << m.ps << ", NG = " << m.ng
-      << ", PRODUCER = " << m.producer << ", MIN_CTAS = " << m.min_ctas << ";\n";
+      << ", PRODUCER = " << m.producer << ", MIN_CTAS = " << m.min_ctas << ", EPI = " << m.epi << ";\n";
     emit_array(s, "int", "FWD_PART_OF_OUT", m.part_of_out, put_int);
     emit_array(s, "int", "BWD_PART_OF_INSTR", m.part_of_instr, put_int);
     emit_array(s, "int", "ZR_OFF", m.zr_off, put_int);
@@ -910,7 +940,10 @@ int build_uvu_recv(const Problem& p, bool deterministic, Kernel& k) {
     // work.  With two wide groups and their staging warps that makes twelve warps, three per scheduler, the
     // same register ceiling (168) as the ten warps without helpers.
     k.map.helper_warps = deterministic ? std::max(0, env_int("OEQ_B200_HELPER_WARPS", 2)) : 0;
-    if (k.map.threads() > 1024) k.map.helper_warps = 0;
+    // narrow problems: their launches are too short for the pipelined row sum, and the two extra warps would
+    // lower the register ceiling of the one-warp groups
+    if (k.map.threads() > 1024 || k.map.epi > 1) k.map.helper_warps = 0;
+    k.map.chunk_floor = deterministic ? 64 : 32;
     const std::string macros = "#define OEQ_HELPER_WARPS " + std::to_string(k.map.helper_warps) + "\n";
     rc = compile_kernel(descriptor_text(p, k.map) + macros, "uvu_kernels.cuh", deterministic ? K_BWD_RECV_DET : K_BWD_RECV_ATOMIC, k.code);
     if (rc) return rc;
@@ -939,6 +972,8 @@ int build_uvu_dblc(const Problem& p, bool deterministic, bool grads, Kernel& k) 
     int rc;
     if (grads) {
         if ((rc = choose_mapping_recv(p, m))) return rc;
+        m.epi = 1;
+        m.stage_cap = 4;
         // fewer dZ values in registers than the first-derivative pass: the cotangents take their place
         const int budget = env_int("OEQ_B200_GZ_REGS_DBL", p.dtype == OEQ_F64 ? 14 : 32);
         m.gz_regs = budget;
@@ -1230,8 +1265,10 @@ int launch_uvu(Kernel& k, const Problem& p, UvuParams& prm, cudaStream_t stream,
     const int e = p.elem();
     int flags = 0;
     if ((p.x_dim * e) % 16 == 0 && aligned16(prm.X)) flags |= 1;
-    if ((p.y_dim * e) % 16 == 0 && aligned16(prm.Y)) flags |= 2;
-    if (!p.shared && !p.unit && (p.w_numel * e) % 16 == 0 && aligned16(prm.W)) flags |= 4;
+    // (with several edges per item a bulk copy covers a run of rows: the run has to be a 16-byte multiple)
+    const int epi = k.map.epi;
+    if ((p.y_dim * e * epi) % 16 == 0 && aligned16(prm.Y)) flags |= 2;
+    if (!p.shared && !p.unit && (p.w_numel * e * epi) % 16 == 0 && aligned16(prm.W)) flags |= 4;
     const void* zlike = prm.dZ ? prm.dZ : prm.Z;
     if ((p.z_dim * e) % 16 == 0 && aligned16(zlike)) flags |= 8;
     if (env_int("OEQ_B200_NO_BULK", 0)) flags = 0;
@@ -1245,11 +1282,19 @@ int launch_uvu(Kernel& k, const Problem& p, UvuParams& prm, cudaStream_t stream,
     }
     prm.flags = flags | extra_flags;
     prm.stages = k.stages;
-    prm.chunk = std::max(1, env_int("OEQ_B200_CHUNK", 128));
     long long want = (prm.n_items + k.map.ng - 1) / k.map.ng;
     long long grid = std::max<long long>(1, std::min<long long>((long long)k.sm_count * k.ctas_per_sm, want));
     if (max_ctas > 0) grid = std::min(grid, max_ctas);     // a caller with bounded scratch narrows the launch
     if (ctas_out) *ctas_out = grid;
+    // chunks of consecutive edges are dealt round-robin to the groups: 128 edges unless that leaves a group fewer
+    // than eight chunks (the last round then idles a large part of the machine)
+    int chunk = env_int("OEQ_B200_CHUNK", 0);
+    if (chunk <= 0) {
+        chunk = 128;
+        const long long groups = grid * k.map.ng;
+        while (chunk > k.map.chunk_floor && prm.n_items / (groups * chunk) < 8) chunk /= 2;
+    }
+    prm.chunk = std::max(1, chunk);
     void* args[] = {&prm};
     OEQ_CUDA(cudaLaunchKernel((const void*)k.fn, dim3((unsigned)grid), dim3((unsigned)k.threads()), args,
                               (size_t)k.smem, stream));

@@ -140,12 +140,22 @@ constexpr int max_phase_width(const int* begin) {
 constexpr int WPHB = (SHARED_W || UNIT_W) ? 0 : pad16(max_phase_width(W_PH_BEGIN) * ELEM);
 constexpr int ZPHB = pad16(max_phase_width(Z_PH_BEGIN) * ELEM);
 
+// Edges per staged item (descriptor constant EPI).  Narrow problems (a group is one warp) spend more instructions on
+// walking the edge list, issuing copies and barrier hand-offs than on arithmetic; with EPI > 1 an item is up to EPI
+// consecutive edges of the receiver-ordered list: one hand-off, one header, one copy of their Y rows and one of their
+// W rows (consecutive edges are contiguous there; rows unpadded), EPI gathered X rows.  Only the walks in
+// receiver order (forward pass, receiver-order backward pass) without staging warps use it.
+constexpr int HDR_SLOTS = EPI > 1 ? 4 + 2 * EPI : 4;     // edge/count, node bounds; then receivers and senders
+constexpr int SLOT_BYTES = 16 + 8 * HDR_SLOTS;           // two barriers and the header per (group, stage)
+constexpr int YBK = EPI > 1 ? pad16(EPI * Y_DIM * ELEM) : YB;
+constexpr int WBK = EPI > 1 ? ((SHARED_W || UNIT_W) ? 0 : pad16(EPI * W_NUMEL * ELEM)) : WB;
+
 template <bool BWD>
 struct StageLayout {
     static constexpr int OFF_X = 0;
-    static constexpr int OFF_Y = OFF_X + XB;
-    static constexpr int OFF_W = OFF_Y + YB;
-    static constexpr int OFF_DZ = OFF_W + (BWD ? WPHB : WB);
+    static constexpr int OFF_Y = OFF_X + (BWD ? 1 : EPI) * XB;
+    static constexpr int OFF_W = OFF_Y + (BWD ? YB : YBK);
+    static constexpr int OFF_DZ = OFF_W + (BWD ? WPHB : WBK);
     static constexpr int OFF_EX = OFF_DZ + (BWD ? ZPHB : 0);       // cotangent rows (second derivatives of the
     static constexpr int OFF_EY = OFF_EX + (DBLC ? XB : 0);        // convolution only)
     static constexpr int OFF_EW = OFF_EY + (DBLC ? YB : 0);
@@ -321,13 +331,13 @@ struct Smem {
     }
     __device__ unsigned long long* empty(int g, int s) const { return full(g, s) + 1; }
     __device__ long long* hdr(int g, int s) const {
-        return reinterpret_cast<long long*>(base + NG * stages * 16) + (g * stages + s) * 4;
+        return reinterpret_cast<long long*>(base + NG * stages * 16) + (g * stages + s) * HDR_SLOTS;
     }
     __device__ long long* total(int g) const {   // number of items of the group, -1 until known
-        return reinterpret_cast<long long*>(base + NG * stages * 48 + g * CTRL);
+        return reinterpret_cast<long long*>(base + NG * stages * SLOT_BYTES + g * CTRL);
     }
-    __device__ int* arrivals(int g) const { return reinterpret_cast<int*>(base + NG * stages * 48 + g * CTRL + 16); }
-    __device__ unsigned char* shared_w() const { return base + NG * stages * 48 + NG * CTRL; }
+    __device__ int* arrivals(int g) const { return reinterpret_cast<int*>(base + NG * stages * SLOT_BYTES + g * CTRL + 16); }
+    __device__ unsigned char* shared_w() const { return base + NG * stages * SLOT_BYTES + NG * CTRL; }
     __device__ unsigned char* group_base(int g) const {
         return shared_w() + SWB + (long long)g * (stages * L::BYTES + EXTRA);
     }
@@ -419,6 +429,43 @@ struct ItemWalker {
                 return true;
             }
         }
+    }
+
+    // Next run of up to EPI consecutive edges of the chunk (receiver-order walks): first edge e0, count, and in
+    // lane i < count the sender and receiver of edge e0 + i.  A run ends at a multiple of EPI (so that full runs
+    // start 16-byte aligned in the per-edge arrays), at the chunk's end or at the end of the 32-edge window.
+    __device__ bool next_block(long long& e0, int& cnt, long long& s_i, long long& r_i, long long& lo, long long& hi) {
+        static_assert(!(BWD && MODE == MODE_DET) || EPI == 1, "runs of edges need the list's own order");
+        lo = hi = -1;
+        if (pos >= end) {
+            if (!next_chunk()) return false;
+        }
+        if (block_base < 0 || pos >= block_base + 32) {
+            block_base = pos;
+            const long long k = pos + lane;
+            long long ls = 0, lr = 0;
+            if (k < end) {
+                ls = p.cols[k];
+                lr = p.rows[k];
+            }
+            is_ = ls; ir = lr;
+        }
+        const int src = (int)(pos - block_base);
+        long long n = end - pos;
+        const long long to_boundary = EPI - (pos % EPI);
+        if (to_boundary < n) n = to_boundary;
+        if (32 - src < n) n = 32 - src;
+        cnt = (int)n;
+        e0 = pos;
+        s_i = __shfl_sync(0xffffffffu, is_, (src + lane) & 31);
+        r_i = __shfl_sync(0xffffffffu, ir, (src + lane) & 31);
+        if (first_in_chunk) {
+            lo = node_lo;
+            first_in_chunk = false;
+        }
+        pos += cnt;
+        if (pos >= end) hi = node_hi;
+        return true;
     }
 
     // Next item: edge/row index e, sender s, receiver r, and the chunk's node range when the
@@ -536,6 +583,57 @@ __device__ __forceinline__ void issue_item(const UvuParams& p, const SMT& sm, in
         }
         cp_async_arrive_noinc(full);
     }
+}
+
+// Stage a run of `cnt` consecutive edges starting at e0 into ring slot `stage` (EPI > 1; all lanes of the
+// group's first warp; lane i < cnt holds sender and receiver of edge e0 + i).  Header: e0, cnt, lo, hi, then the
+// receivers, then the senders.  The barrier always takes the 32 per-lane arrivals (rows of a short run may
+// not qualify for a bulk copy).
+template <int MODE, class SMT>
+__device__ __forceinline__ void issue_block(const UvuParams& p, const SMT& sm, int g, int stage, int lane,
+                                            long long e0, int cnt, long long s_i, long long r_i, long long lo, long long hi) {
+    using L = StageLayout<false>;
+    const bool xb = p.flags & 1, yb = p.flags & 2, wb = p.flags & 4;
+    unsigned char* st = sm.stage(g, stage);
+    unsigned long long* full = sm.full(g, stage);
+    long long* h = sm.hdr(g, stage);
+    const unsigned ybytes = (unsigned)(cnt * Y_DIM * ELEM), wbytes = (unsigned)(cnt * W_NUMEL * ELEM);
+    const bool y_bulk = yb && (ybytes % 16u) == 0;
+    const bool w_bulk = !SHARED_W && !UNIT_W && wb && (wbytes % 16u) == 0;
+    const T* ysrc = p.Y + e0 * Y_DIM;
+    const T* wsrc = (SHARED_W || UNIT_W) ? nullptr : p.W + e0 * (long long)W_NUMEL;
+    if (lane < cnt) {
+        h[4 + lane] = r_i;
+        h[4 + EPI + lane] = s_i;
+    }
+    if (lane == 0) {
+        h[0] = e0;
+        h[1] = cnt;
+        h[2] = lo;
+        h[3] = hi;
+    }
+    __syncwarp();       // the header is complete before lane 0's arrival publishes it
+    const unsigned long long keep = l2_policy_evict_last(), stream = l2_policy_evict_first();
+    if (lane == 0) {
+        mbar_arrive_expect_tx(full, (xb ? (unsigned)cnt * XB : 0u) + (y_bulk ? ybytes : 0u) + (w_bulk ? wbytes : 0u));
+        if (w_bulk) bulk_g2s_hint(st + L::OFF_W, wsrc, wbytes, full, stream);
+        if (y_bulk) bulk_g2s_hint(st + L::OFF_Y, ysrc, ybytes, full, stream);
+    }
+    __syncwarp();       // the byte count is posted before any lane's copy can complete
+    if (xb && lane < cnt) bulk_g2s_hint(st + L::OFF_X + lane * XB, p.X + s_i * X_DIM, XB, full, keep);
+    if (!xb) {
+        for (int i = 0; i < cnt; ++i) {
+            const long long s = __shfl_sync(0xffffffffu, s_i, i);
+            for (int q = lane; q < X_DIM; q += 32) cp_async_elem<ELEM>((T*)(st + L::OFF_X + i * XB) + q, p.X + s * X_DIM + q);
+        }
+    }
+    if (!y_bulk)
+        for (int q = lane; q < cnt * Y_DIM; q += 32) cp_async_elem<ELEM>((T*)(st + L::OFF_Y) + q, ysrc + q);
+    if constexpr (!SHARED_W && !UNIT_W) {
+        if (!w_bulk)
+            for (int q = lane; q < cnt * W_NUMEL; q += 32) cp_async_elem<ELEM>((T*)(st + L::OFF_W) + q, wsrc + q);
+    }
+    cp_async_arrive_noinc(full);
 }
 
 // Producer warp of group g: stages the group's items as stage slots are handed back.
@@ -792,13 +890,26 @@ __device__ void run_forward(const UvuParams& p, const Smem<false, MODE>& sm, int
     bool more = true;
     auto issue_next = [&]() {
         if (!more) return;
-        long long e, s, r, lo, hi;
-        more = walker.next(e, s, r, lo, hi);
-        if (more) {
-            issue_item<MODE, false>(p, sm, g, (int)(issued % S), lane, e, s, r, lo, hi);
-            ++issued;
-        } else if (lane == 0) {
-            *reinterpret_cast<volatile long long*>(sm.total(g)) = issued;
+        if constexpr (EPI > 1) {
+            static_assert(EPI == 1 || (!PRODUCER && MODE != MODE_BATCH && !DBLC), "runs of edges: self-staging convolution walks");
+            long long e0, s_i, r_i, lo, hi;
+            int cnt;
+            more = walker.next_block(e0, cnt, s_i, r_i, lo, hi);
+            if (more) {
+                issue_block<MODE>(p, sm, g, (int)(issued % S), lane, e0, cnt, s_i, r_i, lo, hi);
+                ++issued;
+            } else if (lane == 0) {
+                *reinterpret_cast<volatile long long*>(sm.total(g)) = issued;
+            }
+        } else {
+            long long e, s, r, lo, hi;
+            more = walker.next(e, s, r, lo, hi);
+            if (more) {
+                issue_item<MODE, false>(p, sm, g, (int)(issued % S), lane, e, s, r, lo, hi);
+                ++issued;
+            } else if (lane == 0) {
+                *reinterpret_cast<volatile long long*>(sm.total(g)) = issued;
+            }
         }
     };
     if constexpr (!PRODUCER) {
@@ -819,8 +930,11 @@ __device__ void run_forward(const UvuParams& p, const Smem<false, MODE>& sm, int
         if (acquire_item<MODE, false>(p, sm, g, it) != 0) break;
         const long long* h = sm.hdr(g, stage);
         const unsigned char* st = sm.stage(g, stage);
-        const long long node = h[1];
-        const long long lo = h[2], hi = h[3];
+        const int n_edges = EPI > 1 ? (int)h[1] : 1;
+      for (int ei = 0; ei < n_edges; ++ei) {       // the edges of the item (one unless EPI > 1)
+        const long long node = EPI > 1 ? h[4 + ei] : h[1];
+        const long long lo = (EPI == 1 || ei == 0) ? h[2] : -1;
+        const long long hi = (EPI == 1 || ei == n_edges - 1) ? h[3] : -1;
         if constexpr (MODE != MODE_BATCH) {
             if (lo >= 0) next_unwritten = lo;   // a new chunk starts: its first node is unwritten
             if (prev >= 0 && node != prev) {
@@ -833,9 +947,9 @@ __device__ void run_forward(const UvuParams& p, const Smem<false, MODE>& sm, int
             }
             prev = node;
         }
-        const T* sX = reinterpret_cast<const T*>(st + L::OFF_X);
-        const T* sY = reinterpret_cast<const T*>(st + L::OFF_Y);
-        const T* sWt = SHARED_W ? sWshared : reinterpret_cast<const T*>(st + L::OFF_W);
+        const T* sX = reinterpret_cast<const T*>(st + L::OFF_X + (EPI > 1 ? ei * XB : 0));
+        const T* sY = reinterpret_cast<const T*>(st + L::OFF_Y) + (EPI > 1 ? ei * Y_DIM : 0);
+        const T* sWt = SHARED_W ? sWshared : reinterpret_cast<const T*>(st + L::OFF_W) + (EPI > 1 ? ei * W_NUMEL : 0);
         if constexpr (DBLC) {
             static_assert(!DBLC || (PS == 1 && NCH == 1 && Y_IN_REGS && !SHARED_W && !UNIT_W), "one thread per channel");
             forward_item_dbl(sX, reinterpret_cast<const T*>(st + L::OFF_EX), sY, reinterpret_cast<const T*>(st + L::OFF_EY),
@@ -858,6 +972,8 @@ __device__ void run_forward(const UvuParams& p, const Smem<false, MODE>& sm, int
                 if constexpr (MODE == MODE_DET) zero_nodes(node + 1, hi);
             }
         }
+      }
+        const long long node = h[1];             // (batch mode: the row)
         if constexpr (MODE == MODE_BATCH) {
             T* zb = zbuf + (it & 1) * (ZB / ELEM);
             // the bulk store that last read this buffer (two items ago) must be done
@@ -1325,14 +1441,27 @@ __device__ void run_backward_recv(const UvuParams& p, const Smem<true, MODE, tru
     bool more = true;
     auto issue_next = [&]() {
         if (!more) return;
-        long long e, s, r, lo, hi;
-        more = walker.next(e, s, r, lo, hi);
-        if (more) {
-            // header slot 2 carries the sender (the forward pass keeps a node bound there)
-            issue_item<MODE, false>(p, sm, g, (int)(issued % S), lane, e, s, r, s, hi);
-            ++issued;
-        } else if (lane == 0) {
-            *reinterpret_cast<volatile long long*>(sm.total(g)) = issued;
+        if constexpr (EPI > 1) {
+            static_assert(EPI == 1 || (!PRODUCER && !DBLC), "runs of edges: self-staging walks");
+            long long e0, s_i, r_i, lo, hi;
+            int cnt;
+            more = walker.next_block(e0, cnt, s_i, r_i, lo, hi);
+            if (more) {
+                issue_block<MODE>(p, sm, g, (int)(issued % S), lane, e0, cnt, s_i, r_i, lo, hi);
+                ++issued;
+            } else if (lane == 0) {
+                *reinterpret_cast<volatile long long*>(sm.total(g)) = issued;
+            }
+        } else {
+            long long e, s, r, lo, hi;
+            more = walker.next(e, s, r, lo, hi);
+            if (more) {
+                // header slot 2 carries the sender (the forward pass keeps a node bound there)
+                issue_item<MODE, false>(p, sm, g, (int)(issued % S), lane, e, s, r, s, hi);
+                ++issued;
+            } else if (lane == 0) {
+                *reinterpret_cast<volatile long long*>(sm.total(g)) = issued;
+            }
         }
     };
     if constexpr (!PRODUCER) {
@@ -1343,6 +1472,7 @@ __device__ void run_backward_recv(const UvuParams& p, const Smem<true, MODE, tru
     }
 
     long long prev = -1;
+    long long ec = 0;                    // edges processed (equals `it` unless EPI > 1)
     for (long long it = 0;; ++it) {
         const int stage = (int)(it % S);
         if constexpr (!PRODUCER) {
@@ -1351,12 +1481,14 @@ __device__ void run_backward_recv(const UvuParams& p, const Smem<true, MODE, tru
         if (acquire_item<MODE, false>(p, sm, g, it) != 0) break;
         const long long* h = sm.hdr(g, stage);
         const unsigned char* st = sm.stage(g, stage);
-        const long long item = h[0];
-        const long long node = h[1];     // receiver
-        const long long sender = h[2];
-        const T* sX = reinterpret_cast<const T*>(st + L::OFF_X);
-        const T* sY = reinterpret_cast<const T*>(st + L::OFF_Y);
-        const T* sWt = reinterpret_cast<const T*>(st + L::OFF_W);
+        const int n_edges = EPI > 1 ? (int)h[1] : 1;
+      for (int ei = 0; ei < n_edges; ++ei, ++ec) {       // the edges of the item (one unless EPI > 1)
+        const long long item = EPI > 1 ? h[0] + ei : h[0];
+        const long long node = EPI > 1 ? h[4 + ei] : h[1];     // receiver
+        const long long sender = EPI > 1 ? h[4 + EPI + ei] : h[2];
+        const T* sX = reinterpret_cast<const T*>(st + L::OFF_X + (EPI > 1 ? ei * XB : 0));
+        const T* sY = reinterpret_cast<const T*>(st + L::OFF_Y) + (EPI > 1 ? ei * Y_DIM : 0);
+        const T* sWt = reinterpret_cast<const T*>(st + L::OFF_W) + (EPI > 1 ? ei * W_NUMEL : 0);
         // second derivatives: the cotangents of dX (at the sender), dY and dW of this edge
         const T* sEX = reinterpret_cast<const T*>(st + L::OFF_EX);
         const T* sEY = reinterpret_cast<const T*>(st + L::OFF_EY);
@@ -1383,7 +1515,7 @@ __device__ void run_backward_recv(const UvuParams& p, const Smem<true, MODE, tru
             dyreg[j] = (T)0;
         }
         T* dwrow = p.dW + item * (long long)W_NUMEL;
-        T* dxrow = dxrows + (it & 1) * XS;
+        T* dxrow = dxrows + (ec & 1) * XS;
         const bool row_to_smem = MODE == MODE_DET || dx_bulk;
         // instructions grouped by their first-input irrep: only that block of X and of dX is live at a time,
         // and the block of the dX row leaves the registers as soon as its last instruction is done
@@ -1481,7 +1613,7 @@ __device__ void run_backward_recv(const UvuParams& p, const Smem<true, MODE, tru
         });
         // the stage has been read: hand it back
         if constexpr (PRODUCER) release_stage<MODE, false>(sm, g, stage, lane);
-        const int ring = (int)(it % DY_RING);
+        const int ring = (int)(ec % DY_RING);
         {
             constexpr int SHIFT = 5 - log2_int(next_pow2(Y_DIM));
             warp_reduce_vector<Y_DIM>(dyreg, lane);
@@ -1514,6 +1646,7 @@ __device__ void run_backward_recv(const UvuParams& p, const Smem<true, MODE, tru
                 p.dY[item * (long long)Y_DIM + first] = sum;
             }
         }
+      }
     }
     if (tg == 0) bulk_wait_all<0>();
 }
@@ -1639,7 +1772,7 @@ __device__ __forceinline__ void uvu_body_recv(const UvuParams& p) {
     Smem<true, MODE, true> sm(smem_raw, p.stages);
     const int tid = threadIdx.x;
     if (tid == 0) {
-        const bool any_elem = !(p.flags & 1) || !(p.flags & 2) || (!(p.flags & 4) && !UNIT_W);
+        const bool any_elem = EPI > 1 || !(p.flags & 1) || !(p.flags & 2) || (!(p.flags & 4) && !UNIT_W);
         for (int g = 0; g < NG; ++g) {
             for (int s = 0; s < p.stages; ++s) {
                 mbar_init(sm.full(g, s), 1 + (any_elem ? 32 : 0));
@@ -1913,7 +2046,8 @@ __device__ __forceinline__ void uvu_body(const UvuParams& p) {
     const int tid = threadIdx.x;
 
     if (tid == 0) {
-        const bool any_elem = !(p.flags & 1) || !(p.flags & 2) || (!(p.flags & 4) && !SHARED_W && !UNIT_W) || (BWD && !(p.flags & 8));
+        const bool any_elem = (EPI > 1 && !BWD) || !(p.flags & 1) || !(p.flags & 2) || (!(p.flags & 4) && !SHARED_W && !UNIT_W) ||
+                              (BWD && !(p.flags & 8));
         for (int g = 0; g < NG; ++g) {
             for (int s = 0; s < p.stages; ++s) {
                 mbar_init(sm.full(g, s), 1 + (any_elem ? 32 : 0));

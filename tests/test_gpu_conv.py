@@ -56,6 +56,26 @@ def test_fp64(deterministic):
     check_conv(p, 40, rows, cols, 10, deterministic, dtype=np.float64)
 
 
+@pytest.mark.parametrize("name,dtype,deterministic,epi", [("nequip_32", np.float32, True, 4), ("nequip_32", np.float32, False, 3),
+                                                         ("readme", np.float64, True, 3), ("readme", np.float32, False, 4)])
+def test_edges_per_item(name, dtype, deterministic, epi, monkeypatch):
+    """Narrow problems stage runs of consecutive edges as one item (two by default); other run lengths, ragged
+    runs at chunk ends, rows that do not qualify for bulk copies, and bit-equality with one edge per item in the
+    deterministic variant."""
+    p = problem_by_name(name, irrep_dtype=dtype, weight_dtype=dtype)
+    nodes = 57
+    rows, cols = random_graph(nodes, 1003, seed=41)
+    monkeypatch.setenv("OEQ_B200_EPI", str(epi))
+    monkeypatch.setenv("OEQ_B200_EPI_STAGES", "3")
+    conv, inputs, got = check_conv(p, nodes, rows, cols, 42, deterministic, dtype=dtype)
+    assert conv.internal.launch_info(0)["stages"] <= 3
+    if deterministic:
+        monkeypatch.setenv("OEQ_B200_EPI", "1")
+        one, _, want = check_conv(p, nodes, rows, cols, 42, deterministic, dtype=dtype)
+        for a, b in zip(got, want):
+            assert torch.equal(a, b)
+
+
 def test_fp64_widest_rows():
     """MACE-large rows in FP64: a backward stage only fits because the output-gradient row is staged in phases."""
     p = problem_by_name("mace_large_128", irrep_dtype=np.float64, weight_dtype=np.float64)
