@@ -803,6 +803,11 @@ def run_e2e(args, torch, dist, world, device, conv, det, x, y, w, dz, edges, loc
     (one GPU): copy in, run, copy out."""
     pin = lambda t: torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t)
     pinned_like = lambda t: torch.empty(t.shape, dtype=t.dtype, pin_memory=True)   # empty_like would not pin
+    # pinned buffers on the GPU's own NUMA node (a copy that crosses the socket interconnect is slower)
+    numa_node = None
+    if os.environ.get("OEQ_B200_NUMA_BIND", "1") != "0":
+        from openequivariance_b200.stream import bind_host_to_device_node
+        numa_node = bind_host_to_device_node(device.index if device.index is not None else 0)
 
     def barrier():
         if world > 1:
@@ -813,15 +818,18 @@ def run_e2e(args, torch, dist, world, device, conv, det, x, y, w, dz, edges, loc
         one()
         barrier()
         t0 = time.perf_counter()
+        marks = []
         for _ in range(args.e2e_steps):
             one()
+            marks.append(time.perf_counter())
         barrier()
         dt = torch.tensor([(time.perf_counter() - t0) / args.e2e_steps], device=device, dtype=torch.float64)
+        step_ms = [round((b - a) * 1e3, 1) for a, b in zip([t0] + marks[:-1], marks)]   # this rank's steps, one by one
         if world > 1:
             dist.all_reduce(dt, op=dist.ReduceOp.MAX)
         return {"value": edges / dt.item(), "unit": "edges/s", "h2d_bytes_per_step": int(h2d),
                 "d2h_bytes_per_step": int(d2h), "ms_per_step": dt.item() * 1e3, "steps": args.e2e_steps,
-                "warmup": 1, "note": note}
+                "warmup": 1, "step_ms_rank0": step_ms, "host_numa_node": numa_node, "note": note}
 
     if det:
         # host-tensor entry point of the sharded convolution: X of the rank's nodes goes in, the halo is

@@ -19,6 +19,43 @@ import numpy as np
 import torch
 
 
+def _parse_cpulist(text):
+    cpus = set()
+    for part in text.strip().split(","):
+        if not part:
+            continue
+        lo, _, hi = part.partition("-")
+        cpus.update(range(int(lo), int(hi or lo) + 1))
+    return cpus
+
+
+def bind_host_to_device_node(device_index: int, sysfs: str = "/sys", bus_id: str | None = None):
+    """Keep this process on the CPUs of the NUMA node that the GPU's PCIe link hangs off, so that the pinned
+    buffers it allocates afterwards (first touch) and the copies it drives do not cross the socket interconnect.
+    Returns the node number, or ``None`` when the machine has a single node, the information is missing, or
+    the process is not allowed on any of that node's CPUs (the affinity is then left as it is).  Only this
+    process's own affinity mask changes.  ``bus_id`` ("0000:66:00.0") overrides the device's own."""
+    import os
+    try:
+        if bus_id is None:
+            props = torch.cuda.get_device_properties(device_index)
+            bus_id = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        with open(f"{sysfs}/bus/pci/devices/{bus_id}/numa_node") as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return None
+        with open(f"{sysfs}/devices/system/node/node{node}/cpulist") as f:
+            cpus = _parse_cpulist(f.read())
+        allowed = os.sched_getaffinity(0)
+        mine = cpus & allowed
+        if not mine or mine == allowed:
+            return node if mine else None
+        os.sched_setaffinity(0, mine)
+        return node
+    except (OSError, ValueError, AttributeError):
+        return None
+
+
 class Slab:
     """Edges ``[e0, e1)``, receivers ``[r0, r1)`` and the slab's local index arrays."""
 

@@ -244,3 +244,30 @@ def test_row_sharded_tensor_product_two_ranks():
             want = dw_ref if p.shared_weights else dw_ref[lo:hi]
             assert rel_err(dw.numpy(), want.numpy()) < 1e-12       # every rank holds the full sum of a shared gradient
 
+
+
+def test_bind_host_to_device_node(tmp_path):
+    """The helper that keeps a streaming process on the GPU's NUMA node, against a made-up sysfs tree."""
+    import os
+    from openequivariance_b200.stream import bind_host_to_device_node, _parse_cpulist
+    assert _parse_cpulist("0-2,5,8-9\n") == {0, 1, 2, 5, 8, 9}
+    before = os.sched_getaffinity(0)
+    first = min(before)
+    bus = "0000:66:00.0"
+    dev = tmp_path / "bus" / "pci" / "devices" / bus
+    dev.mkdir(parents=True)
+    node = tmp_path / "devices" / "system" / "node" / "node1"
+    node.mkdir(parents=True)
+    try:
+        (dev / "numa_node").write_text("-1\n")
+        assert bind_host_to_device_node(0, sysfs=str(tmp_path), bus_id=bus) is None      # single-node machine
+        (dev / "numa_node").write_text("1\n")
+        (node / "cpulist").write_text("100000-100003\n")
+        assert bind_host_to_device_node(0, sysfs=str(tmp_path), bus_id=bus) is None      # none of them allowed
+        assert os.sched_getaffinity(0) == before
+        (node / "cpulist").write_text(f"{first}\n")
+        assert bind_host_to_device_node(0, sysfs=str(tmp_path), bus_id=bus) == 1
+        assert os.sched_getaffinity(0) == {first}
+        assert bind_host_to_device_node(0, sysfs=str(tmp_path / "missing"), bus_id=bus) is None
+    finally:
+        os.sched_setaffinity(0, before)
