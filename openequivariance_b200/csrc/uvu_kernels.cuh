@@ -931,48 +931,48 @@ __device__ void run_forward(const UvuParams& p, const Smem<false, MODE>& sm, int
         const long long* h = sm.hdr(g, stage);
         const unsigned char* st = sm.stage(g, stage);
         const int n_edges = EPI > 1 ? (int)h[1] : 1;
-      for (int ei = 0; ei < n_edges; ++ei) {       // the edges of the item (one unless EPI > 1)
-        const long long node = EPI > 1 ? h[4 + ei] : h[1];
-        const long long lo = (EPI == 1 || ei == 0) ? h[2] : -1;
-        const long long hi = (EPI == 1 || ei == n_edges - 1) ? h[3] : -1;
-        if constexpr (MODE != MODE_BATCH) {
-            if (lo >= 0) next_unwritten = lo;   // a new chunk starts: its first node is unwritten
-            if (prev >= 0 && node != prev) {
-                flush(prev);
-                if constexpr (MODE == MODE_DET) next_unwritten = prev + 1 > next_unwritten ? prev + 1 : next_unwritten;
-            }
-            if constexpr (MODE == MODE_DET) {
-                if (next_unwritten < node) zero_nodes(next_unwritten, node);
-                next_unwritten = node + 1;
-            }
-            prev = node;
-        }
-        const T* sX = reinterpret_cast<const T*>(st + L::OFF_X + (EPI > 1 ? ei * XB : 0));
-        const T* sY = reinterpret_cast<const T*>(st + L::OFF_Y) + (EPI > 1 ? ei * Y_DIM : 0);
-        const T* sWt = SHARED_W ? sWshared : reinterpret_cast<const T*>(st + L::OFF_W) + (EPI > 1 ? ei * W_NUMEL : 0);
-        if constexpr (DBLC) {
-            static_assert(!DBLC || (PS == 1 && NCH == 1 && Y_IN_REGS && !SHARED_W && !UNIT_W), "one thread per channel");
-            forward_item_dbl(sX, reinterpret_cast<const T*>(st + L::OFF_EX), sY, reinterpret_cast<const T*>(st + L::OFF_EY),
-                             sWt, reinterpret_cast<const T*>(st + L::OFF_EW), u0, zacc);
-        } else {
-            sfor<0, PS>([&](auto q_) {
-                constexpr int Q = q_;
-                if (part == Q) {
-                    sfor<0, NCH>([&](auto c_) {
-                        constexpr int C = c_;
-                        forward_item<Q, C>(sX, sY, sWt, u0 + C * MULG, zacc);
-                    });
+        for (int ei = 0; ei < n_edges; ++ei) {       // the edges of the item (one unless EPI > 1)
+            const long long node = EPI > 1 ? h[4 + ei] : h[1];
+            const long long lo = (EPI == 1 || ei == 0) ? h[2] : -1;
+            const long long hi = (EPI == 1 || ei == n_edges - 1) ? h[3] : -1;
+            if constexpr (MODE != MODE_BATCH) {
+                if (lo >= 0) next_unwritten = lo;   // a new chunk starts: its first node is unwritten
+                if (prev >= 0 && node != prev) {
+                    flush(prev);
+                    if constexpr (MODE == MODE_DET) next_unwritten = prev + 1 > next_unwritten ? prev + 1 : next_unwritten;
                 }
-            });
-        }
-        if constexpr (MODE != MODE_BATCH) {
-            if (hi >= 0) {                       // the chunk ends: close its last node and its empty tail
-                flush(node);
-                prev = -1;
-                if constexpr (MODE == MODE_DET) zero_nodes(node + 1, hi);
+                if constexpr (MODE == MODE_DET) {
+                    if (next_unwritten < node) zero_nodes(next_unwritten, node);
+                    next_unwritten = node + 1;
+                }
+                prev = node;
+            }
+            const T* sX = reinterpret_cast<const T*>(st + L::OFF_X + (EPI > 1 ? ei * XB : 0));
+            const T* sY = reinterpret_cast<const T*>(st + L::OFF_Y) + (EPI > 1 ? ei * Y_DIM : 0);
+            const T* sWt = SHARED_W ? sWshared : reinterpret_cast<const T*>(st + L::OFF_W) + (EPI > 1 ? ei * W_NUMEL : 0);
+            if constexpr (DBLC) {
+                static_assert(!DBLC || (PS == 1 && NCH == 1 && Y_IN_REGS && !SHARED_W && !UNIT_W), "one thread per channel");
+                forward_item_dbl(sX, reinterpret_cast<const T*>(st + L::OFF_EX), sY, reinterpret_cast<const T*>(st + L::OFF_EY),
+                                 sWt, reinterpret_cast<const T*>(st + L::OFF_EW), u0, zacc);
+            } else {
+                sfor<0, PS>([&](auto q_) {
+                    constexpr int Q = q_;
+                    if (part == Q) {
+                        sfor<0, NCH>([&](auto c_) {
+                            constexpr int C = c_;
+                            forward_item<Q, C>(sX, sY, sWt, u0 + C * MULG, zacc);
+                        });
+                    }
+                });
+            }
+            if constexpr (MODE != MODE_BATCH) {
+                if (hi >= 0) {                       // the chunk ends: close its last node and its empty tail
+                    flush(node);
+                    prev = -1;
+                    if constexpr (MODE == MODE_DET) zero_nodes(node + 1, hi);
+                }
             }
         }
-      }
         const long long node = h[1];             // (batch mode: the row)
         if constexpr (MODE == MODE_BATCH) {
             T* zb = zbuf + (it & 1) * (ZB / ELEM);
@@ -1482,171 +1482,171 @@ __device__ void run_backward_recv(const UvuParams& p, const Smem<true, MODE, tru
         const long long* h = sm.hdr(g, stage);
         const unsigned char* st = sm.stage(g, stage);
         const int n_edges = EPI > 1 ? (int)h[1] : 1;
-      for (int ei = 0; ei < n_edges; ++ei, ++ec) {       // the edges of the item (one unless EPI > 1)
-        const long long item = EPI > 1 ? h[0] + ei : h[0];
-        const long long node = EPI > 1 ? h[4 + ei] : h[1];     // receiver
-        const long long sender = EPI > 1 ? h[4 + EPI + ei] : h[2];
-        const T* sX = reinterpret_cast<const T*>(st + L::OFF_X + (EPI > 1 ? ei * XB : 0));
-        const T* sY = reinterpret_cast<const T*>(st + L::OFF_Y) + (EPI > 1 ? ei * Y_DIM : 0);
-        const T* sWt = reinterpret_cast<const T*>(st + L::OFF_W) + (EPI > 1 ? ei * W_NUMEL : 0);
-        // second derivatives: the cotangents of dX (at the sender), dY and dW of this edge
-        const T* sEX = reinterpret_cast<const T*>(st + L::OFF_EX);
-        const T* sEY = reinterpret_cast<const T*>(st + L::OFF_EY);
-        const T* sEW = reinterpret_cast<const T*>(st + L::OFF_EW);
+        for (int ei = 0; ei < n_edges; ++ei, ++ec) {       // the edges of the item (one unless EPI > 1)
+            const long long item = EPI > 1 ? h[0] + ei : h[0];
+            const long long node = EPI > 1 ? h[4 + ei] : h[1];     // receiver
+            const long long sender = EPI > 1 ? h[4 + EPI + ei] : h[2];
+            const T* sX = reinterpret_cast<const T*>(st + L::OFF_X + (EPI > 1 ? ei * XB : 0));
+            const T* sY = reinterpret_cast<const T*>(st + L::OFF_Y) + (EPI > 1 ? ei * Y_DIM : 0);
+            const T* sWt = reinterpret_cast<const T*>(st + L::OFF_W) + (EPI > 1 ? ei * W_NUMEL : 0);
+            // second derivatives: the cotangents of dX (at the sender), dY and dW of this edge
+            const T* sEX = reinterpret_cast<const T*>(st + L::OFF_EX);
+            const T* sEY = reinterpret_cast<const T*>(st + L::OFF_EY);
+            const T* sEW = reinterpret_cast<const T*>(st + L::OFF_EW);
 
-        if (node != prev) {
-            // a new run: this channel's slice of the receiver's output gradient, kept for the whole run
-            const T* zrow = p.dZ + node * (long long)Z_DIM;
-            sfor<0, N_OUT>([&](auto o_) {
-                constexpr int o = o_;
-                const bool live = (OUT_MUL[o] == CHANNELS) || (u < OUT_MUL[o]);
-#pragma unroll
-                for (int k = 0; k < OUT_D[o]; ++k) {
-                    const T v = live ? __ldg(zrow + OUT_OFF[o] + u * OUT_D[o] + k) : (T)0;
-                    if constexpr (out_reg_off(o) < GZ_REGS) gz[out_reg_off(o) + k] = v;
-                    else gzs[(out_reg_off(o) - GZ_FIRST_SMEM + k) * G + u] = v;    // private to this thread
-                }
-            });
-            prev = node;
-        }
-#pragma unroll
-        for (int j = 0; j < Y_DIM; ++j) {
-            yr[j] = sY[j];
-            dyreg[j] = (T)0;
-        }
-        T* dwrow = p.dW + item * (long long)W_NUMEL;
-        T* dxrow = dxrows + (ec & 1) * XS;
-        const bool row_to_smem = MODE == MODE_DET || dx_bulk;
-        // instructions grouped by their first-input irrep: only that block of X and of dX is live at a time,
-        // and the block of the dX row leaves the registers as soon as its last instruction is done
-        sfor<0, N_IN1>([&](auto a_) {
-            constexpr int a = a_;
-            constexpr int D1 = IN1_D[a];
-            const bool live = (IN1_MUL[a] == CHANNELS) || (u < IN1_MUL[a]);
-            T x[D1], dxa[D1];
-            T ex[DBLC ? D1 : 1];
-#pragma unroll
-            for (int i = 0; i < D1; ++i) {
-                x[i] = live ? sX[IN1_OFF[a] + u * D1 + i] : (T)0;
-                dxa[i] = (T)0;
-                if constexpr (DBLC) ex[i] = live ? sEX[IN1_OFF[a] + u * D1 + i] : (T)0;
+            if (node != prev) {
+                // a new run: this channel's slice of the receiver's output gradient, kept for the whole run
+                const T* zrow = p.dZ + node * (long long)Z_DIM;
+                sfor<0, N_OUT>([&](auto o_) {
+                    constexpr int o = o_;
+                    const bool live = (OUT_MUL[o] == CHANNELS) || (u < OUT_MUL[o]);
+    #pragma unroll
+                    for (int k = 0; k < OUT_D[o]; ++k) {
+                        const T v = live ? __ldg(zrow + OUT_OFF[o] + u * OUT_D[o] + k) : (T)0;
+                        if constexpr (out_reg_off(o) < GZ_REGS) gz[out_reg_off(o) + k] = v;
+                        else gzs[(out_reg_off(o) - GZ_FIRST_SMEM + k) * G + u] = v;    // private to this thread
+                    }
+                });
+                prev = node;
             }
-            sfor<0, N_INSTR>([&](auto p_) {
-                constexpr int P = p_;
-                if constexpr (I_IN1[P] == a && DBLC) {
-                    // gx = w A(ey) + ew A(y),  gy = B(w ex + ew x),  gw = <ex, A(y)> + <x, A(ey)>  with
-                    // A_i(v) = sum_j v_j P_ij, B_j(v) = sum_i v_i P_ij, P_ij = sum_k C_ijk dZ_k
-                    constexpr int b = I_IN2[P], o = I_OUT[P];
-                    constexpr int D2 = IN2_D[b];
-                    const T w = live ? sWt[weight_offset<P>(u, 0)] : (T)0;
-                    const T ew = live ? sEW[weight_offset<P>(u, 0)] : (T)0;
-                    T r[D1], ay[D1], aey[D1], bv[D2], eyv[D2];
-#pragma unroll
-                    for (int i = 0; i < D1; ++i) {
-                        r[i] = fma(w, ex[i], ew * x[i]);
-                        ay[i] = (T)0;
-                        aey[i] = (T)0;
-                    }
-#pragma unroll
-                    for (int j = 0; j < D2; ++j) {
-                        bv[j] = (T)0;
-                        eyv[j] = sEY[IN2_OFF[b] + j];      // one address for the whole warp: a broadcast read
-                    }
-                    if constexpr (out_reg_off(o) < GZ_REGS) {
-                        cg_backward_dbl<P>(r, &yr[IN2_OFF[b]], eyv, &gz[out_reg_off(o)], ay, aey, bv);
-                    } else {
-                        T gs[OUT_D[o]];
-#pragma unroll
-                        for (int k = 0; k < OUT_D[o]; ++k) gs[k] = gzs[(out_reg_off(o) - GZ_FIRST_SMEM + k) * G + u];
-                        cg_backward_dbl<P>(r, &yr[IN2_OFF[b]], eyv, gs, ay, aey, bv);
-                    }
-                    T tw = (T)0;
-#pragma unroll
-                    for (int i = 0; i < D1; ++i) {
-                        tw = fma(ex[i], ay[i], tw);
-                        tw = fma(x[i], aey[i], tw);
-                        dxa[i] = fma(w, aey[i], dxa[i]);
-                        dxa[i] = fma(ew, ay[i], dxa[i]);
-                    }
-                    if (live) __stcs(dwrow + weight_offset<P>(u, 0), tw);
-#pragma unroll
-                    for (int j = 0; j < D2; ++j) dyreg[IN2_OFF[b] + j] += bv[j];
-                } else if constexpr (I_IN1[P] == a) {
-                    constexpr int b = I_IN2[P], o = I_OUT[P];
-                    constexpr int D2 = IN2_D[b];
-                    T av[D1], bv[D2];
-#pragma unroll
-                    for (int i = 0; i < D1; ++i) av[i] = (T)0;
-#pragma unroll
-                    for (int j = 0; j < D2; ++j) bv[j] = (T)0;
-                    const T w = live ? (UNIT_W ? (T)1 : sWt[weight_offset<P>(u, 0)]) : (T)0;
-                    if constexpr (out_reg_off(o) < GZ_REGS) {
-                        cg_backward<P>(x, &yr[IN2_OFF[b]], &gz[out_reg_off(o)], av, bv);
-                    } else {
-                        // this output irrep's slice of dZ is parked in shared memory ([value][channel]: no conflicts)
-                        T gs[OUT_D[o]];
-#pragma unroll
-                        for (int k = 0; k < OUT_D[o]; ++k) gs[k] = gzs[(out_reg_off(o) - GZ_FIRST_SMEM + k) * G + u];
-                        cg_backward<P>(x, &yr[IN2_OFF[b]], gs, av, bv);
-                    }
-                    T tw = (T)0;
-#pragma unroll
-                    for (int i = 0; i < D1; ++i) {
-                        tw = fma(x[i], av[i], tw);
-                        dxa[i] = fma(w, av[i], dxa[i]);
-                    }
-                    if constexpr (!UNIT_W) {
-                        if (live) __stcs(dwrow + weight_offset<P>(u, 0), tw);
-                    }
-#pragma unroll
-                    for (int j = 0; j < D2; ++j) dyreg[IN2_OFF[b] + j] = fma(w, bv[j], dyreg[IN2_OFF[b] + j]);
-                }
-            });
-            if (live) {
-#pragma unroll
+    #pragma unroll
+            for (int j = 0; j < Y_DIM; ++j) {
+                yr[j] = sY[j];
+                dyreg[j] = (T)0;
+            }
+            T* dwrow = p.dW + item * (long long)W_NUMEL;
+            T* dxrow = dxrows + (ec & 1) * XS;
+            const bool row_to_smem = MODE == MODE_DET || dx_bulk;
+            // instructions grouped by their first-input irrep: only that block of X and of dX is live at a time,
+            // and the block of the dX row leaves the registers as soon as its last instruction is done
+            sfor<0, N_IN1>([&](auto a_) {
+                constexpr int a = a_;
+                constexpr int D1 = IN1_D[a];
+                const bool live = (IN1_MUL[a] == CHANNELS) || (u < IN1_MUL[a]);
+                T x[D1], dxa[D1];
+                T ex[DBLC ? D1 : 1];
+    #pragma unroll
                 for (int i = 0; i < D1; ++i) {
-                    if (row_to_smem) dxrow[IN1_OFF[a] + u * D1 + i] = dxa[i];
-                    else if constexpr (any_part_uses_in1(a))
-                        red_add(p.dX + sender * (long long)X_DIM + IN1_OFF[a] + u * D1 + i, dxa[i]);
+                    x[i] = live ? sX[IN1_OFF[a] + u * D1 + i] : (T)0;
+                    dxa[i] = (T)0;
+                    if constexpr (DBLC) ex[i] = live ? sEX[IN1_OFF[a] + u * D1 + i] : (T)0;
+                }
+                sfor<0, N_INSTR>([&](auto p_) {
+                    constexpr int P = p_;
+                    if constexpr (I_IN1[P] == a && DBLC) {
+                        // gx = w A(ey) + ew A(y),  gy = B(w ex + ew x),  gw = <ex, A(y)> + <x, A(ey)>  with
+                        // A_i(v) = sum_j v_j P_ij, B_j(v) = sum_i v_i P_ij, P_ij = sum_k C_ijk dZ_k
+                        constexpr int b = I_IN2[P], o = I_OUT[P];
+                        constexpr int D2 = IN2_D[b];
+                        const T w = live ? sWt[weight_offset<P>(u, 0)] : (T)0;
+                        const T ew = live ? sEW[weight_offset<P>(u, 0)] : (T)0;
+                        T r[D1], ay[D1], aey[D1], bv[D2], eyv[D2];
+    #pragma unroll
+                        for (int i = 0; i < D1; ++i) {
+                            r[i] = fma(w, ex[i], ew * x[i]);
+                            ay[i] = (T)0;
+                            aey[i] = (T)0;
+                        }
+    #pragma unroll
+                        for (int j = 0; j < D2; ++j) {
+                            bv[j] = (T)0;
+                            eyv[j] = sEY[IN2_OFF[b] + j];      // one address for the whole warp: a broadcast read
+                        }
+                        if constexpr (out_reg_off(o) < GZ_REGS) {
+                            cg_backward_dbl<P>(r, &yr[IN2_OFF[b]], eyv, &gz[out_reg_off(o)], ay, aey, bv);
+                        } else {
+                            T gs[OUT_D[o]];
+    #pragma unroll
+                            for (int k = 0; k < OUT_D[o]; ++k) gs[k] = gzs[(out_reg_off(o) - GZ_FIRST_SMEM + k) * G + u];
+                            cg_backward_dbl<P>(r, &yr[IN2_OFF[b]], eyv, gs, ay, aey, bv);
+                        }
+                        T tw = (T)0;
+    #pragma unroll
+                        for (int i = 0; i < D1; ++i) {
+                            tw = fma(ex[i], ay[i], tw);
+                            tw = fma(x[i], aey[i], tw);
+                            dxa[i] = fma(w, aey[i], dxa[i]);
+                            dxa[i] = fma(ew, ay[i], dxa[i]);
+                        }
+                        if (live) __stcs(dwrow + weight_offset<P>(u, 0), tw);
+    #pragma unroll
+                        for (int j = 0; j < D2; ++j) dyreg[IN2_OFF[b] + j] += bv[j];
+                    } else if constexpr (I_IN1[P] == a) {
+                        constexpr int b = I_IN2[P], o = I_OUT[P];
+                        constexpr int D2 = IN2_D[b];
+                        T av[D1], bv[D2];
+    #pragma unroll
+                        for (int i = 0; i < D1; ++i) av[i] = (T)0;
+    #pragma unroll
+                        for (int j = 0; j < D2; ++j) bv[j] = (T)0;
+                        const T w = live ? (UNIT_W ? (T)1 : sWt[weight_offset<P>(u, 0)]) : (T)0;
+                        if constexpr (out_reg_off(o) < GZ_REGS) {
+                            cg_backward<P>(x, &yr[IN2_OFF[b]], &gz[out_reg_off(o)], av, bv);
+                        } else {
+                            // this output irrep's slice of dZ is parked in shared memory ([value][channel]: no conflicts)
+                            T gs[OUT_D[o]];
+    #pragma unroll
+                            for (int k = 0; k < OUT_D[o]; ++k) gs[k] = gzs[(out_reg_off(o) - GZ_FIRST_SMEM + k) * G + u];
+                            cg_backward<P>(x, &yr[IN2_OFF[b]], gs, av, bv);
+                        }
+                        T tw = (T)0;
+    #pragma unroll
+                        for (int i = 0; i < D1; ++i) {
+                            tw = fma(x[i], av[i], tw);
+                            dxa[i] = fma(w, av[i], dxa[i]);
+                        }
+                        if constexpr (!UNIT_W) {
+                            if (live) __stcs(dwrow + weight_offset<P>(u, 0), tw);
+                        }
+    #pragma unroll
+                        for (int j = 0; j < D2; ++j) dyreg[IN2_OFF[b] + j] = fma(w, bv[j], dyreg[IN2_OFF[b] + j]);
+                    }
+                });
+                if (live) {
+    #pragma unroll
+                    for (int i = 0; i < D1; ++i) {
+                        if (row_to_smem) dxrow[IN1_OFF[a] + u * D1 + i] = dxa[i];
+                        else if constexpr (any_part_uses_in1(a))
+                            red_add(p.dX + sender * (long long)X_DIM + IN1_OFF[a] + u * D1 + i, dxa[i]);
+                    }
+                }
+            });
+            // the stage has been read: hand it back
+            if constexpr (PRODUCER) release_stage<MODE, false>(sm, g, stage, lane);
+            const int ring = (int)(ec % DY_RING);
+            {
+                constexpr int SHIFT = 5 - log2_int(next_pow2(Y_DIM));
+                warp_reduce_vector<Y_DIM>(dyreg, lane);
+                const int j = lane >> SHIFT;
+                if ((lane & ((1 << SHIFT) - 1)) == 0 && j < Y_DIM) dyslots[(ring * WARPS_PER_GROUP + warp) * YS + j] = dyreg[0];
+            }
+            // the bulk copy that read the other dX row buffer (issued one edge ago) leaves this one alone; the copy
+            // that read *this* buffer two edges ago was waited for before the previous barrier
+            if (row_to_smem) {
+                fence_async_smem();                     // this thread's part of the row, visible to the bulk copy
+                if (tg == 0) bulk_wait_read<0>();       // every earlier row copy has read its buffer: the next edge may overwrite it
+            }
+            group_sync(bar_id, G);
+            if (tg == 0 && row_to_smem) {
+                if constexpr (MODE == MODE_DET) {
+                    bulk_s2g(reinterpret_cast<unsigned char*>(p.ws) + item * (long long)XB, dxrow, XB);
+                } else {
+                    if constexpr (ELEM == 4) bulk_red_add_f32(reinterpret_cast<float*>(p.dX) + sender * (long long)X_DIM, dxrow, XB);
+                    else bulk_red_add_f64(reinterpret_cast<double*>(p.dX) + sender * (long long)X_DIM, dxrow, XB);
+                }
+                bulk_commit();
+            }
+            {
+                const T* slots = dyslots + ring * WARPS_PER_GROUP * YS;
+                const int first = G >= 64 ? tg - 32 : tg;      // the second warp sums when there is one
+                if (first >= 0 && first < Y_DIM) {
+                    T sum = (T)0;
+    #pragma unroll
+                    for (int w = 0; w < WARPS_PER_GROUP; ++w) sum += slots[w * YS + first];
+                    p.dY[item * (long long)Y_DIM + first] = sum;
                 }
             }
-        });
-        // the stage has been read: hand it back
-        if constexpr (PRODUCER) release_stage<MODE, false>(sm, g, stage, lane);
-        const int ring = (int)(ec % DY_RING);
-        {
-            constexpr int SHIFT = 5 - log2_int(next_pow2(Y_DIM));
-            warp_reduce_vector<Y_DIM>(dyreg, lane);
-            const int j = lane >> SHIFT;
-            if ((lane & ((1 << SHIFT) - 1)) == 0 && j < Y_DIM) dyslots[(ring * WARPS_PER_GROUP + warp) * YS + j] = dyreg[0];
         }
-        // the bulk copy that read the other dX row buffer (issued one edge ago) leaves this one alone; the copy
-        // that read *this* buffer two edges ago was waited for before the previous barrier
-        if (row_to_smem) {
-            fence_async_smem();                     // this thread's part of the row, visible to the bulk copy
-            if (tg == 0) bulk_wait_read<0>();       // every earlier row copy has read its buffer: the next edge may overwrite it
-        }
-        group_sync(bar_id, G);
-        if (tg == 0 && row_to_smem) {
-            if constexpr (MODE == MODE_DET) {
-                bulk_s2g(reinterpret_cast<unsigned char*>(p.ws) + item * (long long)XB, dxrow, XB);
-            } else {
-                if constexpr (ELEM == 4) bulk_red_add_f32(reinterpret_cast<float*>(p.dX) + sender * (long long)X_DIM, dxrow, XB);
-                else bulk_red_add_f64(reinterpret_cast<double*>(p.dX) + sender * (long long)X_DIM, dxrow, XB);
-            }
-            bulk_commit();
-        }
-        {
-            const T* slots = dyslots + ring * WARPS_PER_GROUP * YS;
-            const int first = G >= 64 ? tg - 32 : tg;      // the second warp sums when there is one
-            if (first >= 0 && first < Y_DIM) {
-                T sum = (T)0;
-#pragma unroll
-                for (int w = 0; w < WARPS_PER_GROUP; ++w) sum += slots[w * YS + first];
-                p.dY[item * (long long)Y_DIM + first] = sum;
-            }
-        }
-      }
     }
     if (tg == 0) bulk_wait_all<0>();
 }
