@@ -640,6 +640,9 @@ def run_ours(args):
         local_edges = e_hi - e_lo
         node_lo = plan.node_lo if plan is not None else 0
         x = seeded_rows(torch, args.seed, STREAM_X, node_lo, node_lo + owned, problem.irreps_in1.dim, device)
+        if det and world > 1:
+            # node features live in the rank's gather buffer: the halo exchange copies no owned rows
+            x = conv.owned_buffer(x.shape[1], x.dtype).copy_(x)
         dz = seeded_rows(torch, args.seed, STREAM_DZ, node_lo, node_lo + owned, problem.irreps_out.dim, device)
         vec = torch.from_numpy(graph.vectors[e_lo:e_hi]).to(device=device, dtype=torch.float32)
         y = spherical_harmonics(spec["lmax"], vec).contiguous()

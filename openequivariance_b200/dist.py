@@ -178,14 +178,24 @@ class ShardedTensorProductConv:
             buf = torch.empty((plan.local_nodes, x_owned.shape[1]), dtype=x_owned.dtype, device=x_owned.device)
             if not fresh:
                 self._x_local = buf
-        buf[:plan.owned].copy_(x_owned)
+        if x_owned.data_ptr() != buf.data_ptr():        # a caller that filled ``owned_buffer`` has no copy to pay
+            buf[:plan.owned].copy_(x_owned)
         send = x_owned.index_select(0, self.send_index)
         dist.all_to_all_single(buf[plan.owned:], send, output_split_sizes=self.recv_counts,
                                input_split_sizes=self.send_counts, group=self.group)
         return buf
 
+    def owned_buffer(self, width: int, dtype=torch.float32) -> torch.Tensor:
+        """The first ``owned`` rows of the gather buffer: a caller that keeps its node features there saves
+        ``gather_senders`` the copy of the owned rows (the halo rows behind them are overwritten by every call)."""
+        buf = self._x_local
+        if buf is None or buf.dtype != dtype or buf.shape[1] != width:
+            buf = self._x_local = torch.empty((self.plan.local_nodes, width), dtype=dtype, device=self.device)
+        return buf[:self.plan.owned]
+
     def scatter_sender_grads(self, dx_local: torch.Tensor) -> torch.Tensor:
-        """Halo rows of dX go back to their owners and are added peer by peer in rank order."""
+        """Halo rows of dX go back to their owners and are added peer by peer in rank order.  The owned rows of
+        ``dx_local`` are updated in place and returned as a view."""
         plan = self.plan
         dx_owned = dx_local[:plan.owned]
         if self.world == 1:
@@ -193,7 +203,7 @@ class ShardedTensorProductConv:
         recv = torch.empty((sum(self.send_counts), dx_local.shape[1]), dtype=dx_local.dtype, device=dx_local.device)
         dist.all_to_all_single(recv, dx_local[plan.owned:].contiguous(), output_split_sizes=self.send_counts,
                                input_split_sizes=self.recv_counts, group=self.group)
-        out = dx_owned.clone()
+        out = dx_owned          # dx_local is this step's own result: the peers' rows are added in place
         start = 0
         for peer, count in enumerate(self.send_counts):      # fixed order; indices are unique within a peer
             if count:

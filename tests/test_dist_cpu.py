@@ -271,3 +271,21 @@ def test_bind_host_to_device_node(tmp_path):
         assert bind_host_to_device_node(0, sysfs=str(tmp_path / "missing"), bus_id=bus) is None
     finally:
         os.sched_setaffinity(0, before)
+
+
+def test_owned_buffer_alias_and_in_place_scatter():
+    """World size 1 on CPU tensors: the helpers that save copies keep their contracts (the first owned rows of
+    the gather buffer, and the owned rows of the local gradient returned as a view)."""
+    from openequivariance_b200.dist import ShardedTensorProductConv
+    rows = np.array([0, 0, 1, 2, 2], dtype=np.int64)
+    cols = np.array([1, 2, 0, 0, 1], dtype=np.int64)
+
+    class _NoKernels:           # the exchange steps never touch the local convolution
+        pass
+
+    conv = ShardedTensorProductConv(None, rows, cols, 3, device="cpu", local_conv=_NoKernels())
+    buf = conv.owned_buffer(4, torch.float64)
+    assert buf.shape == (3, 4) and buf.data_ptr() == conv.owned_buffer(4, torch.float64).data_ptr()
+    dx_local = torch.arange(12, dtype=torch.float64).reshape(3, 4)
+    out = conv.scatter_sender_grads(dx_local)
+    assert out.data_ptr() == dx_local.data_ptr() and torch.equal(out, dx_local)
