@@ -85,6 +85,8 @@ PROBLEMS = [
                            [[0, 0, 0, "uvu", True], [1, 1, 0, "uvu", True], [0, 1, 1, "uvu", True],
                             [1, 0, 1, "uvu", True]]],
      {"shared_weights": True, "internal_weights": False}),
+    # a small channel-wise problem for the interaction-block test (energies, forces, one training step)
+    ("interaction_8", "channelwise", ["8x0e+8x1o", "1x0e+1x1o", "8x0e+8x1o"], {}),
     # the reference's benchmark shapes with mixed parities and second-input multiplicity 1
     # (openequivariance/benchmark/benchmark_configs.py:38-47)
     ("tetris_poly_1", "fully_connected", ["1x0e + 1x1o + 1x2e + 1x3o", "1x0e + 1x1o + 1x2e + 1x3o",
