@@ -110,46 +110,82 @@ def measured_peak():
 
 
 class ClockSampler:
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    """SM clock and throttle reasons of one GPU, sampled by `nvidia-smi` in a child process.  The sampler is started
+    before the warm-up steps (the tool needs a moment to come up) and every sample carries the tool's time stamp;
+    `stop` keeps the samples that fall inside the marked region.  A timed region shorter than a sampling period
+    (multi-GPU runs: 10 steps take 0.1 s) falls back to the samples taken since the warm-up began, under the same
+    load, and says so in `window`."""
+    QUERY = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index=0):
         self.gpu_index, self.proc = gpu_index, None
+        self.started = self.begin = self.end = None
 
     def start(self):
+        import datetime
+        self.started = datetime.datetime.now()
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.gpu_index)],
+                                          "-lms", "50", "-i", str(self.gpu_index)],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except Exception:
             self.proc = None
 
+    def mark_begin(self):
+        import datetime
+        self.begin = datetime.datetime.now()
+
+    def mark_end(self):
+        import datetime
+        self.end = datetime.datetime.now()
+
+    @staticmethod
+    def parse(text):
+        """[(time stamp or None, sm MHz, max MHz, [active throttle reasons])] from the tool's CSV lines."""
+        import datetime
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        rows = []
+        for line in text.strip().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm, smax = float(parts[1]), float(parts[2])
+            except ValueError:
+                continue
+            try:
+                stamp = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f")
+            except ValueError:
+                stamp = None
+            rows.append((stamp, sm, smax, [n for n, flag in zip(names, parts[5:9]) if flag.lower().startswith("active")]))
+        return rows
+
+    def summarise(self, rows):
+        inside = [r for r in rows if r[0] is not None and self.begin and self.end and self.begin <= r[0] <= self.end]
+        window = "timed region"
+        if not inside:
+            inside = [r for r in rows if r[0] is None or self.started is None or r[0] >= self.started]
+            window = "warm-up and timed steps (the timed region is shorter than a sampling period)"
+        sm = [r[1] for r in inside]
+        reasons = sorted({name for r in inside for name in r[3]})
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": inside[-1][2] if inside else None,
+                "reasons": reasons, "samples": len(sm), "window": window}
+
     def stop(self):
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"], "samples": 0}
+        if self.end is None:
+            self.mark_end()
+        time.sleep(0.12)             # let the sample that covers the end of the region arrive
         self.proc.terminate()
         try:
             out, _ = self.proc.communicate(timeout=5)
         except Exception:
             self.proc.kill()
             out = ""
-        sm, smax, reasons = [], None, set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in out.strip().splitlines():
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 9:
-                continue
-            try:
-                sm.append(float(parts[1]))
-                smax = float(parts[2])
-            except ValueError:
-                continue
-            for name, flag in zip(names, parts[5:9]):
-                if flag.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": smax,
-                "reasons": sorted(reasons), "samples": len(sm)}
+        return self.summarise(self.parse(out))
 
 
 def build_graph(spec, args, numbering=None):
@@ -656,17 +692,18 @@ def run_ours(args):
             dx, dy, dw = conv.backward_helper(x, y, w, dz, rows_d, cols_d)
             return z, dx, dy, dw
 
+        sampler = ClockSampler(local_rank if os.environ.get("CUDA_VISIBLE_DEVICES") is None else 0)
+        sampler.start()
         for _ in range(max(3, args.warmup)):
             out = step()
             del out
         barrier()
 
         # -- timed region: device events per step, fwd and bwd passes timed separately on the rank's stream
-        sampler = ClockSampler(local_rank if os.environ.get("CUDA_VISIBLE_DEVICES") is None else 0)
         ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(steps)]
         inner = conv.conv if det else conv
-        sampler.start()
         barrier()
+        sampler.mark_begin()
         t0 = time.perf_counter()
         for k in range(steps):
             if det:
@@ -689,6 +726,7 @@ def run_ours(args):
                 del z, dx, dy, dw
         barrier()
         elapsed = time.perf_counter() - t0
+        sampler.mark_end()
         clocks = sampler.stop()
         inner.check_device_status()
         launches_bwd = max(1, inner.internal.last_backward_launches())
