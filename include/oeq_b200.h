@@ -175,9 +175,10 @@ int oeq_conv_backward(oeq_conv* h, int64_t nodes, int64_t edges, const void* X, 
 
 int oeq_conv_check(oeq_conv* h);
 
-/* Number of kernels the most recent oeq_conv_backward on this handle launched (1 for the sender-order
- * kernel; one receiver-order launch plus one row-sum launch per block of edges otherwise).  Benchmarks
- * report it; it has no counterpart in the reference. */
+/* Number of kernels the most recent oeq_conv_backward on this handle launched: 1 for the sender-order kernel
+ * and for the atomic receiver-order kernel; for the deterministic receiver-order pass the kernel that clears dX,
+ * one launch per block of edges (each sums the previous block's rows as well when the blocks are pipelined)
+ * and the row-sum launches.  Benchmarks report it; it has no counterpart in the reference. */
 int oeq_conv_last_backward_launches(const oeq_conv* h);
 
 /* Second derivatives of the convolution in two fused launches (plus the row sum of the deterministic variant).

@@ -2012,6 +2012,7 @@ int oeq_conv_backward(oeq_conv* h, int64_t nodes, int64_t edges, const void* X, 
             void* args[] = {&ptr, &words};
             const unsigned grid = (unsigned)std::max<unsigned long long>(1, std::min<unsigned long long>((unsigned long long)k.sm_count * 8, (words / 4 + 255) / 256));
             OEQ_CUDA(cudaLaunchKernel((const void*)h->clear_fn, dim3(grid), dim3(256), args, 0, st));
+            ++h->last_bwd_launches;
         }
         auto sum_launch = [&](long long e0, long long n, void* scratch, bool first) -> int {
             UvuParams sp{};
