@@ -76,6 +76,16 @@ def test_edges_per_item(name, dtype, deterministic, epi, monkeypatch):
             assert torch.equal(a, b)
 
 
+@pytest.mark.parametrize("name", ["nequip_32", "mace_128"])
+def test_element_copy_staging(name, monkeypatch):
+    """Rows staged with element copies instead of bulk copies (what unaligned buffers get), forced for every array."""
+    monkeypatch.setenv("OEQ_B200_NO_BULK", "1")
+    p = problem_by_name(name)
+    rows, cols = random_graph(31, 400, seed=51)
+    for deterministic in (True, False):
+        check_conv(p, 31, rows, cols, 52, deterministic)
+
+
 def test_fp64_widest_rows():
     """MACE-large rows in FP64: a backward stage only fits because the output-gradient row is staged in phases."""
     p = problem_by_name("mace_large_128", irrep_dtype=np.float64, weight_dtype=np.float64)
