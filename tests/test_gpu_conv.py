@@ -213,6 +213,39 @@ def test_fused_second_derivatives(name, dtype, tol, deterministic):
             assert torch.equal(a, b)
 
 
+def test_fused_second_derivatives_staging_variants(monkeypatch):
+    """Cotangent rows at addresses that rule out bulk copies, and bulk copies switched off altogether: same bits as
+    the aligned run of the deterministic variant (only the way rows reach shared memory differs)."""
+    p = problem_by_name("mace_128")
+    nodes = 50
+    rows, cols = random_graph(nodes, 900, seed=61)
+    rows, cols, order, perm = orc.coord_graph(rows, cols)
+    x, y, w, dz = conv_inputs(p, nodes, len(rows), 62)
+    conv = oeq.TensorProductConv(p, torch_op=True, deterministic=True)
+    r, c, pm = cuda(rows, cols, perm)
+    xt, yt, wt, dzt = cuda(x, y, w, dz)
+    rng = np.random.default_rng(63)
+    ex, ey, ew = (torch.from_numpy(rng.normal(size=a.shape).astype(np.float32)).cuda() for a in (x, y, w))
+    want = conv._double_backward_impl(xt, yt, wt, dzt, ex, ey, ew, r, c, pm)
+    assert want is not None
+
+    def shifted(t):           # the same values four bytes off a 16-byte boundary
+        buf = torch.empty(t.numel() + 1, dtype=t.dtype, device=t.device)
+        out = buf[1:].view(t.shape)
+        out.copy_(t)
+        assert out.data_ptr() % 16 == 4
+        return out
+
+    got = conv._double_backward_impl(xt, yt, wt, dzt, shifted(ex), shifted(ey), shifted(ew), r, c, pm)
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
+    monkeypatch.setenv("OEQ_B200_NO_BULK", "1")
+    got = conv._double_backward_impl(xt, yt, wt, dzt, ex, ey, ew, r, c, pm)
+    conv.check_device_status()
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
+
+
 def test_fused_second_derivatives_edge_blocks(monkeypatch):
     """Scratch smaller than the edge list: the receiver-order walk runs over blocks of edges."""
     monkeypatch.setenv("OEQ_B200_BWD_SCRATCH_MB", "1")
